@@ -1,0 +1,330 @@
+"""Python face of the native sm_100a library (``libcme213_b200.so``, built in-tree by :mod:`.build`).
+
+The library has a plain C ABI (pointers, sizes, a stream handle) and is loaded with ``ctypes``; every
+wrapper here takes ``torch`` tensors, checks them, passes ``data_ptr()`` and the current CUDA stream, and
+raises :class:`NativeError` with the library's message when a call fails.  There is no PyTorch fallback
+behind these functions: on a GPU machine a missing library is an error, not a silent slow path.
+
+The op list mirrors the reference's kernel header (``FINAL_CLEAN_CODE_/include/kernels.h:6-138``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libcme213_b200.so"
+_lib: Optional[ctypes.CDLL] = None
+_tried = False
+
+F32, BF16 = 0, 1
+ACT = {"none": 0, None: 0, "relu": 1, "gelu": 2}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class CmeGemm(ctypes.Structure):
+    _fields_ = [
+        ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("batch", ctypes.c_int),
+        ("A", ctypes.c_void_p), ("lda", ctypes.c_longlong), ("strideA", ctypes.c_longlong), ("a_trans", ctypes.c_int),
+        ("B", ctypes.c_void_p), ("ldb", ctypes.c_longlong), ("strideB", ctypes.c_longlong), ("b_trans", ctypes.c_int),
+        ("C", ctypes.c_void_p), ("ldc", ctypes.c_longlong), ("strideC", ctypes.c_longlong), ("c_dtype", ctypes.c_int),
+        ("ab_dtype", ctypes.c_int),
+        ("bias", ctypes.c_void_p),
+        ("residual", ctypes.c_void_p), ("ldres", ctypes.c_longlong),
+        ("aux_out", ctypes.c_void_p), ("aux_in", ctypes.c_void_p), ("ldaux", ctypes.c_longlong),
+        ("act", ctypes.c_int), ("dact", ctypes.c_int), ("accumulate", ctypes.c_int),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_longlong),
+        ("force_bn", ctypes.c_int), ("force_splits", ctypes.c_int),
+    ]
+
+
+def _load() -> Optional[ctypes.CDLL]:
+    global _lib, _tried
+    if _lib is not None or _tried:
+        return _lib
+    _tried = True
+    if not LIB_PATH.exists():
+        return None
+    try:
+        lib = ctypes.CDLL(str(LIB_PATH))
+    except OSError:
+        return None
+    lib.cme_last_error.restype = ctypes.c_char_p
+    lib.fnv1a_u32.restype = ctypes.c_ulonglong
+    lib.fnv1a_u32.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_ulonglong]
+    _lib = lib
+    return lib
+
+
+def host_lib() -> Optional[ctypes.CDLL]:
+    """The library if it has been built, else ``None`` (host-only helpers have Python fallbacks)."""
+    return _load()
+
+
+def lib() -> ctypes.CDLL:
+    l = _load()
+    if l is None:
+        raise NativeError(f"native library not found at {LIB_PATH}; run `python -m cme213_final_project_b200.ops.build`")
+    return l
+
+
+def available() -> bool:
+    return _load() is not None and torch.cuda.is_available()
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise NativeError(f"native call failed (status {rc}): {lib().cme_last_error().decode()}")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise NativeError(f"unsupported dtype {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _cuda(*ts) -> None:
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise NativeError("native ops need contiguous CUDA tensors")
+
+
+_workspaces = {}
+
+
+def workspace(nbytes: int = 64 << 20) -> torch.Tensor:
+    """Per-device fp32 scratch shared by split-K GEMMs launched through the Python wrappers."""
+    dev = torch.cuda.current_device()
+    w = _workspaces.get(dev)
+    if w is None or w.numel() * 4 < nbytes:
+        w = torch.empty(nbytes // 4, dtype=torch.float32, device="cuda")
+        _workspaces[dev] = w
+    return w
+
+
+# --------------------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_trans: bool = False, b_trans: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+         bias: Optional[torch.Tensor] = None, act: Optional[str] = None, aux_out: Optional[torch.Tensor] = None,
+         dact: Optional[str] = None, aux_in: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+         accumulate: bool = False, backend: str = "auto", force_bn: int = 0, force_splits: int = 0) -> torch.Tensor:
+    """``out (+)= epilogue(op(a) @ op(b))`` for 2-D or batched 3-D row-major operands.
+
+    ``a``: ``[M, K]`` (or ``[K, M]`` with ``a_trans``); ``b``: ``[K, N]`` (or ``[N, K]`` with ``b_trans``);
+    a leading batch dimension on either operand makes the product batched (a 2-D operand is shared).
+    Epilogue order: ``+bias`` -> store pre-activation to ``aux_out`` -> ``act`` -> ``* act'(aux_in)`` (``dact``)
+    -> ``+residual`` -> ``+out`` (``accumulate``).  ``backend``: ``auto`` | ``tcgen05`` | ``simt``.
+    """
+    _cuda(a, b, out, bias, aux_out, aux_in, residual)
+    batch = 1
+    if a.dim() == 3:
+        batch = a.shape[0]
+    if b.dim() == 3:
+        batch = max(batch, b.shape[0])
+    a2, b2 = a.shape[-2:], b.shape[-2:]
+    M, K = (a2[1], a2[0]) if a_trans else (a2[0], a2[1])
+    Kb, N = (b2[1], b2[0]) if b_trans else (b2[0], b2[1])
+    if K != Kb:
+        raise NativeError(f"gemm: inner dimensions differ ({K} vs {Kb})")
+    odt = out_dtype or (out.dtype if out is not None else a.dtype)
+    if out is None:
+        shape = (batch, M, N) if (a.dim() == 3 or b.dim() == 3) else (M, N)
+        out = torch.empty(shape, dtype=odt, device=a.device)
+    ws = workspace()
+    g = CmeGemm()
+    g.M, g.N, g.K, g.batch = M, N, K, batch
+    g.A, g.lda, g.strideA, g.a_trans = a.data_ptr(), a2[1], (a2[0] * a2[1] if a.dim() == 3 else 0), int(a_trans)
+    g.B, g.ldb, g.strideB, g.b_trans = b.data_ptr(), b2[1], (b2[0] * b2[1] if b.dim() == 3 else 0), int(b_trans)
+    g.C, g.ldc, g.strideC, g.c_dtype = out.data_ptr(), N, M * N, _dt(out)
+    g.ab_dtype = _dt(a)
+    g.bias = 0 if bias is None else bias.data_ptr()
+    g.residual, g.ldres = (0 if residual is None else residual.data_ptr()), N
+    g.aux_out = 0 if aux_out is None else aux_out.data_ptr()
+    g.aux_in = 0 if aux_in is None else aux_in.data_ptr()
+    g.ldaux = N
+    g.act, g.dact, g.accumulate = ACT[act], ACT[dact], int(accumulate)
+    g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel() * 4
+    g.force_bn, g.force_splits = force_bn, force_splits
+    _check(lib().cme_gemm(ctypes.byref(g), {"auto": 0, "tcgen05": 1, "simt": 2}[backend], _stream()))
+    return out
+
+
+def gemm_check_status() -> int:
+    """Read and clear the device status word of the tcgen05 GEMM (non-zero: a bounded wait ran out)."""
+    v = ctypes.c_int(0)
+    _check(lib().cme_gemm_check_status(ctypes.byref(v)))
+    return v.value
+
+
+# --------------------------------------------------------------------------------------------------
+# LayerNorm
+# --------------------------------------------------------------------------------------------------
+def layernorm_fwd(x, gamma, beta, eps: float = 1e-5, residual=None, save_sum: bool = False):
+    """``y = LN(x [+ residual])``.  Returns ``(y, mean, rstd, summed)`` where ``summed`` is
+    ``x + residual`` when ``save_sum`` (the fused residual + LayerNorm forward) else ``None``."""
+    _cuda(x, gamma, beta, residual)
+    rows, D = x.numel() // x.shape[-1], x.shape[-1]
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty_like(mean)
+    r = torch.empty_like(x) if (save_sum and residual is not None) else None
+    _check(lib().cme_layernorm_fwd(_dt(x), _p(x), _p(residual), _p(r), _p(gamma), _p(beta), _p(y), _p(mean), _p(rstd),
+                                   rows, D, ctypes.c_float(eps), _stream()))
+    return y, mean, rstd, r
+
+
+def layernorm_bwd(dy, x, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None, accumulate: bool = False):
+    """Returns ``(dx, dgamma, dbeta)``; ``dx`` includes ``+ dres`` when given (fused residual-gradient add)."""
+    _cuda(dy, x, gamma, mean, rstd, dres, dgamma, dbeta)
+    rows, D = x.numel() // x.shape[-1], x.shape[-1]
+    dx = torch.empty_like(x)
+    if dgamma is None:
+        dgamma, dbeta, accumulate = torch.empty_like(gamma), torch.empty_like(gamma), False
+    nb = lib().cme_layernorm_bwd_blocks(rows)
+    scratch = torch.empty(nb * 2 * D, dtype=torch.float32, device=x.device)
+    _check(lib().cme_layernorm_bwd(_dt(x), _p(dy), _p(x), _p(gamma), _p(mean), _p(rstd), _p(dres), _p(dx), _p(dgamma),
+                                   _p(dbeta), _p(scratch), rows, D, int(accumulate), _stream()))
+    return dx, dgamma, dbeta
+
+
+# --------------------------------------------------------------------------------------------------
+# Bias / activation / residual, column sums
+# --------------------------------------------------------------------------------------------------
+def bias_act_residual(x, bias=None, act=None, residual=None, save_pre: bool = False):
+    """``out = act(x + bias) + residual``; returns ``(out, pre)`` with ``pre = x + bias`` if ``save_pre``."""
+    _cuda(x, bias, residual)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    out = torch.empty_like(x)
+    pre = torch.empty_like(x) if save_pre else None
+    _check(lib().cme_bias_act_residual(_dt(x), _p(x), _p(bias), _p(residual), _p(pre), _p(out),
+                                       ctypes.c_longlong(rows), cols, ACT[act], _stream()))
+    return out, pre
+
+
+def dact_colsum(dout, pre=None, act=None, want_g: bool = True, dbias=None, accumulate: bool = False):
+    """``g = dout * act'(pre)`` and ``dbias (+)= g.sum(0)`` — the fused activation-backward + bias-backward."""
+    _cuda(dout, pre, dbias)
+    cols = dout.shape[-1]
+    rows = dout.numel() // cols
+    g = torch.empty_like(dout) if (want_g and pre is not None) else None
+    if dbias is None:
+        dbias, accumulate = torch.empty(cols, dtype=dout.dtype, device=dout.device), False
+    scratch = torch.empty(lib().cme_colsum_splits(rows, cols) * cols, dtype=torch.float32, device=dout.device)
+    _check(lib().cme_dact_colsum(_dt(dout), _p(dout), _p(pre), _p(g), _p(dbias), _p(scratch), rows, cols, ACT[act],
+                                 int(accumulate), _stream()))
+    return g, dbias
+
+
+def scale_(x, s: float):
+    _cuda(x)
+    _check(lib().cme_scale(_dt(x), _p(x), ctypes.c_longlong(x.numel()), ctypes.c_float(s), _stream()))
+    return x
+
+
+def cast(x, dtype):
+    _cuda(x)
+    y = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(lib().cme_cast(_dt(x), _p(x), _dt(y), _p(y), ctypes.c_longlong(x.numel()), _stream()))
+    return y
+
+
+def add(a, b):
+    _cuda(a, b)
+    out = torch.empty_like(a)
+    _check(lib().cme_add(_dt(a), _p(a), _p(b), _p(out), ctypes.c_longlong(a.numel()), _stream()))
+    return out
+
+
+def relu_bwd(x, dy):
+    _cuda(x, dy)
+    dx = torch.empty_like(dy)
+    _check(lib().cme_relu_bwd(_dt(x), _p(x), _p(dy), _p(dx), ctypes.c_longlong(x.numel()), _stream()))
+    return dx
+
+
+def init_uniform_(out, scale: float, seed: int):
+    _cuda(out)
+    _check(lib().cme_init_uniform(_dt(out), _p(out), ctypes.c_longlong(out.numel()), ctypes.c_float(scale),
+                                  ctypes.c_uint(seed & 0xFFFFFFFF), _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# Embedding
+# --------------------------------------------------------------------------------------------------
+def embedding_fwd(tokens, tok, pos):
+    _cuda(tokens, tok, pos)
+    BT, (V, D), T = tokens.numel(), tok.shape, pos.shape[0]
+    out = torch.empty(BT, D, dtype=tok.dtype, device=tok.device)
+    _check(lib().cme_embedding_fwd(_dt(tok), _p(tokens), _p(tok), _p(pos), _p(out), BT, T, D, V, _stream()))
+    return out
+
+
+def embedding_bwd(tokens, dout, V: int, T: int, dtok=None, dpos=None, accumulate: bool = False):
+    _cuda(tokens, dout, dtok, dpos)
+    BT, D = dout.shape
+    if dtok is None:
+        dtok, dpos, accumulate = (torch.empty(V, D, dtype=dout.dtype, device=dout.device),
+                                  torch.empty(T, D, dtype=dout.dtype, device=dout.device), False)
+    _check(lib().cme_embedding_bwd(_dt(dout), _p(tokens), _p(dout), _p(dtok), _p(dpos), BT, T, D, V, int(accumulate),
+                                   _stream()))
+    return dtok, dpos
+
+
+# --------------------------------------------------------------------------------------------------
+# Loss and optimizer
+# --------------------------------------------------------------------------------------------------
+def cross_entropy(logits, targets, grad_scale: Optional[float] = None, prob_eps: float = 0.0, inplace: bool = False):
+    """Returns ``(mean loss [1] fp32, dlogits, per-row losses)``; ``dlogits = (softmax - onehot) * grad_scale``
+    (default ``1/rows``).  ``prob_eps = 1e-9`` reproduces the reference's ``-log(p + 1e-9)`` form."""
+    _cuda(logits, targets)
+    rows, V = logits.shape
+    dl = logits if inplace else torch.empty_like(logits)
+    losses = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
+    gs = 1.0 / rows if grad_scale is None else grad_scale
+    _check(lib().cme_cross_entropy(_dt(logits), _p(logits), _p(targets), _p(dl), _p(losses), _p(loss), rows, V,
+                                   ctypes.c_longlong(V), ctypes.c_float(gs), ctypes.c_float(prob_eps),
+                                   ctypes.c_float(1.0), 0, _stream()))
+    return loss, dl, losses
+
+
+def grad_normsq(g):
+    _cuda(g)
+    partial = torch.empty(1024, dtype=torch.float32, device=g.device)
+    out = torch.empty(1, dtype=torch.float32, device=g.device)
+    _check(lib().cme_grad_normsq(_dt(g), _p(g), ctypes.c_longlong(g.numel()), _p(partial), _p(out), _stream()))
+    return out
+
+
+def adam_step(master, grads, m, v, step_dev, lr_dev, *, compute=None, normsq=None, beta1=0.9, beta2=0.999, eps=1e-8,
+              weight_decay=0.0, grad_scale=1.0, clip_norm=0.0, nodecay=None):
+    """One Adam / AdamW update over a flat range.  ``step_dev`` (int32 [1], already incremented) and
+    ``lr_dev`` (fp32 [1]) live on the device; ``nodecay`` is an int64 ``[k, 2]`` tensor of sorted ranges."""
+    _cuda(master, grads, m, v, step_dev, lr_dev, compute, normsq, nodecay)
+    nn = 0 if nodecay is None else nodecay.shape[0]
+    _check(lib().cme_adam(_dt(grads), _p(master), _p(compute), _p(grads), _p(m), _p(v),
+                          ctypes.c_longlong(master.numel()), _p(step_dev), _p(lr_dev), _p(normsq),
+                          ctypes.c_float(beta1), ctypes.c_float(beta2), ctypes.c_float(eps),
+                          ctypes.c_float(weight_decay), ctypes.c_float(grad_scale), ctypes.c_float(clip_norm),
+                          _p(nodecay), nn, _stream()))

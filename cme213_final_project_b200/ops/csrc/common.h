@@ -1,0 +1,125 @@
+// Common runtime for the native library: error reporting, shape helpers, device math, reductions.
+//
+// Role of the reference's common.h (FINAL_CLEAN_CODE_/include/common.h:20-82): there CUDA_CHECK exits the
+// process; here every exported function returns a status code (0 = ok) and records a message that the
+// Python side turns into an exception, so a failed launch never takes the interpreter down.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+#define CME_API extern "C" __attribute__((visibility("default")))
+
+enum CmeStatus : int {
+    CME_OK = 0,
+    CME_ERR_CUDA = 1,        // a CUDA runtime / driver call failed
+    CME_ERR_SHAPE = 2,       // unsupported or inconsistent shape / alignment
+    CME_ERR_TIMEOUT = 3,     // a bounded device-side wait ran out (reported through a status word)
+    CME_ERR_LIMIT = 4,       // a documented size limit was exceeded
+    CME_ERR_UNSUPPORTED = 5,
+};
+
+// Data type tags passed through the C ABI.
+enum CmeDtype : int { CME_F32 = 0, CME_BF16 = 1 };
+
+void cme_set_error(const char* fmt, ...);
+CME_API const char* cme_last_error();
+
+#define CME_CUDA(call)                                                                         \
+    do {                                                                                       \
+        cudaError_t err__ = (call);                                                            \
+        if (err__ != cudaSuccess) {                                                            \
+            cme_set_error("%s:%d: %s -> %s", __FILE__, __LINE__, #call, cudaGetErrorString(err__)); \
+            return CME_ERR_CUDA;                                                               \
+        }                                                                                      \
+    } while (0)
+
+#define CME_LAUNCH_CHECK() CME_CUDA(cudaGetLastError())
+
+#define CME_REQUIRE(cond, code, ...)                                                           \
+    do {                                                                                       \
+        if (!(cond)) {                                                                         \
+            cme_set_error(__VA_ARGS__);                                                        \
+            return (code);                                                                     \
+        }                                                                                      \
+    } while (0)
+
+static inline int cme_cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+#ifdef __CUDACC__
+
+__host__ __device__ __forceinline__ int cme_cdiv_dev(int a, int b) { return (a + b - 1) / b; }
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; every thread gets the result.  `scratch` holds at least 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? scratch[lane] : 0.f;
+    return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? scratch[lane] : -INFINITY;
+    return warp_max(r);
+}
+
+// tanh-form GELU and its derivative.
+__device__ __forceinline__ float gelu_f(float x) {
+    const float k = 0.7978845608028654f;
+    float u = k * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.f + tanhf(u));
+}
+__device__ __forceinline__ float dgelu_f(float x) {
+    const float k = 0.7978845608028654f;
+    float x2 = x * x;
+    float u = k * (x + 0.044715f * x * x2);
+    float t = tanhf(u);
+    return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x2);
+}
+
+// 8 x bf16 <-> 8 x f32 through one 128-bit word.
+struct alignas(16) Bf16x8 { __nv_bfloat162 v[4]; };
+__device__ __forceinline__ void unpack8(const Bf16x8& p, float* f) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(p.v[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ Bf16x8 pack8(const float* f) {
+    Bf16x8 p;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return p;
+}
+
+#endif  // __CUDACC__

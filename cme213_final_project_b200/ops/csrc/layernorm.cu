@@ -1,0 +1,318 @@
+// LayerNorm forward / backward with fused residual adds, bf16 or fp32 I/O, fp32 statistics.
+//
+// Covers the reference's five LayerNorm kernels (FINAL_CLEAN_CODE_/src/kernels/layernorm.cu:24-305):
+// plain forward, forward saving mean / inverse std, fused residual + LayerNorm forward, backward dx with
+// optional fused "gx += dx" residual-gradient add, and the column-wise d(gamma) / d(beta) reduction.
+// The reference uses one block per row with a two-pass block reduction and a second kernel with one block
+// per column for the weight gradients.  Here one warp owns a row (128-bit loads, shuffles only), and the
+// backward kernel produces dx and per-block partial d(gamma)/d(beta) in a single pass over x and dy; a
+// small second kernel sums the partials in a fixed order (no atomics, bit-reproducible).
+#include "common.h"
+
+namespace {
+
+constexpr int LN_WARPS = 8;            // rows per block iteration
+constexpr int LN_MAX_VEC = 4;          // 16-byte vectors per lane kept in registers (D <= 1024 bf16, 512 fp32)
+
+template <typename T> struct VecOf;
+template <> struct VecOf<float> { static constexpr int N = 4; };
+template <> struct VecOf<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T> __device__ __forceinline__ void load_vec(const T* p, float* f);
+template <> __device__ __forceinline__ void load_vec<float>(const float* p, float* f) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+    unpack8(*reinterpret_cast<const Bf16x8*>(p), f);
+}
+template <typename T> __device__ __forceinline__ void store_vec(T* p, const float* f);
+template <> __device__ __forceinline__ void store_vec<float>(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store_vec<__nv_bfloat16>(__nv_bfloat16* p, const float* f) {
+    *reinterpret_cast<Bf16x8*>(p) = pack8(f);
+}
+
+// y = LN(a [+ b]) * gamma + beta; optionally writes r = a + b, mean and rstd.
+// VEC path: D is a multiple of the vector width and D / width <= 32 * LN_MAX_VEC; row kept in registers.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ r_out, const T* __restrict__ gamma,
+              const T* __restrict__ beta, T* __restrict__ y, float* __restrict__ mean_out,
+              float* __restrict__ rstd_out, int rows, int D, float eps) {
+    constexpr int W = VecOf<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const long long off = (long long)row * D;
+    if constexpr (VEC) {
+        const int nvec = D / W;
+        float x[LN_MAX_VEC][W];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < LN_MAX_VEC; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                load_vec<T>(a + off + v * W, x[i]);
+                if (b) {
+                    float t[W];
+                    load_vec<T>(b + off + v * W, t);
+#pragma unroll
+                    for (int j = 0; j < W; ++j) x[i][j] += t[j];
+                    if (r_out) store_vec<T>(r_out + off + v * W, x[i]);
+                }
+#pragma unroll
+                for (int j = 0; j < W; ++j) s += x[i][j];
+            }
+        }
+        const float mean = warp_sum(s) / D;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < LN_MAX_VEC; ++i) {
+            if (lane + 32 * i < nvec) {
+#pragma unroll
+                for (int j = 0; j < W; ++j) { const float d = x[i][j] - mean; q += d * d; }
+            }
+        }
+        const float rstd = rsqrtf(warp_sum(q) / D + eps);
+#pragma unroll
+        for (int i = 0; i < LN_MAX_VEC; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                float g[W], bt[W], o[W];
+                load_vec<T>(gamma + v * W, g);
+                load_vec<T>(beta + v * W, bt);
+#pragma unroll
+                for (int j = 0; j < W; ++j) o[j] = (x[i][j] - mean) * rstd * g[j] + bt[j];
+                store_vec<T>(y + off + v * W, o);
+            }
+        }
+        if (lane == 0) {
+            if (mean_out) mean_out[row] = mean;
+            if (rstd_out) rstd_out[row] = rstd;
+        }
+    } else {
+        float s = 0.f;
+        for (int c = lane; c < D; c += 32) {
+            float v = to_f32<T>(a[off + c]);
+            if (b) {
+                v += to_f32<T>(b[off + c]);
+                if (r_out) r_out[off + c] = from_f32<T>(v);
+            }
+            s += v;
+        }
+        const float mean = warp_sum(s) / D;
+        const T* src = (b && r_out) ? r_out : a;
+        float q = 0.f;
+        for (int c = lane; c < D; c += 32) {
+            float v = (b && !r_out) ? to_f32<T>(a[off + c]) + to_f32<T>(b[off + c]) : to_f32<T>(src[off + c]);
+            const float d = v - mean;
+            q += d * d;
+        }
+        const float rstd = rsqrtf(warp_sum(q) / D + eps);
+        for (int c = lane; c < D; c += 32) {
+            float v = (b && !r_out) ? to_f32<T>(a[off + c]) + to_f32<T>(b[off + c]) : to_f32<T>(src[off + c]);
+            y[off + c] = from_f32<T>((v - mean) * rstd * to_f32<T>(gamma[c]) + to_f32<T>(beta[c]));
+        }
+        if (lane == 0) {
+            if (mean_out) mean_out[row] = mean;
+            if (rstd_out) rstd_out[row] = rstd;
+        }
+    }
+}
+
+// dx = rstd * (dy*g - mean(dy*g) - xhat * mean(dy*g*xhat)) [+ dres];  per-block partial dgamma / dbeta.
+// Grid-stride over rows; each lane owns fixed columns so its partial sums stay in registers.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+              const float* __restrict__ mean, const float* __restrict__ rstd, const T* __restrict__ dres,
+              T* __restrict__ dx, float* __restrict__ partial /*[gridDim.x][2][D]*/, int rows, int D) {
+    constexpr int W = VecOf<T>::N;
+    extern __shared__ float sm[];     // [LN_WARPS][2][D]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if constexpr (VEC) {
+        const int nvec = D / W;
+        float g[LN_MAX_VEC][W], dg[LN_MAX_VEC][W], db[LN_MAX_VEC][W];
+#pragma unroll
+        for (int i = 0; i < LN_MAX_VEC; ++i) {
+            const int v = lane + 32 * i;
+#pragma unroll
+            for (int j = 0; j < W; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; g[i][j] = 0.f; }
+            if (v < nvec) load_vec<T>(gamma + v * W, g[i]);
+        }
+        for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
+            const long long off = (long long)row * D;
+            const float mu = mean[row], rs = rstd[row];
+            float xh[LN_MAX_VEC][W], dyg[LN_MAX_VEC][W];
+            float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < LN_MAX_VEC; ++i) {
+                const int v = lane + 32 * i;
+                if (v < nvec) {
+                    float xv[W], dv[W];
+                    load_vec<T>(x + off + v * W, xv);
+                    load_vec<T>(dy + off + v * W, dv);
+#pragma unroll
+                    for (int j = 0; j < W; ++j) {
+                        xh[i][j] = (xv[j] - mu) * rs;
+                        dyg[i][j] = dv[j] * g[i][j];
+                        s1 += dyg[i][j];
+                        s2 += dyg[i][j] * xh[i][j];
+                        dg[i][j] += dv[j] * xh[i][j];
+                        db[i][j] += dv[j];
+                    }
+                }
+            }
+            s1 = warp_sum(s1) / D;
+            s2 = warp_sum(s2) / D;
+#pragma unroll
+            for (int i = 0; i < LN_MAX_VEC; ++i) {
+                const int v = lane + 32 * i;
+                if (v < nvec) {
+                    float o[W];
+#pragma unroll
+                    for (int j = 0; j < W; ++j) o[j] = rs * (dyg[i][j] - s1 - xh[i][j] * s2);
+                    if (dres) {
+                        float t[W];
+                        load_vec<T>(dres + off + v * W, t);
+#pragma unroll
+                        for (int j = 0; j < W; ++j) o[j] += t[j];
+                    }
+                    store_vec<T>(dx + off + v * W, o);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < LN_MAX_VEC; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+#pragma unroll
+                for (int j = 0; j < W; ++j) {
+                    sm[(warp * 2 + 0) * D + v * W + j] = dg[i][j];
+                    sm[(warp * 2 + 1) * D + v * W + j] = db[i][j];
+                }
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < LN_WARPS * 2 * D; c += blockDim.x) sm[c] = 0.f;
+        __syncthreads();
+        for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
+            const long long off = (long long)row * D;
+            const float mu = mean[row], rs = rstd[row];
+            float s1 = 0.f, s2 = 0.f;
+            for (int c = lane; c < D; c += 32) {
+                const float xh = (to_f32<T>(x[off + c]) - mu) * rs;
+                const float dv = to_f32<T>(dy[off + c]);
+                const float d = dv * to_f32<T>(gamma[c]);
+                s1 += d;
+                s2 += d * xh;
+                sm[(warp * 2 + 0) * D + c] += dv * xh;
+                sm[(warp * 2 + 1) * D + c] += dv;
+            }
+            s1 = warp_sum(s1) / D;
+            s2 = warp_sum(s2) / D;
+            for (int c = lane; c < D; c += 32) {
+                const float xh = (to_f32<T>(x[off + c]) - mu) * rs;
+                const float d = to_f32<T>(dy[off + c]) * to_f32<T>(gamma[c]);
+                float o = rs * (d - s1 - xh * s2);
+                if (dres) o += to_f32<T>(dres[off + c]);
+                dx[off + c] = from_f32<T>(o);
+            }
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < LN_WARPS; ++w) s += sm[w * 2 * D + c];
+        partial[(long long)blockIdx.x * 2 * D + c] = s;
+    }
+}
+
+// dgamma[c] (+)= sum_b partial[b][0][c];  dbeta[c] (+)= sum_b partial[b][1][c]
+template <typename T>
+__global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int D, T* dgamma, T* dbeta,
+                                       int accumulate) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= 2 * D) return;
+    float s = 0.f;
+    for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * 2 * D + c];
+    T* dst = (c < D) ? dgamma + c : dbeta + (c - D);
+    *dst = from_f32<T>(accumulate ? to_f32<T>(*dst) + s : s);
+}
+
+template <typename T>
+int ln_fwd_t(const void* a, const void* b, void* r, const void* g, const void* be, void* y, float* mean, float* rstd,
+             int rows, int D, float eps, cudaStream_t st) {
+    constexpr int W = VecOf<T>::N;
+    const bool vec = (D % W == 0) && (D / W <= 32 * LN_MAX_VEC);
+    const int grid = cme_cdiv(rows, LN_WARPS);
+    if (vec)
+        ln_fwd_kernel<T, true><<<grid, LN_WARPS * 32, 0, st>>>((const T*)a, (const T*)b, (T*)r, (const T*)g,
+                                                               (const T*)be, (T*)y, mean, rstd, rows, D, eps);
+    else
+        ln_fwd_kernel<T, false><<<grid, LN_WARPS * 32, 0, st>>>((const T*)a, (const T*)b, (T*)r, (const T*)g,
+                                                                (const T*)be, (T*)y, mean, rstd, rows, D, eps);
+    CME_LAUNCH_CHECK();
+    return CME_OK;
+}
+
+template <typename T>
+int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, const float* rstd, const void* dres,
+             void* dx, void* dgamma, void* dbeta, float* scratch, int nblocks, int rows, int D, int accumulate,
+             cudaStream_t st) {
+    constexpr int W = VecOf<T>::N;
+    const bool vec = (D % W == 0) && (D / W <= 32 * LN_MAX_VEC);
+    const size_t smem = (size_t)LN_WARPS * 2 * D * sizeof(float);
+    if (vec) {
+        auto k = ln_bwd_kernel<T, true>;
+        if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<nblocks, LN_WARPS * 32, smem, st>>>((const T*)dy, (const T*)x, (const T*)g, mean, rstd, (const T*)dres,
+                                                (T*)dx, scratch, rows, D);
+    } else {
+        auto k = ln_bwd_kernel<T, false>;
+        if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<nblocks, LN_WARPS * 32, smem, st>>>((const T*)dy, (const T*)x, (const T*)g, mean, rstd, (const T*)dres,
+                                                (T*)dx, scratch, rows, D);
+    }
+    CME_LAUNCH_CHECK();
+    ln_bwd_finalize_kernel<T><<<cme_cdiv(2 * D, 256), 256, 0, st>>>(scratch, nblocks, D, (T*)dgamma, (T*)dbeta,
+                                                                  accumulate);
+    CME_LAUNCH_CHECK();
+    return CME_OK;
+}
+
+}  // namespace
+
+// y = LN(a + b); b, r_out, mean, rstd may be null.
+CME_API int cme_layernorm_fwd(int dtype, const void* a, const void* b, void* r_out, const void* gamma,
+                              const void* beta, void* y, float* mean, float* rstd, int rows, int D, float eps,
+                              void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    CME_REQUIRE(rows > 0 && D > 0, CME_ERR_SHAPE, "layernorm: empty input");
+    return dtype == CME_BF16 ? ln_fwd_t<__nv_bfloat16>(a, b, r_out, gamma, beta, y, mean, rstd, rows, D, eps, st)
+                             : ln_fwd_t<float>(a, b, r_out, gamma, beta, y, mean, rstd, rows, D, eps, st);
+}
+
+// Number of partial blocks the backward uses for `rows`; scratch must hold blocks * 2 * D floats.
+CME_API int cme_layernorm_bwd_blocks(int rows) {
+    int b = cme_cdiv(rows, LN_WARPS);
+    return b < 296 ? b : 296;
+}
+
+// dx = LN'(dy) [+ dres]; dgamma/dbeta (+)= column sums.  `scratch`: cme_layernorm_bwd_blocks(rows)*2*D floats.
+CME_API int cme_layernorm_bwd(int dtype, const void* dy, const void* x, const void* gamma, const float* mean,
+                              const float* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
+                              float* scratch, int rows, int D, int accumulate, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    CME_REQUIRE(rows > 0 && D > 0, CME_ERR_SHAPE, "layernorm: empty input");
+    CME_REQUIRE((size_t)LN_WARPS * 2 * D * 4 <= 200 * 1024, CME_ERR_LIMIT, "layernorm backward: D too large (%d)", D);
+    const int nb = cme_layernorm_bwd_blocks(rows);
+    return dtype == CME_BF16
+               ? ln_bwd_t<__nv_bfloat16>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, nb, rows, D,
+                                         accumulate, st)
+               : ln_bwd_t<float>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, nb, rows, D, accumulate,
+                                 st);
+}

@@ -1,0 +1,76 @@
+"""One training step under every synchronisation policy, for any model that exposes the flat-arena
+interface (``zero_grad / forward / backward / update / read_loss`` plus ``params``, ``grads``, ``layout``).
+
+Mirrors the step structure of the reference driver (``FINAL_CLEAN_CODE_/src/main.cu:357-394``):
+
+    zero_grad -> forward -> backward (plain, or bucketed with asynchronous sync) -> [blocking sync] -> update
+
+and adds gradient accumulation (several micro-batches per optimizer step; only the last one synchronises).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .arena import Bucket
+from .config import OptimConfig, RunConfig, effective_overlap, min_bucket_elems
+from .parallel.dist import DistributedContext
+from .utils.nvtx import nvtx_range
+
+
+class Trainer:
+    def __init__(self, model, dist_ctx: DistributedContext, run: RunConfig, optim: OptimConfig) -> None:
+        self.model = model
+        self.dist = dist_ctx
+        self.run = run
+        self.optim = optim
+        elem_bytes = model.grads.element_size()
+        self.grad_mb = model.layout.total * elem_bytes / (1024.0 * 1024.0)
+        self.use_overlap = effective_overlap(run, self.grad_mb, dist_ctx.world_size)
+        self.buckets: List[Bucket] = model.layout.coalesced_buckets(min_bucket_elems(run.bucket_kb, elem_bytes))
+        self.comm_ms_sum = 0.0
+        self.async_start_ms_sum = 0.0
+        self.steps = 0
+
+    # ---------------------------------------------------------------------------------------------
+    def _bucket_ready(self, b: Bucket) -> None:
+        self.dist.start_async_gradient_sync(self.model.grads[b.start:b.end])
+
+    def step(self, tokens: Sequence[torch.Tensor], targets: Sequence[torch.Tensor]) -> None:
+        """One optimizer step over ``len(tokens)`` micro-batches (``grad_accum`` of them)."""
+        if isinstance(tokens, torch.Tensor):
+            tokens, targets = [tokens], [targets]
+        m, d = self.model, self.dist
+        if hasattr(m, "train_step") and getattr(m, "handles_sync", False):
+            m.train_step(tokens, targets)            # native engine: sync and update are fused on the device
+            self.steps += 1
+            return
+        accum = len(tokens)
+        d.begin_step()
+        m.zero_grad()
+        for i, (x, y) in enumerate(zip(tokens, targets)):
+            last = i == accum - 1
+            with nvtx_range("forward", self.run.profile):
+                m.forward(x, y)
+            if last and self.use_overlap:
+                with nvtx_range("backward_bucketed", self.run.profile):
+                    m.backward(bucket_callback=self._bucket_ready, buckets=self.buckets, scale=1.0 / accum)
+                    d.finish_async_gradient_syncs()
+            else:
+                with nvtx_range("backward", self.run.profile):
+                    m.backward(scale=1.0 / accum)
+                if last and d.world_size > 1:
+                    with nvtx_range("gradient_sync", self.run.profile):
+                        d.sync_gradients(m.grads)
+        self.comm_ms_sum += d.last_sync_ms
+        self.async_start_ms_sum += d.last_async_start_ms
+        grad_scale = 1.0 / d.world_size if d.defer_gradient_average else 1.0
+        with nvtx_range("adam_update", self.run.profile):
+            m.update(grad_scale=grad_scale)
+        self.steps += 1
+
+    def reset_timers(self) -> None:
+        self.comm_ms_sum = 0.0
+        self.async_start_ms_sum = 0.0
+        self.steps = 0
