@@ -8,7 +8,7 @@ orders the 15 tensors so that gradients become final in address order during bac
     Wq[D,D], Wk[D,D], Wv[D,D], ln1_g[D], ln1_b[D], tok_embed[V,D], pos_embed[T,D]
 
 so every gradient bucket is a contiguous range.  This module generalises that order to ``N`` blocks
-(last block first), an optional final LayerNorm (right after the output head) and tied embeddings
+(last block first; GPT mode stores one fused ``Wqkv[D,3D]`` per block), an optional final LayerNorm (right after the output head) and tied embeddings
 (no ``Wout``; the shared table is the last range because the embedding scatter is the last gradient
 to be produced).  With one block, untied, no final LN, the layout is exactly the reference's.
 
@@ -112,9 +112,13 @@ class ArenaLayout:
             close(cur)
             add(p + "Wo", (D, D), "weight", s + 13, cur)
             close(cur)
-            add(p + "Wq", (D, D), "weight", s + 10, cur)
-            add(p + "Wk", (D, D), "weight", s + 11, cur)
-            add(p + "Wv", (D, D), "weight", s + 12, cur)
+            if cfg.mode == "gpt":
+                # one fused [D, 3D] projection: columns [0,D) = Q, [D,2D) = K, [2D,3D) = V
+                add(p + "Wqkv", (D, 3 * D), "weight", s + 10, cur)
+            else:
+                add(p + "Wq", (D, D), "weight", s + 10, cur)
+                add(p + "Wk", (D, D), "weight", s + 11, cur)
+                add(p + "Wv", (D, D), "weight", s + 12, cur)
             close(cur)
             add(p + "ln1_gamma", (D,), "ln_gamma", -1, cur)
             add(p + "ln1_beta", (D,), "ln_beta", -1, cur)

@@ -1,0 +1,217 @@
+"""The native sm_100a engine behind the flat-arena model interface.
+
+Python owns memory (arenas and the activation workspace are ``torch`` tensors), policy (bucket
+coalescing, which synchronisation path runs, CUDA-graph capture) and the optimizer launch; the C++
+executor (``ops/csrc/engine.cu``) owns the op sequence of forward and backward.  Interface and role
+match the reference's ``TransformerModel`` (``FINAL_CLEAN_CODE_/include/model.h:93-145``): public flat
+buffers, ``zero_grad / forward / backward / update / read_loss``.
+
+Arenas: ``params`` (compute dtype: bf16, or fp32 in strict mode), ``master`` (fp32; aliases ``params`` in
+strict mode), ``grads`` (compute dtype), ``adam_m`` / ``adam_v`` (fp32).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..arena import ArenaLayout, Bucket, init_flat
+from ..config import ModelConfig, OptimConfig, RunConfig
+
+
+class _EngineDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("V", "T", "D", "H", "FF", "L", "B", "act", "causal", "head_flat", "tied",
+                                             "final_ln", "fused_qkv")] + \
+               [("ln_eps", ctypes.c_float), ("prob_eps", ctypes.c_float)] + \
+               [(n, ctypes.c_int) for n in ("dtype", "gemm_backend", "attn_backend")]
+
+
+class _LayerSlots(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_longlong) for n in ("W2", "b2", "W1", "b1", "ln2g", "ln2b", "Wo", "Wq", "Wk", "Wv",
+                                                  "Wqkv", "ln1g", "ln1b")]
+
+
+class _GlobalSlots(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_longlong) for n in ("Wout", "lnfg", "lnfb", "tok", "pos")]
+
+
+_BUCKET_FN = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int)
+
+
+class NativeEngine:
+    handles_sync = False
+
+    def __init__(self, cfg: ModelConfig, optim: OptimConfig, run: Optional[RunConfig] = None, dist_ctx=None,
+                 seed: int = 42, device=None, shard_multiple: int = 1) -> None:
+        run = run or RunConfig()
+        self.cfg, self.optim, self.run = cfg, optim, run
+        self.device = torch.device(device) if device is not None else (
+            dist_ctx.device if dist_ctx is not None else torch.device("cuda", torch.cuda.current_device()))
+        if self.device.type != "cuda":
+            raise ops.NativeError("the native engine needs a CUDA device")
+        self.lib = ops.lib()
+        self.strict = run.compute_dtype == "fp32"
+        self.dtype = torch.float32 if self.strict else torch.bfloat16
+        self.layout = ArenaLayout(cfg, align=64, shard_multiple=shard_multiple)
+        n = self.layout.total
+        with torch.cuda.device(self.device):
+            flat = init_flat(self.layout, seed).to(self.device)
+            self.master = flat                                    # fp32
+            self.params = flat if self.strict else flat.to(torch.bfloat16)
+            self.grads = torch.zeros(n, dtype=self.dtype, device=self.device)
+            self.adam_m = torch.zeros(n, dtype=torch.float32, device=self.device)
+            self.adam_v = torch.zeros(n, dtype=torch.float32, device=self.device)
+            self.step_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.lr_dev = torch.full((1,), optim.lr, dtype=torch.float32, device=self.device)
+            self.loss_dev = torch.zeros(1, dtype=torch.float32, device=self.device)
+            self.normsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+            self._norm_partial = torch.empty(1024, dtype=torch.float32, device=self.device)
+        nd = [(s.offset, s.offset + s.numel) for s in self.layout.specs if s.kind not in ("weight", "embed")]
+        self.nodecay = torch.tensor(nd, dtype=torch.int64, device=self.device).reshape(-1, 2)
+        self.step_count = 0
+
+        gemm_backend = {"auto": 0, "tcgen05": 0, "simt": 2, "torch": 0}[run.gemm_backend]
+        d = _EngineDesc(V=cfg.vocab_size, T=cfg.seq_len, D=cfg.hidden, H=cfg.heads, FF=cfg.ff, L=cfg.layers,
+                        B=cfg.batch_size, act=ops.ACT[cfg.activation], causal=int(cfg.causal),
+                        head_flat=int(cfg.head_layout == "flat"), tied=int(cfg.tied_embeddings),
+                        final_ln=int(cfg.final_layernorm), fused_qkv=int(cfg.mode == "gpt"), ln_eps=cfg.ln_eps,
+                        prob_eps=1e-9 if cfg.mode == "parity" else 0.0, dtype=ops.F32 if self.strict else ops.BF16,
+                        gemm_backend=2 if self.strict else gemm_backend, attn_backend=2 if self.strict else 0)
+        off = lambda name: self.layout.by_name[name].offset if name in self.layout.by_name else -1
+        layers = (_LayerSlots * cfg.layers)()
+        for l in range(cfg.layers):
+            p = f"h{l}." if (cfg.layers > 1 or cfg.mode == "gpt") else ""
+            layers[l] = _LayerSlots(off(p + "W2"), off(p + "b2"), off(p + "W1"), off(p + "b1"), off(p + "ln2_gamma"),
+                                    off(p + "ln2_beta"), off(p + "Wo"), off(p + "Wq"), off(p + "Wk"), off(p + "Wv"),
+                                    off(p + "Wqkv"), off(p + "ln1_gamma"), off(p + "ln1_beta"))
+        g = _GlobalSlots(off("Wout"), off("lnf_gamma"), off("lnf_beta"), off("tok_embed"), off("pos_embed"))
+        self._h = ctypes.c_void_p()
+        self.lib.cme_engine_workspace_bytes.restype = ctypes.c_longlong
+        self.lib.cme_engine_logits.restype = ctypes.c_void_p
+        ops._check(self.lib.cme_engine_create(ctypes.byref(d), layers, ctypes.byref(g), ctypes.byref(self._h)))
+        nbytes = int(self.lib.cme_engine_workspace_bytes(self._h))
+        self.workspace = torch.empty(nbytes + 256, dtype=torch.uint8, device=self.device)
+        base = (self.workspace.data_ptr() + 255) // 256 * 256
+        ops._check(self.lib.cme_engine_bind(self._h, ctypes.c_void_p(self.params.data_ptr()),
+                                            ctypes.c_void_p(self.grads.data_ptr()), ctypes.c_void_p(base),
+                                            ctypes.c_longlong(nbytes)))
+        self._tokens: Optional[torch.Tensor] = None
+        self._cb_keepalive = None
+
+    # ---------------------------------------------------------------------------------------------
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                self.lib.cme_engine_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    @property
+    def total_param_count(self) -> int:
+        return self.layout.total
+
+    def master_params(self) -> torch.Tensor:
+        return self.master
+
+    def state(self):
+        return self.master, self.adam_m, self.adam_v, self.step_count
+
+    def load_state(self, p, m, v, step: int) -> None:
+        self.master.copy_(p.to(self.device))
+        if not self.strict:
+            self.params.copy_(self.master)
+        self.adam_m.copy_(m.to(self.device))
+        self.adam_v.copy_(v.to(self.device))
+        self.step_count = step
+        self.step_dev.fill_(step)
+
+    def set_params(self, flat_fp32: torch.Tensor) -> None:
+        self.master.copy_(flat_fp32.to(self.device, torch.float32))
+        if not self.strict:
+            self.params.copy_(self.master)
+
+    def zero_grad(self) -> None:
+        """Kept for interface parity: backward overwrites gradients, so nothing needs clearing."""
+        self._micro = 0
+
+    def set_lr(self, lr: float) -> None:
+        self.lr_dev.fill_(lr)
+
+    # ---------------------------------------------------------------------------------------------
+    def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor], loss_weight: float = 1.0,
+                accumulate_loss: bool = False, grad_scale: Optional[float] = None) -> torch.Tensor:
+        """Enqueue the forward pass; the mean loss lands in ``self.loss_dev`` (no host sync)."""
+        self._tokens = tokens
+        gs = (1.0 / self.cfg.tokens_per_step) if grad_scale is None else grad_scale
+        with torch.cuda.device(self.device):
+            ops._check(self.lib.cme_engine_forward(
+                self._h, ops._p(tokens), ops._p(targets), ops._p(self.loss_dev), ctypes.c_float(loss_weight),
+                int(accumulate_loss), ctypes.c_float(gs), ops._stream()))
+        return self.loss_dev
+
+    def backward(self, bucket_callback: Optional[Callable[[Bucket], None]] = None,
+                 buckets: Optional[Sequence[Bucket]] = None, scale: float = 1.0, accumulate: bool = False) -> None:
+        """Enqueue the backward pass.  ``bucket_callback(bucket)`` runs on the host as soon as the launches that
+        complete a (coalesced) bucket have been enqueued.  ``scale`` must already have been applied through
+        ``forward(grad_scale=...)``; it is accepted for interface parity with the oracle model."""
+        cb = _BUCKET_FN(0)
+        if bucket_callback is not None:
+            ready = {}
+            for b in buckets:
+                last = max(nb.index for nb in self.layout.natural_buckets if b.start <= nb.start and nb.end <= b.end)
+                ready[last] = b
+
+            def _cb(_user, idx):
+                b = ready.get(idx)
+                if b is not None:
+                    bucket_callback(b)
+
+            cb = _BUCKET_FN(_cb)
+        self._cb_keepalive = cb
+        with torch.cuda.device(self.device):
+            ops._check(self.lib.cme_engine_backward(self._h, ops._p(self._tokens), int(accumulate), cb, None,
+                                                    ops._stream()))
+
+    def logits(self) -> torch.Tensor:
+        """A copy of the logits buffer (after ``forward`` with targets it holds d(logits))."""
+        n = self.cfg.tokens_per_step * self.cfg.vocab_size
+        ptr = self.lib.cme_engine_logits(self._h)
+        out = torch.empty(n, dtype=self.dtype, device=self.device)
+        ops._check(self.lib.cme_copy_d2d(ops._p(out), ctypes.c_void_p(ptr), ctypes.c_longlong(n * out.element_size()),
+                                         ops._stream()))
+        return out.view(self.cfg.tokens_per_step, self.cfg.vocab_size)
+
+    def update(self, grad_scale: float = 1.0, lr: Optional[float] = None) -> None:
+        """Unfused optimizer path: global norm (if clipping) then Adam / AdamW over the whole arena."""
+        o = self.optim
+        if lr is not None:
+            self.set_lr(lr)
+        self.step_count += 1
+        with torch.cuda.device(self.device):
+            ops._check(self.lib.cme_step_inc(ops._p(self.step_dev), ops._stream()))
+            normsq = None
+            if o.clip_norm > 0:
+                ops._check(self.lib.cme_grad_normsq(ops._dt(self.grads), ops._p(self.grads),
+                                                    ctypes.c_longlong(self.grads.numel()), ops._p(self._norm_partial),
+                                                    ops._p(self.normsq), ops._stream()))
+                normsq = self.normsq
+            ops.adam_step(self.master, self.grads, self.adam_m, self.adam_v, self.step_dev, self.lr_dev,
+                          compute=None if self.strict else self.params, normsq=normsq, beta1=o.beta1, beta2=o.beta2,
+                          eps=o.eps, weight_decay=o.weight_decay, grad_scale=grad_scale, clip_norm=o.clip_norm,
+                          nodecay=self.nodecay if o.weight_decay > 0 else None)
+
+    def train_step(self, tokens: Sequence[torch.Tensor], targets: Sequence[torch.Tensor],
+                   bucket_callback=None, buckets=None) -> None:
+        """zero_grad + forward/backward over the micro-batches (gradients accumulate, the loss is their mean)."""
+        accum = len(tokens)
+        gs = 1.0 / (self.cfg.tokens_per_step * accum)
+        for i, (x, y) in enumerate(zip(tokens, targets)):
+            self.forward(x, y, loss_weight=1.0 / accum, accumulate_loss=i > 0, grad_scale=gs)
+            last = i == accum - 1
+            self.backward(bucket_callback if last else None, buckets if last else None, accumulate=i > 0)
+
+    def read_loss(self) -> float:
+        return float(self.loss_dev.item())

@@ -60,7 +60,10 @@ def forward(P: Dict[str, torch.Tensor], cfg: ModelConfig, tokens: torch.Tensor, 
     for l in range(cfg.layers):
         p = f"h{l}." if (cfg.layers > 1 or cfg.mode == "gpt") else ""
         h = layer_norm(x, P[p + "ln1_gamma"], P[p + "ln1_beta"], cfg.ln_eps)
-        q, k, v = h @ P[p + "Wq"], h @ P[p + "Wk"], h @ P[p + "Wv"]
+        if cfg.mode == "gpt":
+            q, k, v = (h @ P[p + "Wqkv"]).split(D, dim=-1)
+        else:
+            q, k, v = h @ P[p + "Wq"], h @ P[p + "Wk"], h @ P[p + "Wv"]
         a = attention(q, k, v, cfg, B)
         x = x + a @ P[p + "Wo"]
         h = layer_norm(x, P[p + "ln2_gamma"], P[p + "ln2_beta"], cfg.ln_eps)

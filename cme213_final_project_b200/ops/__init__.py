@@ -328,3 +328,62 @@ def adam_step(master, grads, m, v, step_dev, lr_dev, *, compute=None, normsq=Non
                           ctypes.c_float(beta1), ctypes.c_float(beta2), ctypes.c_float(eps),
                           ctypes.c_float(weight_decay), ctypes.c_float(grad_scale), ctypes.c_float(clip_norm),
                           _p(nodecay), nn, _stream()))
+
+
+# --------------------------------------------------------------------------------------------------
+# Attention
+# --------------------------------------------------------------------------------------------------
+class CmeAttn(ctypes.Structure):
+    _fields_ = [
+        ("nb", ctypes.c_int), ("nh", ctypes.c_int), ("T", ctypes.c_int), ("HD", ctypes.c_int),
+        ("sb", ctypes.c_longlong), ("sh", ctypes.c_longlong), ("st", ctypes.c_longlong),
+        ("osb", ctypes.c_longlong), ("osh", ctypes.c_longlong), ("ost", ctypes.c_longlong),
+        ("causal", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("lse", ctypes.c_void_p),
+        ("d_o", ctypes.c_void_p), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+        ("delta", ctypes.c_void_p), ("dq_accum", ctypes.c_void_p),
+    ]
+
+
+_BACKENDS = {"auto": 0, "tc": 1, "simt": 2}
+
+
+def _attn_desc(q, B, H, T, layout, causal):
+    D = q.shape[-1]
+    HD = D // H
+    a = CmeAttn()
+    a.T, a.HD, a.causal, a.scale, a.dtype = T, HD, int(causal), 1.0 / (HD ** 0.5), _dt(q)
+    if layout == "flat":
+        a.nb, a.nh, a.sb, a.sh, a.st = B * H, 1, T * HD, 0, HD
+    else:
+        a.nb, a.nh, a.sb, a.sh, a.st = B, H, T * D, HD, D
+    a.osb, a.osh, a.ost = a.sb, a.sh, a.st
+    return a
+
+
+def attention_fwd(q, k, v, B: int, H: int, T: int, layout: str = "split", causal: bool = False,
+                  backend: str = "auto"):
+    """``q, k, v``: ``[B*T, D]``.  ``layout="flat"`` views each as ``[B*H, T, HD]`` without a transpose (the
+    reference's head layout); ``"split"`` is the standard ``[B, T, H, HD]`` split.  Returns ``(out, lse)``."""
+    _cuda(q, k, v)
+    a = _attn_desc(q, B, H, T, layout, causal)
+    out = torch.empty_like(q)
+    lse = torch.empty(B * H * T, dtype=torch.float32, device=q.device)
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    _check(lib().cme_attention_fwd(ctypes.byref(a), _BACKENDS[backend], _stream()))
+    return out, lse
+
+
+def attention_bwd(q, k, v, out, lse, dout, B: int, H: int, T: int, layout: str = "split", causal: bool = False,
+                  backend: str = "auto"):
+    _cuda(q, k, v, out, lse, dout)
+    a = _attn_desc(q, B, H, T, layout, causal)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty_like(lse)
+    acc = torch.empty(q.numel(), dtype=torch.float32, device=q.device)
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.d_o, a.dq, a.dk, a.dv = dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.delta, a.dq_accum = delta.data_ptr(), acc.data_ptr()
+    _check(lib().cme_attention_bwd(ctypes.byref(a), _BACKENDS[backend], _stream()))
+    return dq, dk, dv

@@ -1,0 +1,34 @@
+// Attention interface shared by the SIMT kernels, the tcgen05 kernels and the engine.
+//
+// One layout descriptor serves both head layouts of the framework:
+//   * "flat": the reference's reinterpretation of the row-major [B*T, D] projection as [B*H, T, HD]
+//     (FINAL_CLEAN_CODE_/src/model/transformer.cu:71-75,352-356) -> nb = B*H, nh = 1, batch stride T*HD,
+//     row stride HD;
+//   * "split": the standard [B, T, H, HD] split -> nb = B, nh = H, batch stride T*D, head stride HD,
+//     row stride D.
+// Element (b, h, t, d) of Q / K / V / dQ / dK / dV lives at  b*sb + h*sh + t*st + d;  O and dO have their own
+// strides (osb, osh, ost), because a fused [B*T, 3D] projection buffer has a different row pitch than O.
+#pragma once
+#include "common.h"
+
+struct CmeAttn {
+    int nb, nh, T, HD;
+    long long sb, sh, st;        // strides of Q / K / V / dQ / dK / dV
+    long long osb, osh, ost;     // strides of O / dO
+    int causal;
+    float scale;                 // 1 / sqrt(HD)
+    int dtype;                   // CME_BF16 or CME_F32
+    const void* q; const void* k; const void* v;
+    void* o;                     // forward output / backward input
+    float* lse;                  // [nb*nh, T] log-sum-exp of scaled scores (saved by forward)
+    // backward only
+    const void* d_o; void* dq; void* dk; void* dv;
+    float* delta;                // [nb*nh, T] scratch: rowsum(dO * O)
+    float* dq_accum;             // fp32 scratch [nb*nh*T*HD] for the tcgen05 backward (may be null)
+};
+
+int attention_simt_fwd(const CmeAttn* a, cudaStream_t st);
+int attention_simt_bwd(const CmeAttn* a, cudaStream_t st);
+int attention_tc_supported(const CmeAttn* a);
+int attention_tc_fwd(const CmeAttn* a, cudaStream_t st);
+int attention_tc_bwd(const CmeAttn* a, cudaStream_t st);

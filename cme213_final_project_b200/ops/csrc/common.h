@@ -105,21 +105,25 @@ __device__ __forceinline__ float dgelu_f(float x) {
     return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x2);
 }
 
-// 8 x bf16 <-> 8 x f32 through one 128-bit word.
-struct alignas(16) Bf16x8 { __nv_bfloat162 v[4]; };
+// 8 x bf16 <-> 8 x f32 through one 128-bit word (a uint4, so loads and stores stay single 128-bit accesses).
+typedef uint4 Bf16x8;
+__device__ __forceinline__ float2 bf2_to_f2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+__device__ __forceinline__ uint32_t f2_to_bf2(float lo, float hi) {
+    uint32_t w;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+    return w;
+}
 __device__ __forceinline__ void unpack8(const Bf16x8& p, float* f) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float2 t = __bfloat1622float2(p.v[i]);
-        f[2 * i] = t.x;
-        f[2 * i + 1] = t.y;
-    }
+    float2 t;
+    t = bf2_to_f2(p.x); f[0] = t.x; f[1] = t.y;
+    t = bf2_to_f2(p.y); f[2] = t.x; f[3] = t.y;
+    t = bf2_to_f2(p.z); f[4] = t.x; f[5] = t.y;
+    t = bf2_to_f2(p.w); f[6] = t.x; f[7] = t.y;
 }
 __device__ __forceinline__ Bf16x8 pack8(const float* f) {
-    Bf16x8 p;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    return p;
+    return make_uint4(f2_to_bf2(f[0], f[1]), f2_to_bf2(f[2], f[3]), f2_to_bf2(f[4], f[5]), f2_to_bf2(f[6], f[7]));
 }
 
 #endif  // __CUDACC__

@@ -1,0 +1,349 @@
+// Native model executor: forward and backward of the transformer over the flat arenas, every op one of
+// this library's kernels, every launch on the caller's stream (so a whole step can be captured in a
+// CUDA graph by the caller).
+//
+// Role of the reference's TransformerModel::forward_no_sync / backward_bucketed
+// (FINAL_CLEAN_CODE_/src/model/transformer.cu:337-408, 417-590).  Differences by design:
+//   * N blocks, ReLU or GELU, causal or not, flat or split heads, tied or untied head, optional final LN;
+//   * bias / activation / residual adds ride in GEMM epilogues instead of separate kernels
+//     (the reference launches bias_relu, residual_add_with_bias, residual+LayerNorm kernels);
+//   * the ReLU / GELU derivative rides in the dgrad GEMM epilogue; bias gradients are column sums;
+//   * weight gradients overwrite (or accumulate, for micro-batches after the first), so there is no
+//     gradient memset per step (the reference zeroes all gradients because split-K uses atomics);
+//   * `bucket_ready(index)` is called on the host right after the launches that complete a natural gradient
+//     bucket have been enqueued, in arena order -- the hook the reference calls sync_bucket (:428-457).
+#include "attention.h"
+#include "gemm.h"
+
+#include <new>
+#include <vector>
+
+extern "C" {
+int cme_layernorm_fwd(int, const void*, const void*, void*, const void*, const void*, void*, float*, float*, int, int,
+                      float, void*);
+int cme_layernorm_bwd_blocks(int);
+int cme_layernorm_bwd(int, const void*, const void*, const void*, const float*, const float*, const void*, void*, void*,
+                      void*, float*, int, int, int, void*);
+int cme_colsum_splits(int, int);
+int cme_dact_colsum(int, const void*, const void*, void*, void*, float*, int, int, int, int, void*);
+int cme_embedding_fwd(int, const int*, const void*, const void*, void*, int, int, int, int, void*);
+int cme_embedding_bwd(int, const int*, const void*, void*, void*, int, int, int, int, int, void*);
+int cme_cross_entropy(int, const void*, const int*, void*, float*, float*, int, int, long long, float, float, float,
+                      int, void*);
+int cme_attention_fwd(const CmeAttn*, int, void*);
+int cme_attention_bwd(const CmeAttn*, int, void*);
+int cme_gemm(const CmeGemm*, int, void*);
+}
+
+struct CmeEngineDesc {
+    int V, T, D, H, FF, L, B;
+    int act;             // CME_ACT_RELU | CME_ACT_GELU
+    int causal, head_flat, tied, final_ln, fused_qkv;
+    float ln_eps, prob_eps;
+    int dtype;           // CME_BF16 | CME_F32
+    int gemm_backend;    // 0 auto, 1 tcgen05, 2 simt
+    int attn_backend;    // 0 auto, 1 tensor-core, 2 simt
+};
+
+// Element offsets into the parameter / gradient arenas; -1 = tensor absent.
+struct CmeLayerSlots { long long W2, b2, W1, b1, ln2g, ln2b, Wo, Wq, Wk, Wv, Wqkv, ln1g, ln1b; };
+struct CmeGlobalSlots { long long Wout, lnfg, lnfb, tok, pos; };
+
+typedef void (*CmeBucketFn)(void* user, int natural_bucket);
+
+namespace {
+
+struct LayerAct {
+    char *ln1, *qkv, *attn, *xmid, *ln2, *ffpre, *ffact;
+    float *mean1, *rstd1, *mean2, *rstd2, *lse;
+};
+
+struct Engine {
+    CmeEngineDesc d;
+    size_t es;
+    int BT, BH;
+    std::vector<CmeLayerSlots> ls;
+    CmeGlobalSlots gs;
+    char* params = nullptr;
+    char* grads = nullptr;
+    char* ws = nullptr;
+    size_t ws_bytes = 0;
+    // activations
+    std::vector<char*> x;          // L+1 residual-stream buffers
+    std::vector<LayerAct> la;
+    char *xf, *logits;
+    float *meanf, *rstdf, *losses;
+    // backward temporaries
+    char *dxa, *dxb, *dff, *dln, *dqkv, *dattn;
+    float *delta, *dq_accum, *ln_scratch, *col_scratch;
+    void* gemm_ws; long long gemm_ws_bytes;
+
+    char* P(long long off) const { return params + off * (long long)es; }
+    char* G(long long off) const { return grads + off * (long long)es; }
+};
+
+size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+
+// One pass computes the carve-up; with base == nullptr it only measures.
+size_t carve(Engine& e, char* base) {
+    const CmeEngineDesc& d = e.d;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        char* p = base ? base + off : nullptr;
+        off += align_up(bytes);
+        return p;
+    };
+    const size_t BT = e.BT, D = d.D, FF = d.FF, es = e.es;
+    e.x.resize(d.L + 1);
+    for (int l = 0; l <= d.L; ++l) e.x[l] = take(BT * D * es);
+    e.la.resize(d.L);
+    for (int l = 0; l < d.L; ++l) {
+        LayerAct& a = e.la[l];
+        a.ln1 = take(BT * D * es);
+        a.qkv = take(3 * BT * D * es);
+        a.attn = take(BT * D * es);
+        a.xmid = take(BT * D * es);
+        a.ln2 = take(BT * D * es);
+        a.ffpre = d.act == CME_ACT_GELU ? take(BT * FF * es) : nullptr;
+        a.ffact = take(BT * FF * es);
+        a.mean1 = (float*)take(BT * 4); a.rstd1 = (float*)take(BT * 4);
+        a.mean2 = (float*)take(BT * 4); a.rstd2 = (float*)take(BT * 4);
+        a.lse = (float*)take((size_t)e.BH * d.T * 4);
+    }
+    e.xf = d.final_ln ? take(BT * D * es) : nullptr;
+    e.meanf = (float*)take(BT * 4); e.rstdf = (float*)take(BT * 4);
+    e.logits = take(BT * (size_t)d.V * es);
+    e.losses = (float*)take(BT * 4);
+    e.dxa = take(BT * D * es); e.dxb = take(BT * D * es);
+    e.dff = take(BT * FF * es);
+    e.dln = take(BT * D * es);
+    e.dqkv = take(3 * BT * D * es);
+    e.dattn = take(BT * D * es);
+    e.delta = (float*)take((size_t)e.BH * d.T * 4);
+    e.dq_accum = (float*)take(BT * D * 4);
+    const size_t widest = FF > D ? FF : D;
+    e.ln_scratch = (float*)take((size_t)cme_layernorm_bwd_blocks((int)BT) * 2 * D * 4);
+    e.col_scratch = (float*)take((size_t)(cme_colsum_splits((int)BT, (int)D) + cme_colsum_splits((int)BT, (int)FF)) *
+                                 widest * 4);
+    e.gemm_ws_bytes = 64ll << 20;
+    e.gemm_ws = take((size_t)e.gemm_ws_bytes);
+    return off;
+}
+
+int gemm(const Engine& e, cudaStream_t st, int M, int N, int K, const void* A, long long lda, int a_trans,
+         const void* B, long long ldb, int b_trans, void* C, long long ldc, int accumulate = 0,
+         const void* bias = nullptr, int act = 0, void* aux_out = nullptr, int dact = 0, const void* aux_in = nullptr,
+         long long ldaux = 0, const void* residual = nullptr, long long ldres = 0, int batch = 1, long long sA = 0,
+         long long sB = 0, long long sC = 0) {
+    CmeGemm g{};
+    g.M = M; g.N = N; g.K = K; g.batch = batch;
+    g.A = A; g.lda = lda; g.strideA = sA; g.a_trans = a_trans;
+    g.B = B; g.ldb = ldb; g.strideB = sB; g.b_trans = b_trans;
+    g.C = C; g.ldc = ldc; g.strideC = sC; g.c_dtype = e.d.dtype; g.ab_dtype = e.d.dtype;
+    g.bias = bias; g.residual = residual; g.ldres = ldres;
+    g.aux_out = aux_out; g.aux_in = aux_in; g.ldaux = ldaux;
+    g.act = act; g.dact = dact; g.accumulate = accumulate;
+    g.workspace = e.gemm_ws; g.workspace_bytes = e.gemm_ws_bytes;
+    return cme_gemm(&g, e.d.gemm_backend, st);
+}
+
+void fill_attn(const Engine& e, int l, CmeAttn& a) {
+    const CmeEngineDesc& d = e.d;
+    const int HD = d.D / d.H;
+    const long long BT = e.BT, D = d.D;
+    a = CmeAttn{};
+    a.T = d.T; a.HD = HD; a.causal = d.causal; a.scale = 1.0f / sqrtf((float)HD); a.dtype = d.dtype;
+    char* qkv = e.la[l].qkv;
+    if (d.fused_qkv) {            // [BT, 3D] rows: Q | K | V
+        a.nb = d.B; a.nh = d.H; a.sb = (long long)d.T * 3 * D; a.sh = HD; a.st = 3 * D;
+        a.q = qkv; a.k = qkv + D * e.es; a.v = qkv + 2 * D * e.es;
+        a.dq = e.dqkv; a.dk = e.dqkv + D * e.es; a.dv = e.dqkv + 2 * D * e.es;
+    } else {                      // three [BT, D] planes
+        if (d.head_flat) { a.nb = d.B * d.H; a.nh = 1; a.sb = (long long)d.T * HD; a.sh = 0; a.st = HD; }
+        else { a.nb = d.B; a.nh = d.H; a.sb = (long long)d.T * D; a.sh = HD; a.st = D; }
+        a.q = qkv; a.k = qkv + BT * D * e.es; a.v = qkv + 2 * BT * D * e.es;
+        a.dq = e.dqkv; a.dk = e.dqkv + BT * D * e.es; a.dv = e.dqkv + 2 * BT * D * e.es;
+    }
+    if (d.head_flat) { a.osb = (long long)d.T * HD; a.osh = 0; a.ost = HD; }
+    else { a.osb = (long long)d.T * D; a.osh = HD; a.ost = D; }
+    a.lse = e.la[l].lse; a.delta = e.delta; a.dq_accum = e.dq_accum;
+}
+
+#define TRY(expr) do { int rc__ = (expr); if (rc__) return rc__; } while (0)
+
+}  // namespace
+
+CME_API int cme_engine_create(const CmeEngineDesc* desc, const CmeLayerSlots* layers, const CmeGlobalSlots* globals,
+                              void** out) {
+    CME_REQUIRE(desc->L >= 1 && desc->D % desc->H == 0, CME_ERR_SHAPE, "engine: bad model shape");
+    CME_REQUIRE(!(desc->fused_qkv && desc->head_flat), CME_ERR_SHAPE, "engine: fused QKV needs split heads");
+    CME_REQUIRE(!desc->head_flat || desc->T % desc->H == 0, CME_ERR_SHAPE, "engine: flat heads need T %% H == 0");
+    Engine* e = new (std::nothrow) Engine();
+    CME_REQUIRE(e != nullptr, CME_ERR_CUDA, "engine: out of host memory");
+    e->d = *desc;
+    e->es = desc->dtype == CME_BF16 ? 2 : 4;
+    e->BT = desc->B * desc->T;
+    e->BH = desc->B * desc->H;
+    e->ls.assign(layers, layers + desc->L);
+    e->gs = *globals;
+    e->ws_bytes = carve(*e, nullptr);
+    *out = e;
+    return CME_OK;
+}
+
+CME_API long long cme_engine_workspace_bytes(void* h) { return (long long)static_cast<Engine*>(h)->ws_bytes; }
+
+CME_API int cme_engine_bind(void* h, void* params, void* grads, void* workspace, long long workspace_bytes) {
+    Engine* e = static_cast<Engine*>(h);
+    CME_REQUIRE((size_t)workspace_bytes >= e->ws_bytes, CME_ERR_LIMIT, "engine: workspace too small");
+    CME_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, CME_ERR_SHAPE, "engine: workspace must be 256-byte aligned");
+    e->params = (char*)params; e->grads = (char*)grads; e->ws = (char*)workspace;
+    carve(*e, e->ws);
+    return CME_OK;
+}
+
+CME_API void cme_engine_destroy(void* h) { delete static_cast<Engine*>(h); }
+
+CME_API void* cme_engine_logits(void* h) { return static_cast<Engine*>(h)->logits; }
+CME_API void* cme_engine_activation(void* h, int layer, int which) {
+    Engine* e = static_cast<Engine*>(h);
+    if (which == 0) return e->x[layer];
+    const LayerAct& a = e->la[layer];
+    switch (which) {
+        case 1: return a.ln1; case 2: return a.qkv; case 3: return a.attn; case 4: return a.xmid;
+        case 5: return a.ln2; case 6: return a.ffact; default: return nullptr;
+    }
+}
+
+// Forward: logits, per-token losses, and *loss_out (+)= loss_weight * mean loss.  With targets == null
+// only the logits are produced.  The cross-entropy kernel leaves d(logits) * grad_scale in the logits
+// buffer, ready for backward.
+CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, float* loss_out, float loss_weight,
+                               int accumulate_loss, float grad_scale, void* stream) {
+    Engine& e = *static_cast<Engine*>(h);
+    const CmeEngineDesc& d = e.d;
+    cudaStream_t st = (cudaStream_t)stream;
+    CME_REQUIRE(e.ws != nullptr, CME_ERR_SHAPE, "engine: not bound");
+    const int BT = e.BT, D = d.D, FF = d.FF, V = d.V, dt = d.dtype;
+    TRY(cme_embedding_fwd(dt, tokens, e.P(e.gs.tok), e.P(e.gs.pos), e.x[0], BT, d.T, D, V, st));
+    for (int l = 0; l < d.L; ++l) {
+        const CmeLayerSlots& s = e.ls[l];
+        LayerAct& a = e.la[l];
+        TRY(cme_layernorm_fwd(dt, e.x[l], nullptr, nullptr, e.P(s.ln1g), e.P(s.ln1b), a.ln1, a.mean1, a.rstd1, BT, D,
+                              d.ln_eps, st));
+        if (d.fused_qkv)
+            TRY(gemm(e, st, BT, 3 * D, D, a.ln1, D, 0, e.P(s.Wqkv), 3 * D, 0, a.qkv, 3 * D));
+        else      // three weight matrices back to back, one shared A: a batch of 3
+            TRY(gemm(e, st, BT, D, D, a.ln1, D, 0, e.P(s.Wq), D, 0, a.qkv, D, 0, nullptr, 0, nullptr, 0, nullptr, 0,
+                     nullptr, 0, 3, 0, (long long)D * D, (long long)BT * D));
+        CmeAttn at;
+        fill_attn(e, l, at);
+        at.o = a.attn;
+        TRY(cme_attention_fwd(&at, d.attn_backend, st));
+        // x_mid = x + attn @ Wo
+        TRY(gemm(e, st, BT, D, D, a.attn, D, 0, e.P(s.Wo), D, 0, a.xmid, D, 0, nullptr, 0, nullptr, 0, nullptr, 0,
+                 e.x[l], D));
+        TRY(cme_layernorm_fwd(dt, a.xmid, nullptr, nullptr, e.P(s.ln2g), e.P(s.ln2b), a.ln2, a.mean2, a.rstd2, BT, D,
+                              d.ln_eps, st));
+        // ff_act = act(ln2 @ W1 + b1)   (GELU also keeps the pre-activation for its derivative)
+        TRY(gemm(e, st, BT, FF, D, a.ln2, D, 0, e.P(s.W1), FF, 0, a.ffact, FF, 0, e.P(s.b1), d.act, a.ffpre, 0, nullptr,
+                 FF));
+        // x_next = x_mid + ff_act @ W2 + b2
+        TRY(gemm(e, st, BT, D, FF, a.ffact, FF, 0, e.P(s.W2), D, 0, e.x[l + 1], D, 0, e.P(s.b2), 0, nullptr, 0, nullptr,
+                 0, a.xmid, D));
+    }
+    const void* xlast = e.x[d.L];
+    if (d.final_ln) {
+        TRY(cme_layernorm_fwd(dt, e.x[d.L], nullptr, nullptr, e.P(e.gs.lnfg), e.P(e.gs.lnfb), e.xf, e.meanf, e.rstdf,
+                              BT, D, d.ln_eps, st));
+        xlast = e.xf;
+    }
+    if (d.tied) TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.tok), D, 1, e.logits, V));
+    else        TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.Wout), V, 0, e.logits, V));
+    if (targets)
+        TRY(cme_cross_entropy(dt, e.logits, targets, e.logits, e.losses, loss_out, BT, V, V, grad_scale, d.prob_eps,
+                              loss_weight, accumulate_loss, st));
+    return CME_OK;
+}
+
+// Backward from d(logits) left in the logits buffer by forward.  accumulate != 0 adds into the gradient
+// arena (micro-batches after the first); otherwise every gradient is overwritten.
+CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeBucketFn bucket_ready, void* user,
+                                void* stream) {
+    Engine& e = *static_cast<Engine*>(h);
+    const CmeEngineDesc& d = e.d;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int BT = e.BT, D = d.D, FF = d.FF, V = d.V, dt = d.dtype;
+    int bucket = 0;
+    auto emit = [&]() { if (bucket_ready) bucket_ready(user, bucket); ++bucket; };
+    float* col_a = e.col_scratch;
+    const void* xlast = d.final_ln ? e.xf : e.x[d.L];
+    char* dx = e.dxa;       // gradient w.r.t. the residual stream entering the part being processed
+    char* dx_other = e.dxb;
+    // ---- output head
+    if (d.tied) {
+        TRY(gemm(e, st, BT, D, V, e.logits, V, 0, e.P(e.gs.tok), D, 0, dx, D));                 // dX = dL @ tok
+        TRY(gemm(e, st, V, D, BT, e.logits, V, 1, xlast, D, 0, e.G(e.gs.tok), D, accumulate));  // dtok = dL^T @ X
+    } else {
+        TRY(gemm(e, st, BT, D, V, e.logits, V, 0, e.P(e.gs.Wout), V, 1, dx, D));                // dX = dL @ Wout^T
+        TRY(gemm(e, st, D, V, BT, xlast, D, 1, e.logits, V, 0, e.G(e.gs.Wout), V, accumulate)); // dWout = X^T @ dL
+        emit();
+    }
+    if (d.final_ln) {
+        TRY(cme_layernorm_bwd(dt, dx, e.x[d.L], e.P(e.gs.lnfg), e.meanf, e.rstdf, nullptr, dx_other, e.G(e.gs.lnfg),
+                              e.G(e.gs.lnfb), e.ln_scratch, BT, D, accumulate, st));
+        std::swap(dx, dx_other);
+        emit();
+    }
+    for (int l = d.L - 1; l >= 0; --l) {
+        const CmeLayerSlots& s = e.ls[l];
+        LayerAct& a = e.la[l];
+        // ---- FFN2:  x_next = x_mid + ff_act @ W2 + b2
+        const void* aux = d.act == CME_ACT_GELU ? a.ffpre : a.ffact;       // relu'(pre) == (act > 0)
+        TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF, 0, nullptr, 0, nullptr, d.act, aux, FF));
+        TRY(gemm(e, st, FF, D, BT, a.ffact, FF, 1, dx, D, 0, e.G(s.W2), D, accumulate));
+        TRY(cme_dact_colsum(dt, dx, nullptr, nullptr, e.G(s.b2), col_a, BT, D, 0, accumulate, st));
+        emit();
+        // ---- FFN1:  ff_pre = ln2 @ W1 + b1   (e.dff now holds d ff_pre)
+        TRY(gemm(e, st, BT, D, FF, e.dff, FF, 0, e.P(s.W1), FF, 1, e.dln, D));
+        TRY(gemm(e, st, D, FF, BT, a.ln2, D, 1, e.dff, FF, 0, e.G(s.W1), FF, accumulate));
+        TRY(cme_dact_colsum(dt, e.dff, nullptr, nullptr, e.G(s.b1), col_a, BT, FF, 0, accumulate, st));
+        emit();
+        // ---- LN2 (+ residual gradient): d x_mid = LN'(d ln2) + dx
+        TRY(cme_layernorm_bwd(dt, e.dln, a.xmid, e.P(s.ln2g), a.mean2, a.rstd2, dx, dx_other, e.G(s.ln2g), e.G(s.ln2b),
+                              e.ln_scratch, BT, D, accumulate, st));
+        std::swap(dx, dx_other);                                            // dx = d x_mid
+        emit();
+        // ---- attention output projection:  x_mid = x + attn @ Wo
+        TRY(gemm(e, st, BT, D, D, dx, D, 0, e.P(s.Wo), D, 1, e.dattn, D));
+        TRY(gemm(e, st, D, D, BT, a.attn, D, 1, dx, D, 0, e.G(s.Wo), D, accumulate));
+        emit();
+        // ---- attention
+        CmeAttn at;
+        fill_attn(e, l, at);
+        at.o = a.attn; at.d_o = e.dattn;
+        TRY(cme_attention_bwd(&at, d.attn_backend, st));
+        // ---- QKV projection
+        if (d.fused_qkv) {
+            TRY(gemm(e, st, BT, D, 3 * D, e.dqkv, 3 * D, 0, e.P(s.Wqkv), 3 * D, 1, e.dln, D));
+            TRY(gemm(e, st, D, 3 * D, BT, a.ln1, D, 1, e.dqkv, 3 * D, 0, e.G(s.Wqkv), 3 * D, accumulate));
+        } else {
+            const long long pl = (long long)BT * D * e.es, wm = (long long)D * D * e.es;
+            for (int i = 0; i < 3; ++i)
+                TRY(gemm(e, st, BT, D, D, e.dqkv + i * pl, D, 0, e.P(s.Wq) + i * wm, D, 1, e.dln, D, i > 0));
+            TRY(gemm(e, st, D, D, BT, a.ln1, D, 1, e.dqkv, D, 0, e.G(s.Wq), D, accumulate, nullptr, 0, nullptr, 0,
+                     nullptr, 0, nullptr, 0, 3, 0, (long long)BT * D, (long long)D * D));
+        }
+        emit();
+        // ---- LN1 (+ residual gradient): d x = LN'(d ln1) + d x_mid
+        TRY(cme_layernorm_bwd(dt, e.dln, e.x[l], e.P(s.ln1g), a.mean1, a.rstd1, dx, dx_other, e.G(s.ln1g), e.G(s.ln1b),
+                              e.ln_scratch, BT, D, accumulate, st));
+        std::swap(dx, dx_other);
+        emit();
+    }
+    // ---- embeddings (tied: the table gradient already holds the output-head part, so the scatter adds)
+    TRY(cme_embedding_bwd(dt, tokens, dx, e.G(e.gs.tok), nullptr, BT, d.T, D, V, (d.tied || accumulate) ? 1 : 0, st));
+    TRY(cme_embedding_bwd(dt, tokens, dx, nullptr, e.G(e.gs.pos), BT, d.T, D, V, accumulate, st));
+    emit();
+    return CME_OK;
+}

@@ -38,7 +38,8 @@ template <int BN> struct Cfg {
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int STAGING_BYTES = 4 * 2 * 4096;     // per epilogue warp: two 32-row x 128-byte buffers
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 struct EpiParams {
@@ -50,6 +51,7 @@ struct EpiParams {
     const void* residual; long long ldres;
     void* aux_out; const void* aux_in; long long ldaux;
     int act, dact, accumulate;
+    int tma_store;                 // outputs go through shared memory and TMA tile stores
     int* status;
 };
 
@@ -73,7 +75,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
                     acc[j] += o.x; acc[j + 1] += o.y; acc[j + 2] += o.z; acc[j + 3] += o.w;
                 }
             } else {
-                for (int j = 0; j < ncols; ++j) acc[j] += C[j];
+                _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) acc[j] += C[j];
             }
         }
         if (full) {
@@ -81,7 +83,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
             for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<float4*>(C + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
         } else {
-            for (int j = 0; j < ncols; ++j) C[j] = acc[j];
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) C[j] = acc[j];
         }
         return;
     }
@@ -92,7 +94,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
 #pragma unroll
             for (int j = 0; j < 32; j += 8) *reinterpret_cast<Bf16x8*>(X + j) = pack8(acc + j);
         } else {
-            for (int j = 0; j < ncols; ++j) X[j] = __float2bfloat16_rn(acc[j]);
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) X[j] = __float2bfloat16_rn(acc[j]);
         }
     }
     if (p.act == CME_ACT_RELU) {
@@ -109,7 +111,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
 #pragma unroll
             for (int j = 0; j < 32; j += 8) unpack8(*reinterpret_cast<const Bf16x8*>(X + j), x + j);
         } else {
-            for (int j = 0; j < 32; ++j) x[j] = (j < ncols) ? __bfloat162float(X[j]) : 0.f;
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) x[j] = (j < ncols) ? __bfloat162float(X[j]) : 0.f;
         }
         if (p.dact == CME_ACT_RELU) {
 #pragma unroll
@@ -130,7 +132,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
                 for (int q = 0; q < 8; ++q) acc[j + q] += r[q];
             }
         } else {
-            for (int j = 0; j < ncols; ++j) acc[j] += __bfloat162float(R[j]);
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) acc[j] += __bfloat162float(R[j]);
         }
     }
     if (p.accumulate) {
@@ -143,24 +145,94 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
                 for (int q = 0; q < 8; ++q) acc[j + q] += r[q];
             }
         } else {
-            for (int j = 0; j < ncols; ++j) acc[j] += __bfloat162float(C[j]);
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) acc[j] += __bfloat162float(C[j]);
         }
     }
     if (full) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) *reinterpret_cast<Bf16x8*>(C + j) = pack8(acc + j);
     } else {
-        for (int j = 0; j < ncols; ++j) C[j] = __float2bfloat16_rn(acc[j]);
+        _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) C[j] = __float2bfloat16_rn(acc[j]);
+    }
+}
+
+
+// Guarded 8-wide bf16 row read: vector when the group is inside the matrix, scalar at the ragged edge.
+__device__ __forceinline__ void load8_guard(const __nv_bfloat16* rowp, int n, int N, bool row_ok, float* f) {
+    if (row_ok && n + 8 <= N) {
+        unpack8(*reinterpret_cast<const Bf16x8*>(rowp + n), f);
+    } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] = (row_ok && n + q < N) ? __bfloat162float(rowp[n + q]) : 0.f;
+    }
+}
+
+// Fused epilogue arithmetic on 32 columns of one row (bf16 outputs).  `pre` receives the pre-activation.
+__device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, float* pre, bool row_ok, long long offc,
+                                              long long offr, long long offa, int n) {
+    if (p.bias) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float b[8];
+            load8_guard(p.bias, n + g * 8, p.N, true, b);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += b[q];
+        }
+    }
+    if (p.aux_out) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) pre[j] = acc[j];
+    }
+    if (p.act == CME_ACT_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
+    } else if (p.act == CME_ACT_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = gelu_f(acc[j]);
+    }
+    if (p.dact) {
+        const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + offa;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float x[8];
+            load8_guard(X, n + g * 8, p.N, row_ok, x);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                acc[g * 8 + q] = (p.dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
+                                                          : acc[g * 8 + q] * dgelu_f(x[q]);
+        }
+    }
+    if (p.residual) {
+        const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.residual) + offr;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float x[8];
+            load8_guard(R, n + g * 8, p.N, row_ok, x);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
+        }
+    }
+    if (p.accumulate) {
+        const __nv_bfloat16* Cp = reinterpret_cast<const __nv_bfloat16*>(p.C) + offc;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float x[8];
+            load8_guard(Cp, n + g * 8, p.N, row_ok, x);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
+        }
     }
 }
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const EpiParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const EpiParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint8_t* staging = smem + C::STAGES * C::STAGE_BYTES;       // 1024-byte aligned
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::STAGING_BYTES);
     uint64_t* full_bar = bars;                       // [STAGES]  TMA -> MMA
     uint64_t* empty_bar = bars + C::STAGES;          // [STAGES]  MMA -> TMA
     uint64_t* tfull_bar = bars + 2 * C::STAGES;      // [2]       MMA -> epilogue
@@ -281,6 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const bool vec_ok = (p.N % 8 == 0) && (p.ldc % 8 == 0) &&
                             (!p.residual || p.ldres % 8 == 0) && ((!p.aux_in && !p.aux_out) || p.ldaux % 8 == 0);
         int it = 0;
+        uint32_t store_cnt = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int mn = tile % tiles_mn, rest = tile / tiles_mn;
@@ -295,22 +368,95 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const long long offc = zoff * p.strideC + (long long)row * p.ldc;
             const long long offr = (long long)bidx * p.strideC + (long long)row * p.ldres;
             const long long offa = (long long)bidx * p.strideC + (long long)row * p.ldaux;
+            const uint32_t tmem_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+            if (!p.tma_store) {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + c * 32, r);
-                tmem_wait_ld();
-                const int n = n0 + c * 32;
-                if (row < p.M && n < p.N) {
-                    float acc[32];
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_row + c * 32, r);
+                    tmem_wait_ld();
+                    const int n = n0 + c * 32;
+                    if (row < p.M && n < p.N) {
+                        float acc[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-                    epilogue_chunk(p, acc, offc, offr, offa, n, min(32, p.N - n), vec_ok);
+                        for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+                        epilogue_chunk(p, acc, offc, offr, offa, n, min(32, p.N - n), vec_ok);
+                    }
+                }
+            } else if (p.c_f32) {
+                // fp32 output (split-K partials, fp32 C): 32 columns = one 128-byte staging row per TMA store
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int n = n0 + c * 32;
+                    if (n >= p.N) break;
+                    uint32_t r[32];
+                    tmem_ld32(tmem_row + c * 32, r);
+                    tmem_wait_ld();
+                    if (p.accumulate) {
+                        const float* Cp = reinterpret_cast<const float*>(p.C) + offc;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (row < p.M && n + j < p.N) r[j] = __float_as_uint(__uint_as_float(r[j]) + Cp[n + j]);
+                    }
+                    uint8_t* sb = staging + quarter * 8192 + (store_cnt & 1) * 4096;
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(sb + lane * 128 + ((q ^ (lane & 7)) * 16)) =
+                            make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&tmC, sb, n, m0 + quarter * 32, (int)zoff);
+                        tma_store_commit();
+                    }
+                    ++store_cnt;
+                }
+            } else {
+                // bf16 output: 64 columns = one 128-byte staging row per TMA store
+                const bool row_ok = row < p.M;
+#pragma unroll 1
+                for (int c2 = 0; c2 < BN / 64; ++c2) {
+                    const int n = n0 + c2 * 64;
+                    if (n >= p.N) break;
+                    uint8_t* sbC = staging + quarter * 8192 + (p.aux_out ? 0 : (store_cnt & 1) * 4096);
+                    uint8_t* sbX = staging + quarter * 8192 + 4096;
+                    if (lane == 0) {
+                        if (p.aux_out) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem_row + c2 * 64 + h * 32, r);
+                        tmem_wait_ld();
+                        float acc[32], pre[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+                        epilogue_math(p, acc, pre, row_ok, offc, offr, offa, n + h * 32);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const int q = h * 4 + g;
+                            *reinterpret_cast<uint4*>(sbC + lane * 128 + ((q ^ (lane & 7)) * 16)) = pack8(acc + g * 8);
+                            if (p.aux_out)
+                                *reinterpret_cast<uint4*>(sbX + lane * 128 + ((q ^ (lane & 7)) * 16)) = pack8(pre + g * 8);
+                        }
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&tmC, sbC, n, m0 + quarter * 32, (int)zoff);
+                        if (p.aux_out) tma_store_3d(&tmX, sbX, n, m0 + quarter * 32, bidx);
+                        tma_store_commit();
+                    }
+                    ++store_cnt;
                 }
             }
             tc_fence_before();
             mbar_arrive(&tempty_bar[buf]);
         }
+        if (p.tma_store && lane == 0) tma_store_wait<0>();   // stores complete before shared memory goes away
     }
 
     tc_fence_before();
@@ -363,18 +509,19 @@ EncodeTiledFn get_encoder() {
     return fn;
 }
 
-// 3-D bf16 tensor map: dims (inner, rows, batch), 128-byte swizzle, box (64, box_rows, 1).
+// 3-D tensor map: dims (inner, rows, batch), 128-byte swizzle, box (128 bytes of inner, box_rows, 1).
 int make_tmap(CUtensorMap* out, const void* base, long long inner, long long rows, long long ld, long long batch,
-              long long batch_stride, int box_rows) {
+              long long batch_stride, int box_rows, bool f32 = false) {
     EncodeTiledFn enc = get_encoder();
     CME_REQUIRE(enc != nullptr, CME_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const int es = f32 ? 4 : 2;
     cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch_stride > 0 ? batch_stride : ld * rows) * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * es, (cuuint64_t)(batch_stride > 0 ? batch_stride : ld * rows) * es};
+    cuuint32_t box[3] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CME_REQUIRE(r == CUDA_SUCCESS, CME_ERR_CUDA,
                 "cuTensorMapEncodeTiled failed (%d): inner=%lld rows=%lld ld=%lld batch=%lld bstride=%lld box_rows=%d",
                 (int)r, inner, rows, ld, batch, batch_stride, box_rows);
@@ -385,25 +532,26 @@ int g_num_sms = 0;
 int* g_status = nullptr;     // device status word shared by all launches on this device
 
 template <int BN, bool A_MN, bool B_MN>
-int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const EpiParams& ep, int grid, cudaStream_t st) {
+int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
+               const EpiParams& ep, int grid, cudaStream_t st) {
     auto kern = gemm_tc_kernel<BN, A_MN, B_MN>;
     static bool attr_set = false;
     if (!attr_set) {
         CME_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
         attr_set = true;
     }
-    kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ta, tb, ep);
+    kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ta, tb, tc, tx, ep);
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
 
 template <int BN>
-int launch_bn(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const EpiParams& ep, int grid,
-              cudaStream_t st) {
-    if (!a_mn && !b_mn) return launch_cfg<BN, false, false>(ta, tb, ep, grid, st);
-    if (!a_mn && b_mn) return launch_cfg<BN, false, true>(ta, tb, ep, grid, st);
-    if (a_mn && !b_mn) return launch_cfg<BN, true, false>(ta, tb, ep, grid, st);
-    return launch_cfg<BN, true, true>(ta, tb, ep, grid, st);
+int launch_bn(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+              const CUtensorMap& tx, const EpiParams& ep, int grid, cudaStream_t st) {
+    if (!a_mn && !b_mn) return launch_cfg<BN, false, false>(ta, tb, tc, tx, ep, grid, st);
+    if (!a_mn && b_mn) return launch_cfg<BN, false, true>(ta, tb, tc, tx, ep, grid, st);
+    if (a_mn && !b_mn) return launch_cfg<BN, true, false>(ta, tb, tc, tx, ep, grid, st);
+    return launch_cfg<BN, true, true>(ta, tb, tc, tx, ep, grid, st);
 }
 
 }  // namespace
@@ -444,30 +592,40 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     }
     const int tiles_m = cme_cdiv(g->M, BM);
     const int num_kb = cme_cdiv(g->K, BK);
-    // Tile width: the widest that still gives every SM a tile; narrow tiles for small problems.
-    int bn = g->force_bn;
-    if (!bn) {
-        bn = 256;
-        while (bn > 64 && (long long)tiles_m * cme_cdiv(g->N, bn) * g->batch < g_num_sms) bn >>= 1;
-        if (g->N <= 64) bn = 64;
-        else if (g->N <= 128 && bn > 128) bn = 128;
+    // Tile width and K splits: minimise  waves x k-blocks per unit x cost(bn)  (+ fixed per-tile and
+    // per-split overheads).  cost(bn) per 16-deep MMA is max(tensor time bn/2, shared-memory read time
+    // (128 + bn)/4) in clocks: 128 / 64 / 48 for bn = 256 / 128 / 64.
+    const bool plain_epi = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;
+    int bn = g->force_bn, splits = g->force_splits;
+    if (!bn || !splits) {
+        double best = 1e30;
+        int best_bn = 128, best_s = 1;
+        const int bns[3] = {256, 128, 64};
+        const double cost[3] = {128.0, 64.0, 48.0};
+        for (int i = 0; i < 3; ++i) {
+            if (g->force_bn && bns[i] != g->force_bn) continue;
+            if (bns[i] > 64 && g->N <= bns[i] / 2) continue;            // tile mostly padding
+            const long long t = (long long)tiles_m * cme_cdiv(g->N, bns[i]) * g->batch;
+            for (int s = 1; s <= 16; ++s) {
+                if (g->force_splits && s != g->force_splits) continue;
+                if (s > 1 && (!plain_epi || !g->workspace || num_kb / s < 4 ||
+                              (long long)s * g->batch * g->M * g->N * 4 > g->workspace_bytes)) break;
+                const long long units = t * s;
+                const double waves = (double)((units + g_num_sms - 1) / g_num_sms);
+                const double kb = (double)cme_cdiv(num_kb, s);
+                // 4 MMAs per k-block; epilogue / pipeline fill ~ 6 k-blocks of the widest tile per unit;
+                // a split adds one fp32 write + read of the output per split
+                double est = waves * ((kb + 2.0) * 4.0 * cost[i] + 6.0 * 4.0 * bns[i] / 2.0);
+                if (s > 1) est += 400.0 + (double)s * g->M * g->N * g->batch / g_num_sms / 16.0;
+                if (est < best) { best = est; best_bn = bns[i]; best_s = s; }
+            }
+        }
+        if (!bn) bn = best_bn;
+        if (!splits) splits = best_s;
     }
     CME_REQUIRE(bn == 64 || bn == 128 || bn == 256, CME_ERR_SHAPE, "tile width must be 64, 128 or 256");
     const int tiles_n = cme_cdiv(g->N, bn);
     const long long tiles = (long long)tiles_m * tiles_n * g->batch;
-    // Split-K when the output has too few tiles to fill the machine and K is long.
-    int splits = g->force_splits;
-    const bool plain_epi = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;
-    if (!splits) {
-        splits = 1;
-        if (plain_epi && g->workspace && tiles * 2 <= g_num_sms && num_kb >= 8) {
-            splits = (int)(g_num_sms / tiles);
-            if (splits > num_kb / 4) splits = num_kb / 4;
-            while (splits > 1 &&
-                   (long long)splits * g->batch * g->M * g->N * 4 > g->workspace_bytes) --splits;
-            if (splits < 1) splits = 1;
-        }
-    }
     if (splits > 1) {
         CME_REQUIRE(plain_epi, CME_ERR_SHAPE, "split-K supports only the plain / accumulate epilogue");
         CME_REQUIRE(g->workspace && (long long)splits * g->batch * g->M * g->N * 4 <= g->workspace_bytes,
@@ -501,12 +659,30 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         ep.aux_out = g->aux_out; ep.aux_in = g->aux_in; ep.ldaux = g->ldaux;
         ep.act = g->act; ep.dact = g->dact; ep.accumulate = g->accumulate;
     }
+    // Outputs through shared-memory staging + TMA tile stores when rows are 16-byte addressable.
+    CUtensorMap tc = ta, tx = ta;
+    {
+        const int es = ep.c_f32 ? 4 : 2;
+        auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        const long long nb = (long long)splits * g->batch;
+        bool ok = al16(ep.C) && (ep.ldc * es) % 16 == 0 && (nb == 1 || (ep.strideC * es) % 16 == 0);
+        if (ep.aux_out) ok = ok && al16(ep.aux_out) && (ep.ldaux * 2) % 16 == 0;
+        if (ok) {
+            rc = make_tmap(&tc, ep.C, g->N, g->M, ep.ldc, nb, nb > 1 ? ep.strideC : 0, 32, ep.c_f32 != 0);
+            if (rc) return rc;
+            if (ep.aux_out) {
+                rc = make_tmap(&tx, ep.aux_out, g->N, g->M, ep.ldaux, g->batch, g->batch > 1 ? ep.strideC : 0, 32);
+                if (rc) return rc;
+            }
+            ep.tma_store = 1;
+        }
+    }
     const long long total = tiles * splits;
     const int grid = (int)(total < g_num_sms ? total : g_num_sms);
     const bool a_mn = g->a_trans != 0, b_mn = g->b_trans == 0;
-    if (bn == 256) rc = launch_bn<256>(a_mn, b_mn, ta, tb, ep, grid, stream);
-    else if (bn == 128) rc = launch_bn<128>(a_mn, b_mn, ta, tb, ep, grid, stream);
-    else rc = launch_bn<64>(a_mn, b_mn, ta, tb, ep, grid, stream);
+    if (bn == 256) rc = launch_bn<256>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+    else if (bn == 128) rc = launch_bn<128>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+    else rc = launch_bn<64>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
     if (rc) return rc;
     if (splits > 1) {
         const long long per = (long long)g->batch * g->M * g->N;

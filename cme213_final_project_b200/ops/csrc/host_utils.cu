@@ -38,3 +38,9 @@ CME_API int cme_device_info(int* sms, int* cc_major, int* cc_minor, long long* s
     *smem_optin = (long long)prop.sharedMemPerBlockOptin;
     return CME_OK;
 }
+
+// Device-to-device copy on a stream (used to read engine-owned buffers into caller-owned tensors).
+CME_API int cme_copy_d2d(void* dst, const void* src, long long bytes, void* stream) {
+    CME_CUDA(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return CME_OK;
+}

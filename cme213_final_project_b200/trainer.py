@@ -42,8 +42,22 @@ class Trainer:
         if isinstance(tokens, torch.Tensor):
             tokens, targets = [tokens], [targets]
         m, d = self.model, self.dist
-        if hasattr(m, "train_step") and getattr(m, "handles_sync", False):
-            m.train_step(tokens, targets)            # native engine: sync and update are fused on the device
+        if hasattr(m, "train_step"):                 # native engine: one call enqueues every micro-batch
+            d.begin_step()
+            with nvtx_range("backward_bucketed" if self.use_overlap else "forward_backward", self.run.profile):
+                if self.use_overlap:
+                    m.train_step(tokens, targets, self._bucket_ready, self.buckets)
+                    d.finish_async_gradient_syncs()
+                else:
+                    m.train_step(tokens, targets)
+                    if d.world_size > 1 and not getattr(m, "handles_sync", False):
+                        with nvtx_range("gradient_sync", self.run.profile):
+                            d.sync_gradients(m.grads)
+            self.comm_ms_sum += d.last_sync_ms
+            self.async_start_ms_sum += d.last_async_start_ms
+            if not getattr(m, "handles_sync", False):
+                with nvtx_range("adam_update", self.run.profile):
+                    m.update(grad_scale=1.0 / d.world_size if d.defer_gradient_average else 1.0)
             self.steps += 1
             return
         accum = len(tokens)
