@@ -387,3 +387,10 @@ def attention_bwd(q, k, v, out, lse, dout, B: int, H: int, T: int, layout: str =
     a.delta, a.dq_accum = delta.data_ptr(), acc.data_ptr()
     _check(lib().cme_attention_bwd(ctypes.byref(a), _BACKENDS[backend], _stream()))
     return dq, dk, dv
+
+
+def launch_count() -> int:
+    """Kernels launched (or captured) by the native library so far in this process."""
+    l = lib()
+    l.cme_launch_count.restype = ctypes.c_longlong
+    return int(l.cme_launch_count())

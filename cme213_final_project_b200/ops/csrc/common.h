@@ -36,7 +36,13 @@ CME_API const char* cme_last_error();
         }                                                                                      \
     } while (0)
 
-#define CME_LAUNCH_CHECK() CME_CUDA(cudaGetLastError())
+// Every kernel launch of the library goes through this check; the counter is what `cme_launch_count` reports.
+extern long long g_cme_launches;
+#define CME_LAUNCH_CHECK()                  \
+    do {                                    \
+        ++g_cme_launches;                   \
+        CME_CUDA(cudaGetLastError());       \
+    } while (0)
 
 #define CME_REQUIRE(cond, code, ...)                                                           \
     do {                                                                                       \

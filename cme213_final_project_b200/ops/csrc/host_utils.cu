@@ -6,6 +6,7 @@
 #include <cstring>
 
 static thread_local char g_err[1024] = "";
+long long g_cme_launches = 0;
 
 void cme_set_error(const char* fmt, ...) {
     va_list ap;
@@ -44,3 +45,6 @@ CME_API int cme_copy_d2d(void* dst, const void* src, long long bytes, void* stre
     CME_CUDA(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
     return CME_OK;
 }
+
+// Number of kernels this library has launched (or captured into a graph) in this process.
+CME_API long long cme_launch_count() { return g_cme_launches; }

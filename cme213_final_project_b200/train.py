@@ -117,9 +117,12 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
 
     all_x = all_x.to(d.device)
     all_y = all_y.to(d.device)
-    if run.cuda_graph and d.device.type == "cuda" and hasattr(model, "enable_cuda_graph"):
-        model.enable_cuda_graph(warmup_steps=3)
-        say("CUDA Graph: enabled, capture after 3 warmup steps")
+    if run.cuda_graph and d.device.type == "cuda":
+        if trainer.enable_cuda_graph(warmup_steps=3):
+            say("CUDA Graph: enabled, capture after 3 warmup steps")
+        elif root:
+            print("Warning: --cuda-graph needs the native engine and, with several ranks, the fused sync path; "
+                  "running eagerly", file=sys.stderr)
 
     BT = model_cfg.tokens_per_step
     step_loss = 0.0

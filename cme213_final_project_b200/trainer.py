@@ -32,6 +32,21 @@ class Trainer:
         self.comm_ms_sum = 0.0
         self.async_start_ms_sum = 0.0
         self.steps = 0
+        self.graphed = None
+
+    def enable_cuda_graph(self, warmup_steps: int = 3) -> bool:
+        """Replay the whole step as one CUDA graph after ``warmup_steps`` eager steps (the reference's
+        ``CME213_USE_CUDA_GRAPH=1``, ``main.cu:299-355``).  Host-issued collectives with host waits cannot be
+        captured, so with more than one rank this needs the fused device synchronisation path."""
+        m = self.model
+        if not hasattr(m, "train_step") or m.device.type != "cuda":
+            return False
+        if self.dist.world_size > 1 and not getattr(m, "handles_sync", False):
+            return False
+        from .graph import GraphedStep
+        self.graphed = GraphedStep(self._step, m.cfg.tokens_per_step, max(self.run.grad_accum, 1), m.device,
+                                   warmup=warmup_steps)
+        return True
 
     # ---------------------------------------------------------------------------------------------
     def _bucket_ready(self, b: Bucket) -> None:
@@ -41,6 +56,13 @@ class Trainer:
         """One optimizer step over ``len(tokens)`` micro-batches (``grad_accum`` of them)."""
         if isinstance(tokens, torch.Tensor):
             tokens, targets = [tokens], [targets]
+        if self.graphed is not None:
+            self.graphed(tokens, targets)
+            self.steps += 1
+        else:
+            self._step(tokens, targets)
+
+    def _step(self, tokens: Sequence[torch.Tensor], targets: Sequence[torch.Tensor]) -> None:
         m, d = self.model, self.dist
         if hasattr(m, "train_step"):                 # native engine: one call enqueues every micro-batch
             d.begin_step()
