@@ -450,3 +450,55 @@ CME_API int cme_embedding_bwd(int dtype, const int* tokens, const void* dout, vo
     }
     return CME_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of cme_dact_colsum (see noalloc.h for who it is for and the rules of use).
+// ---------------------------------------------------------------------------------------------------
+#include "noalloc.h"
+
+#include <mutex>
+
+// Scratch for the per-split partial column sums.  In host code this name is only a handle for the runtime
+// (it is not a device address); the address kernels may use comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_scratch[CME_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device; looked up once per device.
+int noalloc_scratch(float** out) {
+    int dev = 0;
+    CME_CUDA(cudaGetDevice(&dev));
+    CME_REQUIRE(dev >= 0 && dev < kMaxDevices, CME_ERR_LIMIT, "noalloc: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        CME_CUDA(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+        CME_REQUIRE(p != nullptr, CME_ERR_CUDA, "noalloc: cudaGetSymbolAddress returned a null address");
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return CME_OK;
+}
+}  // namespace
+
+CME_API int cme_dact_colsum_noalloc(int dtype, const void* dout, const void* pre, void* g, void* dbias, int rows,
+                                    int cols, int act, int accumulate, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    CME_REQUIRE(rows > 0 && cols > 0, CME_ERR_SHAPE, "dact_colsum_noalloc: empty input");
+    CME_REQUIRE(dtype == CME_F32 || dtype == CME_BF16, CME_ERR_SHAPE, "dact_colsum_noalloc: unknown dtype %d", dtype);
+    const int splits = cme_colsum_splits(rows, cols);
+    const long long need = (long long)splits * cols;
+    CME_REQUIRE(need <= (long long)CME_NOALLOC_SCRATCH_FLOATS, CME_ERR_LIMIT,
+                "dact_colsum_noalloc: %d rows x %d cols needs %lld scratch floats, the built-in scratch holds %d; "
+                "use cme_dact_colsum with a caller-provided buffer",
+                rows, cols, need, (int)CME_NOALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    return DISPATCH_T(dtype,
+                      dact_colsum_t<__nv_bfloat16>(dout, pre, g, dbias, scratch, splits, rows, cols, act, accumulate, st),
+                      dact_colsum_t<float>(dout, pre, g, dbias, scratch, splits, rows, cols, act, accumulate, st));
+}
