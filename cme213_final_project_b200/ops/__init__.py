@@ -394,3 +394,10 @@ def launch_count() -> int:
     l = lib()
     l.cme_launch_count.restype = ctypes.c_longlong
     return int(l.cme_launch_count())
+
+
+def attention_check_status() -> int:
+    """Read and clear the status word of the tensor-core attention kernels (non-zero: a wait ran out)."""
+    v = ctypes.c_int(0)
+    _check(lib().cme_attention_check_status(ctypes.byref(v)))
+    return v.value

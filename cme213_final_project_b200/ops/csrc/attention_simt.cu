@@ -242,6 +242,15 @@ int check(const CmeAttn* a, bool bwd) {
 
 }  // namespace
 
+// delta[bh, t] = sum_d dO * O, shared with the tensor-core backward.
+int attention_delta_launch(const CmeAttn* a, cudaStream_t st) {
+    const int rows = a->nb * a->nh * a->T;
+    if (a->dtype == CME_BF16) attn_delta_kernel<__nv_bfloat16><<<cme_cdiv(rows, 8), 256, 0, st>>>(*a);
+    else attn_delta_kernel<float><<<cme_cdiv(rows, 8), 256, 0, st>>>(*a);
+    CME_LAUNCH_CHECK();
+    return CME_OK;
+}
+
 int attention_simt_fwd(const CmeAttn* a, cudaStream_t st) {
     int rc = check(a, false);
     if (rc) return rc;
