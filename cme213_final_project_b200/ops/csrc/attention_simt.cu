@@ -112,6 +112,25 @@ __global__ void attn_delta_kernel(const CmeAttn a) {
     s = warp_sum(s);
     if ((threadIdx.x & 31) == 0) a.delta[row] = s;
 }
+// bf16, head size 64, 16-byte aligned rows: 8 lanes per row (one 128-bit load each), 4 rows per warp.
+__global__ void attn_delta_hd64_kernel(const CmeAttn a) {
+    const int rows = a.nb * a.nh * a.T;
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 3, sub = threadIdx.x & 7;
+    float s = 0.f;
+    if (row < rows) {
+        const int bh = row / a.T, t = row % a.T;
+        const long long off = head_base_o(a, bh) + (long long)t * a.ost + sub * 8;
+        float x[8], y[8];
+        unpack8(*reinterpret_cast<const Bf16x8*>((const __nv_bfloat16*)a.d_o + off), x);
+        unpack8(*reinterpret_cast<const Bf16x8*>((const __nv_bfloat16*)a.o + off), y);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += x[i] * y[i];
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (row < rows && sub == 0) a.delta[row] = s;
+}
 
 // KV = false: block owns RT queries, streams keys:    dQ = scale * sum_j dS_ij K_j
 // KV = true : block owns RT keys, streams queries:    dV = sum_i P_ij dO_i ;  dK = scale * sum_i dS_ij Q_i
@@ -245,7 +264,11 @@ int check(const CmeAttn* a, bool bwd) {
 // delta[bh, t] = sum_d dO * O, shared with the tensor-core backward.
 int attention_delta_launch(const CmeAttn* a, cudaStream_t st) {
     const int rows = a->nb * a->nh * a->T;
-    if (a->dtype == CME_BF16) attn_delta_kernel<__nv_bfloat16><<<cme_cdiv(rows, 8), 256, 0, st>>>(*a);
+    const bool al = ((reinterpret_cast<uintptr_t>(a->d_o) | reinterpret_cast<uintptr_t>(a->o)) & 15) == 0 &&
+                    a->ost % 8 == 0 && a->osh % 8 == 0 && a->osb % 8 == 0;
+    if (a->dtype == CME_BF16 && a->HD == 64 && al)
+        attn_delta_hd64_kernel<<<cme_cdiv((long long)rows * 8, 256), 256, 0, st>>>(*a);
+    else if (a->dtype == CME_BF16) attn_delta_kernel<__nv_bfloat16><<<cme_cdiv(rows, 8), 256, 0, st>>>(*a);
     else attn_delta_kernel<float><<<cme_cdiv(rows, 8), 256, 0, st>>>(*a);
     CME_LAUNCH_CHECK();
     return CME_OK;

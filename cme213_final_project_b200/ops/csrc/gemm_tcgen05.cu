@@ -102,7 +102,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
         for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
     } else if (p.act == CME_ACT_GELU) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = gelu_f(acc[j]);
+        for (int j = 0; j < 32; ++j) acc[j] = gelu_fast(acc[j]);
     }
     if (p.dact) {
         const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + row_off_aux + n;
@@ -118,7 +118,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
             for (int j = 0; j < 32; ++j) acc[j] = x[j] > 0.f ? acc[j] : 0.f;
         } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] *= dgelu_f(x[j]);
+            for (int j = 0; j < 32; ++j) acc[j] *= dgelu_fast(x[j]);
         }
     }
     if (p.residual) {
@@ -188,7 +188,7 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
         for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
     } else if (p.act == CME_ACT_GELU) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = gelu_f(acc[j]);
+        for (int j = 0; j < 32; ++j) acc[j] = gelu_fast(acc[j]);
     }
     if (p.dact) {
         const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + offa;
@@ -199,7 +199,7 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
 #pragma unroll
             for (int q = 0; q < 8; ++q)
                 acc[g * 8 + q] = (p.dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
-                                                          : acc[g * 8 + q] * dgelu_f(x[q]);
+                                                          : acc[g * 8 + q] * dgelu_fast(x[q]);
         }
     }
     if (p.residual) {
@@ -601,7 +601,7 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         double best = 1e30;
         int best_bn = 128, best_s = 1;
         const int bns[3] = {256, 128, 64};
-        const double cost[3] = {128.0, 64.0, 48.0};
+        const double cost[3] = {128.0, 80.0, 64.0};     // narrower tiles re-read A more often than they compute
         for (int i = 0; i < 3; ++i) {
             if (g->force_bn && bns[i] != g->force_bn) continue;
             if (bns[i] > 64 && g->N <= bns[i] / 2) continue;            // tile mostly padding

@@ -232,15 +232,26 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
 }
 
 // dgamma[c] (+)= sum_b partial[b][0][c];  dbeta[c] (+)= sum_b partial[b][1][c]
+// Block (32 columns x 8 block-groups): each thread sums every 8th partial, then a fixed-order shared-memory
+// reduction over the 8 groups (deterministic).
 template <typename T>
-__global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int D, T* dgamma, T* dbeta,
-                                       int accumulate) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= 2 * D) return;
+__global__ void __launch_bounds__(256)
+ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int D, T* dgamma, T* dbeta, int accumulate) {
+    __shared__ float sm[8][33];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
     float s = 0.f;
-    for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * 2 * D + c];
-    T* dst = (c < D) ? dgamma + c : dbeta + (c - D);
-    *dst = from_f32<T>(accumulate ? to_f32<T>(*dst) + s : s);
+    if (c < 2 * D)
+        for (int b = ry; b < nblocks; b += 8) s += partial[(long long)b * 2 * D + c];
+    sm[ry][cx] = s;
+    __syncthreads();
+    if (ry == 0 && c < 2 * D) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t += sm[r][cx];
+        T* dst = (c < D) ? dgamma + c : dbeta + (c - D);
+        *dst = from_f32<T>(accumulate ? to_f32<T>(*dst) + t : t);
+    }
 }
 
 template <typename T>
@@ -278,7 +289,7 @@ int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, co
                                                 (T*)dx, scratch, rows, D);
     }
     CME_LAUNCH_CHECK();
-    ln_bwd_finalize_kernel<T><<<cme_cdiv(2 * D, 256), 256, 0, st>>>(scratch, nblocks, D, (T*)dgamma, (T*)dbeta,
+    ln_bwd_finalize_kernel<T><<<cme_cdiv(2 * D, 32), 256, 0, st>>>(scratch, nblocks, D, (T*)dgamma, (T*)dbeta,
                                                                   accumulate);
     CME_LAUNCH_CHECK();
     return CME_OK;
@@ -299,7 +310,7 @@ CME_API int cme_layernorm_fwd(int dtype, const void* a, const void* b, void* r_o
 // Number of partial blocks the backward uses for `rows`; scratch must hold blocks * 2 * D floats.
 CME_API int cme_layernorm_bwd_blocks(int rows) {
     int b = cme_cdiv(rows, LN_WARPS);
-    return b < 296 ? b : 296;
+    return b < 592 ? b : 592;
 }
 
 // dx = LN'(dy) [+ dres]; dgamma/dbeta (+)= column sums.  `scratch`: cme_layernorm_bwd_blocks(rows)*2*D floats.

@@ -52,6 +52,60 @@ cross_entropy_kernel(const T* __restrict__ logits, const int* __restrict__ targe
     }
 }
 
+
+// bf16 rows whose length is a multiple of 8 and whose base is 16-byte aligned: 128-bit loads, the row is kept
+// in shared memory between the statistics pass and the gradient pass when it fits (read once from DRAM).
+constexpr int CEV_THREADS = 512;
+__global__ void __launch_bounds__(CEV_THREADS)
+cross_entropy_bf16_vec_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                              __nv_bfloat16* dlogits, float* __restrict__ losses, int V, long long ld,
+                              float grad_scale, float prob_eps, int cache_row) {
+    extern __shared__ uint4 srow[];
+    __shared__ float scratch[32];
+    const long long off = (long long)blockIdx.x * ld;
+    const uint4* row = reinterpret_cast<const uint4*>(logits + off);
+    const int nv = V / 8;
+    float m = -INFINITY, s = 0.f;
+    for (int i = threadIdx.x; i < nv; i += CEV_THREADS) {
+        const uint4 u = row[i];
+        if (cache_row) srow[i] = u;
+        float x[8];
+        unpack8(u, x);
+        float mx = x[0];
+#pragma unroll
+        for (int j = 1; j < 8; ++j) mx = fmaxf(mx, x[j]);
+        if (mx > m) { s *= __expf(m - mx); m = mx; }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += __expf(x[j] - m);
+    }
+    const float row_max = block_max(m, scratch);
+    s = (m == -INFINITY) ? 0.f : s * __expf(m - row_max);
+    const float denom = block_sum(s, scratch);
+    const float inv = 1.f / (denom + prob_eps);
+    int tgt = targets[blockIdx.x];
+    tgt = tgt < 0 ? 0 : (tgt >= V ? V - 1 : tgt);
+    if (threadIdx.x == 0) {
+        const float xt = __bfloat162float(logits[off + tgt]);
+        const float p = __expf(xt - row_max) * inv;
+        losses[blockIdx.x] = prob_eps > 0.f ? -logf(p + prob_eps) : -(xt - row_max - logf(denom));
+    }
+    __syncthreads();
+    if (dlogits) {
+        uint4* g = reinterpret_cast<uint4*>(dlogits + off);
+        for (int i = threadIdx.x; i < nv; i += CEV_THREADS) {
+            float x[8];
+            unpack8(cache_row ? srow[i] : row[i], x);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float p = __expf(x[j] - row_max) * inv;
+                if (i * 8 + j == tgt) p -= 1.f;
+                x[j] = p * grad_scale;
+            }
+            g[i] = pack8(x);
+        }
+    }
+}
+
 // out (+)= weight * sum(x[0..n)); single block, fixed order.
 __global__ void __launch_bounds__(1024) reduce_scalar_kernel(const float* __restrict__ x, int n, float weight, float* out,
                                                              int accumulate) {
@@ -118,6 +172,61 @@ __global__ void __launch_bounds__(256) adam_kernel(const AdamArgs a) {
     }
 }
 
+
+// Four elements per thread-iteration (128-bit accesses on the fp32 state).  Requires n % 4 == 0, 16-byte
+// aligned arenas, and no-decay ranges whose ends are multiples of 4 (arena tensors start on 64-element
+// boundaries, so a group of four never straddles two tensors).
+template <typename TG>
+__global__ void __launch_bounds__(256) adam_vec4_kernel(const AdamArgs a) {
+    const int t = *a.step;
+    const float lr = *a.lr;
+    const float bc1 = 1.f - powf(a.beta1, (float)t), bc2 = 1.f - powf(a.beta2, (float)t);
+    const float ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
+    float gs = a.grad_scale;
+    if (a.normsq && a.clip_norm > 0.f) {
+        const float norm = sqrtf(*a.normsq) * a.grad_scale;
+        if (norm > a.clip_norm) gs *= a.clip_norm / norm;
+    }
+    const long long nv = a.n >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
+        const long long e = i << 2;
+        float g[4];
+        if constexpr (sizeof(TG) == 2) {
+            const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.grads) + e);
+            float2 lo = bf2_to_f2(u.x), hi = bf2_to_f2(u.y);
+            g[0] = lo.x; g[1] = lo.y; g[2] = hi.x; g[3] = hi.y;
+        } else {
+            const float4 u = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grads) + e);
+            g[0] = u.x; g[1] = u.y; g[2] = u.z; g[3] = u.w;
+        }
+        float4 m4 = *reinterpret_cast<const float4*>(a.m + e);
+        float4 v4 = *reinterpret_cast<const float4*>(a.v + e);
+        float4 p4 = *reinterpret_cast<const float4*>(a.master + e);
+        float decay = 1.f;
+        if (a.weight_decay > 0.f) {
+            int lo = 0, hi = a.n_nodecay;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (a.nodecay[2 * mid + 1] > e) hi = mid; else lo = mid + 1;
+            }
+            if (!(lo < a.n_nodecay && a.nodecay[2 * lo] <= e)) decay = 1.f - lr * a.weight_decay;
+        }
+        float* mp = &m4.x; float* vp = &v4.x; float* pp = &p4.x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float gj = g[j] * gs;
+            mp[j] = a.beta1 * mp[j] + (1.f - a.beta1) * gj;
+            vp[j] = a.beta2 * vp[j] + (1.f - a.beta2) * gj * gj;
+            pp[j] = pp[j] * decay - lr * (mp[j] * ibc1) / (sqrtf(vp[j] * ibc2) + a.eps);
+        }
+        *reinterpret_cast<float4*>(a.m + e) = m4;
+        *reinterpret_cast<float4*>(a.v + e) = v4;
+        *reinterpret_cast<float4*>(a.master + e) = p4;
+        if (a.compute)
+            *reinterpret_cast<uint2*>(a.compute + e) = make_uint2(f2_to_bf2(p4.x, p4.y), f2_to_bf2(p4.z, p4.w));
+    }
+}
+
 }  // namespace
 
 // Per-row loss and gradient, then *loss_out (+)= loss_weight * mean(losses).
@@ -127,7 +236,21 @@ CME_API int cme_cross_entropy(int dtype, const void* logits, const int* targets,
                               float loss_weight, int accumulate_loss, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     CME_REQUIRE(rows > 0 && V > 0, CME_ERR_SHAPE, "cross_entropy: empty input");
-    if (dtype == CME_BF16)
+    const bool vec = dtype == CME_BF16 && V % 8 == 0 && ld % 8 == 0 && V >= 2048 &&
+                     (reinterpret_cast<uintptr_t>(logits) & 15) == 0 &&
+                     (!dlogits || (reinterpret_cast<uintptr_t>(dlogits) & 15) == 0);
+    if (vec) {
+        const size_t row_bytes = (size_t)V * 2;
+        const int cache = row_bytes <= 110 * 1024;          // two blocks per SM still fit
+        static bool attr = false;
+        if (!attr) {
+            CME_CUDA(cudaFuncSetAttribute(cross_entropy_bf16_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          110 * 1024));
+            attr = true;
+        }
+        cross_entropy_bf16_vec_kernel<<<rows, CEV_THREADS, cache ? row_bytes : 0, st>>>(
+            (const __nv_bfloat16*)logits, targets, (__nv_bfloat16*)dlogits, losses, V, ld, grad_scale, prob_eps, cache);
+    } else if (dtype == CME_BF16)
         cross_entropy_kernel<__nv_bfloat16><<<rows, CE_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets,
                                                                          (__nv_bfloat16*)dlogits, losses, V, ld,
                                                                          grad_scale, prob_eps);
@@ -172,7 +295,15 @@ CME_API int cme_adam(int grad_dtype, float* master, void* compute_bf16, const vo
                weight_decay, grad_scale, clip_norm, nodecay, n_nodecay};
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    if (grad_dtype == CME_BF16) adam_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, st>>>(a);
+    auto al = [](const void* p, int b) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & (b - 1)) == 0; };
+    bool vec = n % 4 == 0 && al(master, 16) && al(m, 16) && al(v, 16) && al(compute_bf16, 8) &&
+               al(grads, grad_dtype == CME_BF16 ? 8 : 16);
+    if (vec) {
+        blocks = (n / 4 + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (grad_dtype == CME_BF16) adam_vec4_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, st>>>(a);
+        else adam_vec4_kernel<float><<<(int)blocks, 256, 0, st>>>(a);
+    } else if (grad_dtype == CME_BF16) adam_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, st>>>(a);
     else adam_kernel<float><<<(int)blocks, 256, 0, st>>>(a);
     CME_LAUNCH_CHECK();
     return CME_OK;
