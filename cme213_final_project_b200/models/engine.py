@@ -97,8 +97,22 @@ class NativeEngine:
         ops._check(self.lib.cme_engine_bind(self._h, ctypes.c_void_p(self.params.data_ptr()),
                                             ctypes.c_void_p(self.grads.data_ptr()), ctypes.c_void_p(base),
                                             ctypes.c_longlong(nbytes)))
+        self._ws_base, self._ws_bytes = base, nbytes
         self._tokens: Optional[torch.Tensor] = None
         self._cb_keepalive = None
+        self.fused = None                 # set by parallel.fused_sync.attach_fused_sync
+        self.handles_sync = False
+
+    def rebind(self, params: torch.Tensor, grads: torch.Tensor) -> None:
+        """Point the executor at other parameter / gradient arenas (e.g. symmetric, peer-mapped buffers)."""
+        assert params.numel() >= self.layout.total and grads.numel() >= self.layout.total
+        assert params.dtype == self.dtype and grads.dtype == self.dtype
+        self.params, self.grads = params, grads
+        if self.strict:
+            self.master = params
+        ops._check(self.lib.cme_engine_bind(self._h, ctypes.c_void_p(params.data_ptr()),
+                                            ctypes.c_void_p(grads.data_ptr()), ctypes.c_void_p(self._ws_base),
+                                            ctypes.c_longlong(self._ws_bytes)))
 
     # ---------------------------------------------------------------------------------------------
     def __del__(self):
@@ -114,10 +128,16 @@ class NativeEngine:
         return self.layout.total
 
     def master_params(self) -> torch.Tensor:
+        """fp32 view of the parameters for checksums and trajectory statistics.  Under the fused path each rank
+        keeps fp32 master values only for the slices it owns, so the (rank-identical) bf16 parameters are used."""
+        if self.fused is not None and self.fused.world > 1:
+            return self.params.float()
         return self.master
 
     def state(self):
-        return self.master, self.adam_m, self.adam_v, self.step_count
+        if self.fused is not None and self.fused.world > 1:
+            return self.fused.gather_state()
+        return self.master, self.adam_m, self.adam_v, int(self.step_dev.item())
 
     def load_state(self, p, m, v, step: int) -> None:
         self.master.copy_(p.to(self.device))
@@ -185,7 +205,10 @@ class NativeEngine:
         return out.view(self.cfg.tokens_per_step, self.cfg.vocab_size)
 
     def update(self, grad_scale: float = 1.0, lr: Optional[float] = None) -> None:
-        """Unfused optimizer path: global norm (if clipping) then Adam / AdamW over the whole arena."""
+        """Unfused optimizer path: global norm (if clipping) then Adam / AdamW over the whole arena.
+        With the fused synchronisation path attached the update already happened inside the bucket kernels."""
+        if self.handles_sync:
+            return
         o = self.optim
         if lr is not None:
             self.set_lr(lr)
@@ -205,7 +228,16 @@ class NativeEngine:
 
     def train_step(self, tokens: Sequence[torch.Tensor], targets: Sequence[torch.Tensor],
                    bucket_callback=None, buckets=None) -> None:
-        """zero_grad + forward/backward over the micro-batches (gradients accumulate, the loss is their mean)."""
+        """zero_grad + forward/backward over the micro-batches (gradients accumulate, the loss is their mean).
+        With the fused path attached this is the whole optimizer step: buckets are reduced, applied and
+        redistributed by device kernels while backward runs."""
+        if self.fused is not None:
+            self.fused.train_step(tokens, targets)
+        else:
+            self.train_step_raw(tokens, targets, bucket_callback, buckets)
+
+    def train_step_raw(self, tokens: Sequence[torch.Tensor], targets: Sequence[torch.Tensor],
+                       bucket_callback=None, buckets=None) -> None:
         accum = len(tokens)
         gs = 1.0 / (self.cfg.tokens_per_step * accum)
         for i, (x, y) in enumerate(zip(tokens, targets)):

@@ -67,7 +67,9 @@ class Trainer:
         if hasattr(m, "train_step"):                 # native engine: one call enqueues every micro-batch
             d.begin_step()
             with nvtx_range("backward_bucketed" if self.use_overlap else "forward_backward", self.run.profile):
-                if self.use_overlap:
+                if getattr(m, "handles_sync", False):
+                    m.train_step(tokens, targets)
+                elif self.use_overlap:
                     m.train_step(tokens, targets, self._bucket_ready, self.buckets)
                     d.finish_async_gradient_syncs()
                 else:

@@ -1,0 +1,82 @@
+"""Multi-rank checks of the peer-memory kernels; run under torch.distributed.run by test_multi_gpu.py."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    from cme213_final_project_b200.config import RunConfig, preset
+    from cme213_final_project_b200.models.engine import NativeEngine
+    from cme213_final_project_b200.parallel.dist import DistributedContext
+    from cme213_final_project_b200.parallel.fused_sync import PeerComm, attach_fused_sync
+    from cme213_final_project_b200.parallel.symm import SymmetricBuffer
+    ctx = DistributedContext().init(backend="nccl", device="cuda")
+    dev, W, R = ctx.device, ctx.world_size, ctx.rank
+    res = {"world": W}
+    comm = PeerComm(dev, max_buckets=8, budget_ms=5000.0)
+    # ---- all-reduce kernels: rank-fill pattern (FINAL_CLEAN_CODE_/tests/benchmark_allreduce_alpha_beta.cu:205,236)
+    # and random data against an fp64 sum
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (W * 8, 4096 * W, 1 << 20):
+            src, dst = SymmetricBuffer(n, dtype, dev), SymmetricBuffer(n, dtype, dev)
+            algos = ["one_shot", "two_shot"] + (["nvls"] if src.multicast_ptr else [])
+            for i, algo in enumerate(algos):
+                src.tensor.fill_(R + 1)
+                src.barrier()
+                comm.allreduce(src, dst, n, algo=algo, bucket=i)
+                torch.cuda.synchronize()
+                assert comm.check_status() == 0, (algo, n)
+                want = W * (W + 1) / 2
+                assert (dst.tensor.float() - want).abs().max().item() < 1e-4 * want, (algo, dtype, n)
+                g = torch.Generator(device=dev).manual_seed(100 + R)
+                src.tensor.copy_(torch.randn(n, generator=g, device=dev).to(dtype))
+                ref = src.tensor.double().clone()
+                dist.all_reduce(ref)
+                src.barrier()
+                comm.allreduce(src, dst, n, algo=algo, scale=1.0 / W, bucket=i)
+                torch.cuda.synchronize()
+                tol = 1e-5 if dtype == torch.float32 else 2e-2
+                assert (dst.tensor.double() - ref / W).abs().max().item() < tol, (algo, dtype, n)
+                dst.barrier()
+    res["allreduce"] = "ok"
+    res["multicast"] = bool(SymmetricBuffer(64, torch.float32, dev).multicast_ptr)
+    # ---- fused RS + AdamW + AG against one process that accumulates every rank's batch
+    cfg, optim = preset("tiny-gpt")
+    run = RunConfig(bucket_kb=256, sync_mode="overlap")
+    eng = NativeEngine(cfg, optim, run, ctx, seed=7)
+    fs = attach_fused_sync(eng, ctx, run, use_nvls=os.environ.get("CME_TEST_NVLS", "1") == "1")
+    ref = NativeEngine(cfg, optim, RunConfig(), ctx, seed=7)
+    g = torch.Generator().manual_seed(5)
+    n = cfg.tokens_per_step
+    steps = 3
+    xs = torch.randint(0, cfg.vocab_size, (steps, W, n), generator=g, dtype=torch.int32).to(dev)
+    ys = torch.randint(0, cfg.vocab_size, (steps, W, n), generator=g, dtype=torch.int32).to(dev)
+    for s in range(steps):
+        eng.train_step([xs[s, R]], [ys[s, R]])
+        ref.train_step([xs[s, r] for r in range(W)], [ys[s, r] for r in range(W)])
+        ref.update()
+    torch.cuda.synchronize()
+    assert fs.comm.check_status() == 0
+    p = eng.params.float()
+    lo, hi = p.clone(), p.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    assert torch.equal(lo, hi), "parameters must be bit-identical on every rank"
+    err = (p - ref.params.float()).abs().max().item()
+    upd = (ref.params.float() - NativeEngine(cfg, optim, RunConfig(), ctx, seed=7).params.float()).abs().max().item()
+    assert err < 0.1 * upd + 1e-3, (err, upd)
+    master, m1, v1, t = eng.state()
+    assert t == steps and (master - ref.master).abs().max().item() < 0.1 * upd + 1e-3
+    res["fused"] = {"max_err": err, "max_update": upd, "buckets": len(fs.buckets), "nvls": bool(fs.use_nvls)}
+    if R == 0:
+        print("MP_RESULT " + json.dumps(res), flush=True)
+    ctx.finalize()
+
+
+if __name__ == "__main__":
+    main()
