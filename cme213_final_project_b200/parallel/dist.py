@@ -71,7 +71,7 @@ class DistributedContext:
         self._cv = threading.Condition()
         self._shutdown = False
         self._worker: Optional[threading.Thread] = None
-        self.drop_next_bucket = False       # host-side fault injection: a bucket hand-off that is lost
+        self.drop_next_bucket = False       # host-side fault injection: the next reduced bucket is lost on this rank
 
     # -- life cycle --------------------------------------------------------------------------------
     def init(self, backend: str = "auto", device: str = "auto", comm_thread: bool = False,
@@ -186,10 +186,11 @@ class DistributedContext:
         if self.world_size == 1:
             return
         t0 = time.perf_counter()
-        if self.drop_next_bucket:               # injected fault: the hand-off is lost
+        if self.drop_next_bucket:
+            # injected fault: this rank takes part in the collective (its peers must not be left waiting) but the
+            # reduced bucket never reaches its gradient arena
             self.drop_next_bucket = False
-            self.last_async_start_ms += (time.perf_counter() - t0) * 1e3
-            return
+            buf = buf.clone()
         p = _Pending(buf)
         if self.use_comm_thread:
             if buf.is_cuda:
