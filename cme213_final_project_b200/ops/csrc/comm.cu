@@ -21,6 +21,9 @@
 namespace {
 
 constexpr int MAX_RANKS = 16;
+// 128-thread CTAs: small enough in registers to share an SM with a resident GEMM or attention CTA, so a
+// communication kernel does not have to wait for (or displace) the persistent compute kernels.
+constexpr int COMM_THREADS = 128;
 
 struct Peers {
     void* buf[MAX_RANKS];          // the symmetric data buffer as mapped for each rank (index = rank)
@@ -158,7 +161,7 @@ __device__ __forceinline__ void reduce_peers(const Peers& P, long long vec_index
 // All-reduce of P.buf[*][0..n) across ranks into P.buf2[rank][0..n) (out of place: every rank's result lands in
 // its own second buffer).  n is a multiple of (16 bytes / element) * world.
 template <typename T>
-__global__ void __launch_bounds__(256) allreduce_kernel(const ArArgs a) {
+__global__ void __launch_bounds__(COMM_THREADS) allreduce_kernel(const ArArgs a) {
     constexpr int W = Vec16<T>::N;
     const Peers& P = a.P;
     const uint32_t e = a.ctl[3 * a.bucket] + 1;
@@ -245,7 +248,7 @@ struct FusedArgs {
 // One bucket of the data-parallel step: barrier -> reduce-scatter (this rank's 1/world slice of the bucket, fp32
 // accumulation in rank order) -> x grad_scale -> AdamW on the fp32 master slice -> bf16 parameters into every
 // rank's parameter arena -> barrier.  After the kernel every rank holds identical bf16 parameters for the bucket.
-__global__ void __launch_bounds__(256) fused_rs_adamw_ag_kernel(const FusedArgs a) {
+__global__ void __launch_bounds__(COMM_THREADS) fused_rs_adamw_ag_kernel(const FusedArgs a) {
     const Peers& P = a.P;
     const uint32_t e = a.ctl[3 * a.bucket] + 1;
     const int slot0 = 2 * a.bucket, slot1 = slot0 + 1;
@@ -364,7 +367,7 @@ CME_API int cme_comm_allreduce(int dtype, int world, int rank, void* const* buf,
     CME_REQUIRE(n > 0 && n % ((long long)w * world) == 0, CME_ERR_SHAPE,
                 "comm: element count %lld is not a multiple of %d", n, w * world);
     CME_REQUIRE(algo != 2 || mc_buf != nullptr, CME_ERR_UNSUPPORTED, "comm: NVLS requested without a multicast mapping");
-    CME_REQUIRE(ctas >= 1 && ctas <= 148, CME_ERR_SHAPE, "comm: CTA count must be in [1, 148]");
+    CME_REQUIRE(ctas >= 1 && ctas <= 740, CME_ERR_SHAPE, "comm: CTA count must be in [1, 740]");
     ArArgs a{};
     void* b1[MAX_RANKS]; void* b2[MAX_RANKS];
     for (int r = 0; r < world; ++r) {
@@ -377,8 +380,8 @@ CME_API int cme_comm_allreduce(int dtype, int world, int rank, void* const* buf,
     a.ctl = static_cast<uint32_t*>(ctl); a.status = status;
     a.budget_ns = (unsigned long long)(budget_ms * 1e6);
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == CME_BF16) allreduce_kernel<__nv_bfloat16><<<ctas, 256, 0, st>>>(a);
-    else allreduce_kernel<float><<<ctas, 256, 0, st>>>(a);
+    if (dtype == CME_BF16) allreduce_kernel<__nv_bfloat16><<<ctas, COMM_THREADS, 0, st>>>(a);
+    else allreduce_kernel<float><<<ctas, COMM_THREADS, 0, st>>>(a);
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
@@ -395,7 +398,7 @@ CME_API int cme_comm_fused_adamw(int world, int rank, void* const* grads, void* 
     CME_REQUIRE(count > 0 && count % (8ll * world) == 0 && start % 8 == 0, CME_ERR_SHAPE,
                 "comm: bucket [%lld, +%lld) is not aligned to 8 * world elements", start, count);
     CME_REQUIRE(!use_nvls || mc_grads != nullptr, CME_ERR_UNSUPPORTED, "comm: NVLS requested without a multicast mapping");
-    CME_REQUIRE(ctas >= 1 && ctas <= 148, CME_ERR_SHAPE, "comm: CTA count must be in [1, 148]");
+    CME_REQUIRE(ctas >= 1 && ctas <= 740, CME_ERR_SHAPE, "comm: CTA count must be in [1, 740]");
     FusedArgs a{};
     fill_peers(a.P, world, rank, grads, params, flags, mc_grads, mc_params);
     a.start = start; a.count = count; a.master = master; a.m = m; a.v = v; a.step = step; a.lr = lr;
@@ -403,7 +406,7 @@ CME_API int cme_comm_fused_adamw(int world, int rank, void* const* grads, void* 
     a.nodecay = nodecay; a.n_nodecay = n_nodecay; a.use_nvls = use_nvls; a.bucket = bucket;
     a.ctl = static_cast<uint32_t*>(ctl); a.status = status;
     a.budget_ns = (unsigned long long)(budget_ms * 1e6);
-    fused_rs_adamw_ag_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(a);
+    fused_rs_adamw_ag_kernel<<<ctas, COMM_THREADS, 0, (cudaStream_t)stream>>>(a);
     CME_LAUNCH_CHECK();
     return CME_OK;
 }

@@ -44,7 +44,7 @@ class PeerComm:
         self.flags.barrier()
 
     def allreduce(self, src, dst, n: int, offset: int = 0, algo: str = "two_shot", scale: float = 1.0,
-                  bucket: int = 0, ctas: int = 32, stream: Optional[torch.cuda.Stream] = None) -> None:
+                  bucket: int = 0, ctas: int = 64, stream: Optional[torch.cuda.Stream] = None) -> None:
         """``dst[offset:offset+n] = scale * sum_ranks src[offset:offset+n]`` (``src`` / ``dst``: symmetric buffers)."""
         st = stream or torch.cuda.current_stream()
         ops._check(self.lib.cme_comm_allreduce(
@@ -76,7 +76,7 @@ def choose_algo(nbytes: int, world: int, has_multicast: bool, table: Optional[di
 class FusedSync:
     """Owns the symmetric gradient / parameter arenas of an engine and launches the fused kernel per bucket."""
 
-    def __init__(self, model, ctx, run: RunConfig, ctas: int = 32, use_nvls: Optional[bool] = None,
+    def __init__(self, model, ctx, run: RunConfig, ctas: int = 296, use_nvls: Optional[bool] = None,
                  budget_ms: float = 5000.0) -> None:
         if model.strict:
             raise ops.NativeError("the fused synchronisation path needs bf16 gradients (--compute-dtype bf16)")
@@ -99,9 +99,15 @@ class FusedSync:
         elem = 2
         self.buckets: List[Bucket] = model.layout.coalesced_buckets(min_bucket_elems(run.bucket_kb, elem))
         self.comm = PeerComm(dev, max_buckets=max(len(self.buckets), 1), budget_ms=budget_ms, single=single)
-        self.ctas = ctas
+        import os
+        # SM budget: one small CTA per SM while backward is still running (they share SMs with the compute
+        # kernels); the last bucket has the GPU to itself and gets four per SM
+        self.ctas = int(os.environ.get("CME213_COMM_CTAS", ctas))
+        self.tail_ctas = int(os.environ.get("CME213_COMM_TAIL_CTAS", 4 * 148))
         mc = self.grads.multicast_ptr != 0 and self.params.multicast_ptr != 0
         self.use_nvls = mc if use_nvls is None else (use_nvls and mc)
+        if os.environ.get("CME213_COMM_NVLS") is not None:
+            self.use_nvls = mc and os.environ["CME213_COMM_NVLS"] != "0"
         self.stream = torch.cuda.Stream(device=dev)
         self.grad_scale = 1.0 / self.world
         self.lib = ops.lib()
@@ -121,7 +127,8 @@ class FusedSync:
             ctypes.c_longlong(b.start), ctypes.c_longlong(b.numel), ops._p(m.master), ops._p(m.adam_m),
             ops._p(m.adam_v), ops._p(m.step_dev), ops._p(m.lr_dev), ctypes.c_float(o.beta1), ctypes.c_float(o.beta2),
             ctypes.c_float(o.eps), ctypes.c_float(o.weight_decay), ctypes.c_float(self.grad_scale), ops._p(nd),
-            0 if nd is None else nd.shape[0], int(self.use_nvls), b.index, self.ctas, ops._p(self.comm.ctl),
+            0 if nd is None else nd.shape[0], int(self.use_nvls), b.index,
+            self.tail_ctas if b.index == len(self.buckets) - 1 else self.ctas, ops._p(self.comm.ctl),
             ops._p(self.comm.status), ctypes.c_double(self.comm.budget_ms), ctypes.c_void_p(self.stream.cuda_stream)))
         self.launched += 1
 
