@@ -8,12 +8,16 @@
 //
 // Forward, per CTA = one (batch, head) and 128 queries; 4 softmax warps (thread = query row) + 1 warp whose
 // lane 0 issues TMA loads and tcgen05.mma:
-//     S = Q K_j^T (TMEM)  ->  online softmax in registers  ->  P_j (bf16, shared, swizzled K-major)
-//     O_j = P_j V_j (TMEM, fresh each block)  ->  o = o * alpha + O_j in registers
-// Backward, per CTA = one (batch, head) and 128 keys, looping over query blocks:
-//     S^T = K Q_i^T,  dP^T = V dO_i^T (TMEM)  ->  P^T, dS^T (bf16, shared)
-//     dV += P^T dO_i,  dK += dS^T Q_i (TMEM accumulators)  dQ_i = dS K (TMEM, added to fp32 global with
-//     vector reductions; a small kernel scales and casts dQ at the end)
+//     S_j = Q K_j^T (TMEM) -> copied to registers (the tensor core starts S_{j+1} at once) -> online softmax with a
+//     lazily raised reference maximum -> P_j (bf16, shared, swizzled K-major) -> O += P_j V_j (TMEM accumulator,
+//     rescaled in place only when the reference maximum is raised)
+// Backward, per CTA = one (batch, head) and 128 keys, looping over query blocks (thread = query row, so the
+// row's log-sum-exp and delta are two registers):
+//     S = Q_i K^T,  dP = dO_i V^T (TMEM)  ->  P, dS (bf16, shared, double buffered)
+//     dV += P^T dO_i,  dK += dS^T Q_i (A operand read transposed; TMEM accumulators),  dQ_i = dS K (TMEM, added
+//     to fp32 global with vector reductions; a small kernel scales and casts dQ at the end).
+//     The scores of block i+1 are issued before the gradient MMAs of block i, so the arithmetic of block i+1
+//     overlaps them.
 // Every mbarrier wait is bounded; on expiry the CTA flags the status word, frees TMEM and returns.
 #include "attention.h"
 #include "sm100_ptx.cuh"
@@ -47,9 +51,20 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* s
                  "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* src, int c0, int c1, int c2) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+
+// A descriptor whose start address is `bytes` further than that of `base` (the address field counts 16-byte
+// units and never carries out of its 14 bits for shared-memory offsets), so the issuing thread spends one add
+// per operand instead of re-encoding the descriptor for each of the ~30 MMAs of a block.
+__device__ __forceinline__ uint64_t desc_add(uint64_t base, uint32_t bytes) { return base + (uint64_t)(bytes >> 4); }
 
 // Swizzled position of 16-byte chunk `c` of row `r` inside a [rows x 128 B] tile.
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
@@ -67,7 +82,8 @@ struct FwdParams {
 // shared: Q 16K | K[2] 32K | V[2] 32K | P 32K | barriers
 constexpr int FWD_SMEM = 7 * TILE_BYTES + 128;      // two CTAs per SM must fit: 2 x (this + 1 KB reserved) <= 228 KB
 constexpr int FWD_THREADS = 160;
-constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O partial: [128,192)
+constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O accumulator: [128,192)
+constexpr float RESCALE_THRESHOLD = 8.f;   // log2 units: the running maximum is only raised when it grows by > 2^8
 
 __global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -87,9 +103,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint64_t* kv_full = bars + 1;             // [2]
     uint64_t* kv_empty = bars + 3;            // [2]
     uint64_t* s_full = bars + 5;              // S ready for softmax
-    uint64_t* p_ready = bars + 6;             // P written (128 arrivals), S consumed
-    uint64_t* o_full = bars + 7;              // O partial ready, P consumed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* s_free = bars + 6;              // S copied to registers (128 arrivals): the next S may be issued
+    uint64_t* p_ready = bars + 7;             // P written, O rescaled (128 arrivals)
+    uint64_t* o_full = bars + 8;              // P V accumulated, P consumed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -103,6 +120,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
         mbar_init(s_full, 1);
+        mbar_init(s_free, 128);
         mbar_init(p_ready, 128);
         mbar_init(o_full, 1);
         fence_barrier_init();
@@ -128,12 +146,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tma_load_4d(sK + st * TILE_BYTES, &tmK, &kv_full[st], 0, j * BKV, h, b);
                 tma_load_4d(sV + st * TILE_BYTES, &tmV, &kv_full[st], 0, j * BKV, h, b);
             };
+            const uint64_t dQ_ = make_smem_desc(smem_u32(sQ), 0, 1024);
+            const uint64_t dK0 = make_smem_desc(smem_u32(sK), 0, 1024);
+            const uint64_t dV0 = make_smem_desc(smem_u32(sV), TILE_BYTES, 1024);
+            const uint64_t dP_ = make_smem_desc(smem_u32(sP), 0, 1024);
             auto issue_s = [&](int j) {
-                const uint32_t a = smem_u32(sQ), bb = smem_u32(sK + (j & 1) * TILE_BYTES);
+                const uint64_t kd = desc_add(dK0, (j & 1) * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    mma_f16_ss(tmem_S, make_smem_desc(a + k * 32, 0, 1024), make_smem_desc(bb + k * 32, 0, 1024),
-                               idesc_s, k > 0);
+                    mma_f16_ss(tmem_S, desc_add(dQ_, k * 32), desc_add(kd, k * 32), idesc_s, k > 0);
                 mma_commit(s_full);
             };
             load_kv(0);
@@ -142,21 +163,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (ok) { tc_fence_after(); issue_s(0); }
             for (int j = 0; j < nkv && ok; ++j) {
                 const int st = j & 1;
-                // P_j written and S_j consumed
-                if (!mbar_wait(p_ready, j & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t pa = smem_u32(sP), vb = smem_u32(sV + st * TILE_BYTES);
-#pragma unroll
-                for (int k = 0; k < BKV / 16; ++k)
-                    mma_f16_ss(tmem_O, make_smem_desc(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
-                               make_smem_desc(vb + k * 2048, TILE_BYTES, 1024), idesc_o, k > 0);
-                mma_commit(o_full);
-                mma_commit(&kv_empty[st]);
                 if (j + 1 < nkv) {
-                    if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    // S_j sits in registers now: the tensor core computes S_{j+1} while softmax_j runs
+                    if (!mbar_wait(s_free, j & 1, abort_flag) ||
+                        !mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
+                if (!mbar_wait(p_ready, j & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t vd = desc_add(dV0, st * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k)
+                    mma_f16_ss(tmem_O, desc_add(dP_, (k >> 2) * TILE_BYTES + (k & 3) * 32), desc_add(vd, k * 2048),
+                               idesc_o, (j > 0 || k > 0));
+                mma_commit(o_full);
+                mma_commit(&kv_empty[st]);
                 if (j + 2 < nkv) {
                     if (!mbar_wait(&kv_empty[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
                     load_kv(j + 2);
@@ -169,90 +191,83 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int row = warp * 32 + lane;                 // 0..127 == TMEM lane
         const int q = q0 + row;
         const uint32_t lane_addr = uint32_t(warp * 32) << 16;
-        float m = -INFINITY, l = 0.f, o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.f;
+        float m_ref = -INFINITY, l = 0.f;                 // reference maximum (log2 units) and running row sum
         bool ok = true;
         for (int j = 0; j < nkv && ok; ++j) {
             if (!mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const int k0 = j * BKV;
-            const bool need_mask = (k0 + BKV > p.T) || (p.causal && k0 + BKV - 1 > q0);
-            // pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_S + lane_addr + c * 32, r);
-                tmem_wait_ld();
+            uint32_t r[128];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(r[i]) * p.scale_log2;
-                    if (need_mask) {
-                        const int key = k0 + c * 32 + i;
-                        if (key >= p.T || (p.causal && key > q)) s = -INFINITY;
-                    }
-                    mx = fmaxf(mx, s);
+            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S + lane_addr + c * 32, r + c * 32);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(s_free);
+            const int k0 = j * BKV;
+            if ((k0 + BKV > p.T) || (p.causal && k0 + BKV - 1 > q0)) {        // diagonal or ragged block
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    const int key = k0 + i;
+                    if (key >= p.T || (p.causal && key > q)) r[i] = 0xff800000u;     // -inf
                 }
             }
-            const float m_new = fmaxf(m, mx);
-            const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            // the previous block's P V product must be finished before P is overwritten; fold it in
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+            mx *= p.scale_log2;                            // scale > 0, so the maximum commutes with it
+            // Raise the reference maximum only when it would grow by more than the threshold: the accumulated
+            // output then needs a rescale, which is rare after the first blocks.
+            const bool raise = (j == 0) ? true : (mx > m_ref + RESCALE_THRESHOLD);
+            float alpha = 1.f;
+            if (raise) {
+                alpha = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - mx);
+                m_ref = mx;
+            }
             if (j > 0) {
+                // the previous P V product must be complete before P is overwritten or O is rescaled
                 if (!mbar_wait(o_full, (j - 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_O + lane_addr + c * 32, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < HD; ++i) o[i] *= alpha;
-            // pass 2: probabilities -> shared (bf16), row sum
-            float sum = 0.f;
+                if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_S + lane_addr + c * 32, r);
-                tmem_wait_ld();
-                float pr[32];
+                    for (int c = 0; c < HD / 16; ++c) {       // 16 columns at a time: the score row stays in registers
+                        uint32_t o[16];
+                        tmem_ld16(tmem_O + lane_addr + c * 16, o);
+                        tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(r[i]) * p.scale_log2;
-                    if (need_mask) {
-                        const int key = k0 + c * 32 + i;
-                        if (key >= p.T || (p.causal && key > q)) s = -INFINITY;
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st16(tmem_O + lane_addr + c * 16, o);
                     }
-                    pr[i] = exp2f(s - m_use);
+                    tmem_wait_st();
+                }
+                l *= alpha;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float sum = 0.f;
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {                 // 16 groups of 8 keys = 16-byte chunks of the P row
+                float pr[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    pr[i] = ex2_approx(fmaf(__uint_as_float(r[g * 8 + i]), p.scale_log2, -m_use));
                     sum += pr[i];
                 }
-                uint8_t* atom = sP + (c >> 1) * TILE_BYTES;
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    *reinterpret_cast<uint4*>(atom + swz(row, (c & 1) * 4 + g)) = pack8(pr + g * 8);
+                *reinterpret_cast<uint4*>(sP + (g >> 3) * TILE_BYTES + swz(row, g & 7)) = pack8(pr);
             }
-            l = l * alpha + sum;
-            m = m_new;
+            l += sum;
             tc_fence_before();
             fence_proxy_async();
             mbar_arrive(p_ready);
         }
-        // last block's product
         if (ok && nkv > 0) {
             if (mbar_wait(o_full, (nkv - 1) & 1, abort_flag)) {
                 tc_fence_after();
+                float o[HD];
 #pragma unroll
                 for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_O + lane_addr + c * 32, r);
+                    uint32_t t[32];
+                    tmem_ld32(tmem_O + lane_addr + c * 32, t);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(t[i]);
                 }
                 const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -268,7 +283,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     tma_store_commit();
                     tma_store_wait<0>();
                 }
-                if (q < p.T) p.lse[(long long)bh * p.T + q] = (m == -INFINITY) ? -INFINITY : (m + log2f(l)) / LOG2E;
+                if (q < p.T) p.lse[(long long)bh * p.T + q] = (m_ref == -INFINITY) ? -INFINITY : (m_ref + log2f(l)) / LOG2E;
             }
         }
     }
@@ -278,7 +293,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem_base, FWD_TMEM_COLS); }
 }
 
-
 // ------------------------------------------------------------------------------------------------------
 // Backward
 // ------------------------------------------------------------------------------------------------------
@@ -287,20 +301,23 @@ struct BwdParams {
     float scale, scale_log2;
     const float* lse;
     const float* delta;
-    float* dq_accum;               // fp32 [nb*nh, T, HD], zeroed by the launcher
+    float* dq_accum;               // fp32 [nb*nh, T, HD] accumulator (zeroed by the launcher); unused by the kernel body
+    __nv_bfloat16* dk; __nv_bfloat16* dv;
+    long long sb, sh, st;          // strides of dK / dV
     int* status;
 };
 
-// shared: K 16K | V 16K | Q[2] 32K | dO[2] 32K | P^T 32K | dS^T 32K | barriers
-constexpr int BWD_SMEM = 10 * TILE_BYTES + 128;
-constexpr int BWD_THREADS = 160;
-constexpr int BWD_TMEM_COLS = 512;     // S^T [0,128) dP^T [128,256) dV [256,320) dK [320,384) dQ [384,448)
+// shared: K 16K | V 16K | Q[2] 32K | dO[2] 32K | P 32K | dS[2] 64K | dQ staging (fp32) 32K | barriers   (one CTA per SM)
+constexpr int BWD_SMEM = 14 * TILE_BYTES + 128;
+constexpr int BWD_MMA_WARP = 16;           // warps 0..15 compute, warp 16 issues TMA loads and MMA,
+constexpr int BWD_STORE_WARP = 17;         // warp 17 issues the dQ reduce-stores
+constexpr int BWD_THREADS = 18 * 32;
+constexpr int BWD_TMEM_COLS = 512;     // S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ [384,448)
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
-                   const BwdParams p) {
+                   const __grid_constant__ CUtensorMap tmdQ, const BwdParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     if (smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0 && p.status) atomicExch(p.status, CME_ERR_SHAPE);
@@ -310,16 +327,20 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* sV = sK + TILE_BYTES;
     uint8_t* sQ = sV + TILE_BYTES;             // 2 stages
     uint8_t* sdO = sQ + 2 * TILE_BYTES;        // 2 stages
-    uint8_t* sPt = sdO + 2 * TILE_BYTES;       // [2 query atoms][128 key rows][128 B]
-    uint8_t* sdSt = sPt + 2 * TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sdSt + 2 * TILE_BYTES);
+    uint8_t* sP = sdO + 2 * TILE_BYTES;        // [2 key atoms][128 query rows][128 B]; free again once dV's MMAs ran
+    uint8_t* sdS = sP + 2 * TILE_BYTES;        // 2 buffers, same layout
+    uint8_t* sdQ = sdS + 4 * TILE_BYTES;       // fp32 dQ staging: [2 column atoms][128 query rows][128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sdQ + 2 * TILE_BYTES);
     uint64_t* kv_full = bars;
     uint64_t* q_full = bars + 1;               // [2]
     uint64_t* q_empty = bars + 3;              // [2]
-    uint64_t* s_full = bars + 5;
-    uint64_t* p_ready = bars + 6;              // 128 arrivals
-    uint64_t* dq_full = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* s_full = bars + 5;               // S and dP of a query block are in TMEM
+    uint64_t* p_ready = bars + 6;              // P, dS written; S, dP, previous dQ consumed (512 arrivals)
+    uint64_t* dq_full = bars + 7;              // dV, dK accumulated and dQ of a query block complete
+    uint64_t* p_free = bars + 8;               // dV's MMAs of a block have read P
+    uint64_t* dqs_full = bars + 9;             // dQ staging written (512 arrivals)
+    uint64_t* dqs_free = bars + 10;            // dQ staging read by the reduce-store
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -334,23 +355,26 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_init(kv_full, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
         mbar_init(s_full, 1);
-        mbar_init(p_ready, 128);
+        mbar_init(p_ready, 512);
         mbar_init(dq_full, 1);
+        mbar_init(p_free, 1);
+        mbar_init(dqs_full, 512);
+        mbar_init(dqs_free, 1);
         fence_barrier_init();
     }
-    if (warp == 4) { tmem_alloc(tmem_slot, BWD_TMEM_COLS); tmem_relinquish(); }
+    if (warp == BWD_MMA_WARP) { tmem_alloc(tmem_slot, BWD_TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_St = tmem_base, tmem_dPt = tmem_base + 128, tmem_dV = tmem_base + 256,
+    const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256,
                    tmem_dK = tmem_base + 320, tmem_dQ = tmem_base + 384;
 
-    if (warp == 4) {
+    if (warp == BWD_MMA_WARP) {
         if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc(1, false, false, 128, 128);    // K Q^T, V dO^T
-            constexpr uint32_t idesc_kv = make_idesc(1, false, true, 128, HD);     // P^T dO, dS^T Q
-            constexpr uint32_t idesc_dq = make_idesc(1, true, true, 128, HD);      // dS K (A read transposed)
+            constexpr uint32_t idesc_s = make_idesc(1, false, false, 128, 128);    // Q K^T, dO V^T
+            constexpr uint32_t idesc_t = make_idesc(1, true, true, 128, HD);       // P^T dO, dS^T Q (A read transposed)
+            constexpr uint32_t idesc_q = make_idesc(1, false, true, 128, HD);      // dS K
             bool ok = true;
             mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
             tma_load_4d(sK, &tmK, kv_full, 0, k0, h, b);
@@ -361,18 +385,24 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tma_load_4d(sQ + st * TILE_BYTES, &tmQ, &q_full[st], 0, (i_begin + it) * BQ, h, b);
                 tma_load_4d(sdO + st * TILE_BYTES, &tmdO, &q_full[st], 0, (i_begin + it) * BQ, h, b);
             };
+            // descriptors are encoded once; per MMA only a byte offset is added
+            const uint64_t kK = make_smem_desc(smem_u32(sK), 0, 1024), vK = make_smem_desc(smem_u32(sV), 0, 1024);
+            const uint64_t kMN = make_smem_desc(smem_u32(sK), TILE_BYTES, 1024);
+            // stage / buffer 1 of each ring lies a fixed distance after stage 0, so its descriptor is base + offset
+            const uint64_t qK0 = make_smem_desc(smem_u32(sQ), 0, 1024), oK0 = make_smem_desc(smem_u32(sdO), 0, 1024);
+            const uint64_t qMN0 = make_smem_desc(smem_u32(sQ), TILE_BYTES, 1024);
+            const uint64_t oMN0 = make_smem_desc(smem_u32(sdO), TILE_BYTES, 1024);
+            const uint64_t pMN0 = make_smem_desc(smem_u32(sP), TILE_BYTES, 1024);
+            const uint64_t sMN0 = make_smem_desc(smem_u32(sdS), TILE_BYTES, 1024);
+            const uint64_t sK0 = make_smem_desc(smem_u32(sdS), 0, 1024);
             auto issue_s = [&](int it) {
-                const int st = it & 1;
-                const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-                const uint32_t qb = smem_u32(sQ + st * TILE_BYTES), ob = smem_u32(sdO + st * TILE_BYTES);
+                const uint64_t qd = desc_add(qK0, (it & 1) * TILE_BYTES), od = desc_add(oK0, (it & 1) * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    mma_f16_ss(tmem_St, make_smem_desc(ka + k * 32, 0, 1024), make_smem_desc(qb + k * 32, 0, 1024),
-                               idesc_s, k > 0);
+                    mma_f16_ss(tmem_S, desc_add(qd, k * 32), desc_add(kK, k * 32), idesc_s, k > 0);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    mma_f16_ss(tmem_dPt, make_smem_desc(va + k * 32, 0, 1024), make_smem_desc(ob + k * 32, 0, 1024),
-                               idesc_s, k > 0);
+                    mma_f16_ss(tmem_dP, desc_add(od, k * 32), desc_add(vK, k * 32), idesc_s, k > 0);
                 mma_commit(s_full);
             };
             if (n_it > 0) load_q(0);
@@ -386,27 +416,28 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 const int st = it & 1;
                 if (!mbar_wait(p_ready, it & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t pt = smem_u32(sPt), dst = smem_u32(sdSt), ka = smem_u32(sK);
-                const uint32_t qb = smem_u32(sQ + st * TILE_BYTES), ob = smem_u32(sdO + st * TILE_BYTES);
-#pragma unroll
-                for (int k = 0; k < BQ / 16; ++k) {     // reduction over the 128 queries of this block
-                    const uint32_t a_off = (k >> 2) * TILE_BYTES + (k & 3) * 32;
-                    mma_f16_ss(tmem_dV, make_smem_desc(pt + a_off, 0, 1024),
-                               make_smem_desc(ob + k * 2048, TILE_BYTES, 1024), idesc_kv, (it > 0 || k > 0));
-                    mma_f16_ss(tmem_dK, make_smem_desc(dst + a_off, 0, 1024),
-                               make_smem_desc(qb + k * 2048, TILE_BYTES, 1024), idesc_kv, (it > 0 || k > 0));
-                }
-#pragma unroll
-                for (int k = 0; k < BKV / 16; ++k)      // reduction over the 128 keys of this CTA
-                    mma_f16_ss(tmem_dQ, make_smem_desc(dst + k * 2048, TILE_BYTES, 1024),
-                               make_smem_desc(ka + k * 2048, TILE_BYTES, 1024), idesc_dq, k > 0);
-                mma_commit(dq_full);
-                mma_commit(&q_empty[st]);
-                if (it + 1 < n_it) {
+                if (it + 1 < n_it) {       // next block's scores first: the softmax warps can start on them at once
                     if (!mbar_wait(&q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     issue_s(it + 1);
                 }
+                const uint64_t pd = pMN0, sd = desc_add(sMN0, st * 2 * TILE_BYTES),
+                               sk = desc_add(sK0, st * 2 * TILE_BYTES), qd = desc_add(qMN0, st * TILE_BYTES),
+                               od = desc_add(oMN0, st * TILE_BYTES);
+                const uint32_t acc = it > 0;
+#pragma unroll
+                for (int k = 0; k < BQ / 16; ++k)        // dV first: P is single-buffered and is released right after
+                    mma_f16_ss(tmem_dV, desc_add(pd, k * 2048), desc_add(od, k * 2048), idesc_t, acc | (k > 0));
+                mma_commit(p_free);
+#pragma unroll
+                for (int k = 0; k < BQ / 16; ++k)        // reduction over the 128 queries of this block
+                    mma_f16_ss(tmem_dK, desc_add(sd, k * 2048), desc_add(qd, k * 2048), idesc_t, acc | (k > 0));
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k)       // reduction over the 128 keys of this CTA
+                    mma_f16_ss(tmem_dQ, desc_add(sk, (k >> 2) * TILE_BYTES + (k & 3) * 32), desc_add(kMN, k * 2048),
+                               idesc_q, k > 0);
+                mma_commit(dq_full);
+                mma_commit(&q_empty[st]);
                 if (it + 2 < n_it) {
                     if (!mbar_wait(&q_empty[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
                     load_q(it + 2);
@@ -414,131 +445,138 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             if (!ok) for (int i = 0; i < 2000; ++i) __nanosleep(500);
         }
+    } else if (warp == BWD_STORE_WARP) {
+        // ---------------- dQ reduce-store issuer: adds each staged 128 x 64 fp32 tile into the global accumulator
+        if (lane == 0) {
+            for (int f = 0; f < n_it; ++f) {
+                if (!mbar_wait(dqs_full, f & 1, abort_flag)) break;
+                const int q0 = (i_begin + f) * BQ;
+                tma_reduce_add_3d(&tmdQ, sdQ, 0, q0, bh);
+                tma_reduce_add_3d(&tmdQ, sdQ + TILE_BYTES, 32, q0, bh);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+                mbar_arrive(dqs_free);
+            }
+            tma_store_wait<0>();
+        }
     } else {
-        const int row = warp * 32 + lane;               // key row for S^T / dP^T, query row for dQ
-        const int key = k0 + row;
-        const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+        // ---------------- gradient warps: 16 warps; warp w owns TMEM lanes 32*(w&3).. (query rows) and the
+        // 32-column group (w>>2) of every S / dP tile, so each scheduler has four warps to hide latency with ----
+        const int quarter = warp & 3, cg = warp >> 2;
+        const int row = quarter * 32 + lane;            // TMEM lane: query row for S, dP, dQ; key row for dV, dK
+        const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
         bool ok = true;
+        // dQ of a finished query block: this warp's 16 columns go to the fp32 staging tile (swizzled for TMA); the
+        // store warp then adds the tile into the global accumulator with one bulk reduce per 32-column half
+        auto flush_dq = [&](int f) -> bool {
+            if (!mbar_wait(dq_full, f & 1, abort_flag)) return false;
+            tc_fence_after();
+            uint32_t t[16];
+            tmem_ld16(tmem_dQ + lane_addr + cg * 16, t);
+            tmem_wait_ld();
+            if (f > 0 && !mbar_wait(dqs_free, (f - 1) & 1, abort_flag)) return false;
+            uint8_t* atom = sdQ + (cg >> 1) * TILE_BYTES;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+                *reinterpret_cast<uint4*>(atom + swz(row, (cg & 1) * 4 + g)) =
+                    make_uint4(t[4 * g], t[4 * g + 1], t[4 * g + 2], t[4 * g + 3]);
+            fence_proxy_async();
+            mbar_arrive(dqs_full);
+            return true;
+        };
         for (int it = 0; it < n_it && ok; ++it) {
             const int qi0 = (i_begin + it) * BQ;
-            // per-query statistics are read straight from global memory: every lane of a warp asks for the
-            // same address, so each read is one broadcast transaction (no block-wide barrier to get stuck in)
-            const float* lse_row = p.lse + (long long)bh * p.T;
-            const float* dl_row = p.delta + (long long)bh * p.T;
+            const int q = qi0 + row;
+            const int qc = min(q, p.T - 1);
+            const float lse2 = p.lse[(long long)bh * p.T + qc] * LOG2E;
+            const float dl = p.delta[(long long)bh * p.T + qc];
+            uint8_t* bufP = sP;
+            uint8_t* bufS = sdS + (it & 1) * 2 * TILE_BYTES;
             if (!mbar_wait(s_full, it & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const bool need_mask = (qi0 + BQ > p.T) || (k0 + BKV > p.T) || (p.causal && qi0 < k0 + BKV);
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t rs[32], rd[32];
-                tmem_ld32(tmem_St + lane_addr + c * 32, rs);
-                tmem_ld32(tmem_dPt + lane_addr + c * 32, rd);
-                tmem_wait_ld();
-                float pr[32], ds[32];
+            uint32_t rs[32], rd[32];
+            tmem_ld32(tmem_S + lane_addr + cg * 32, rs);
+            tmem_ld32(tmem_dP + lane_addr + cg * 32, rd);
+            tmem_wait_ld();
+            if (it > 0 && !mbar_wait(p_free, (it - 1) & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int qq = c * 32 + i;
-                    const int qc = min(qi0 + qq, p.T - 1);
-                    float pv = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - __ldg(lse_row + qc) * LOG2E);
+            for (int g = 0; g < 4; ++g) {
+                float pr[8], ds[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float pv = ex2_approx(fmaf(__uint_as_float(rs[g * 8 + i]), p.scale_log2, -lse2));
                     if (need_mask) {
-                        const int q = qi0 + qq;
+                        const int key = k0 + cg * 32 + g * 8 + i;
                         if (q >= p.T || key >= p.T || (p.causal && key > q)) pv = 0.f;
                     }
                     pr[i] = pv;
-                    ds[i] = pv * (__uint_as_float(rd[i]) - __ldg(dl_row + qc));
+                    ds[i] = pv * (__uint_as_float(rd[g * 8 + i]) - dl);
                 }
-                const uint32_t atom = (c >> 1) * TILE_BYTES;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const uint32_t off = atom + swz(row, (c & 1) * 4 + g);
-                    *reinterpret_cast<uint4*>(sPt + off) = pack8(pr + g * 8);
-                    *reinterpret_cast<uint4*>(sdSt + off) = pack8(ds + g * 8);
-                }
+                const uint32_t off = (cg >> 1) * TILE_BYTES + swz(row, (cg & 1) * 4 + g);
+                *reinterpret_cast<uint4*>(bufP + off) = pack8(pr);
+                *reinterpret_cast<uint4*>(bufS + off) = pack8(ds);
             }
+            // the previous block's dQ is read here, after this block's arithmetic, so that its MMAs had the whole
+            // time of that arithmetic to finish
+            if (it > 0 && !flush_dq(it - 1)) { ok = false; break; }
             tc_fence_before();
             fence_proxy_async();
             mbar_arrive(p_ready);
-            // dQ partial of this query block: add into the fp32 accumulator
-            if (!mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            {
-                const int q = qi0 + row;
-                float* dst = p.dq_accum + ((long long)bh * p.T + q) * HD;
-#pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_dQ + lane_addr + c * 32, r);
-                    tmem_wait_ld();
-                    if (q < p.T) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            red_add_v4(dst + c * 32 + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]),
-                                       __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-                    }
-                }
-            }
-            tc_fence_before();
         }
-        // dK, dV of this key block (all MMAs are complete: the last dq_full wait covered them)
+        if (ok && n_it > 0) ok = flush_dq(n_it - 1);
+        // dK, dV of this key block (all MMAs are complete: the last dq_full wait covered them); this warp stores its
+        // 16 columns (32 bytes = one full sector per row) straight from registers
         if (ok) {
-            float v[HD];
-            uint8_t* stage = sPt + warp * 8192;           // P^T / dS^T are free now
-            if (n_it > 0) {
+            const int key = k0 + row;
+            const long long off = (long long)b * p.sb + (long long)h * p.sh + (long long)key * p.st + cg * 16;
+            uint32_t t[16];
+            float v[16];
+            if (n_it > 0) { tmem_ld16(tmem_dV + lane_addr + cg * 16, t); tmem_wait_ld(); }
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_dV + lane_addr + c * 32, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[c * 32 + i] = __uint_as_float(r[i]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < HD; ++i) v[i] = 0.f;
+            for (int i = 0; i < 16; ++i) v[i] = n_it > 0 ? __uint_as_float(t[i]) : 0.f;
+            if (key < p.T) {
+                *reinterpret_cast<uint4*>(p.dv + off) = pack8(v);
+                *reinterpret_cast<uint4*>(p.dv + off + 8) = pack8(v + 8);
             }
+            if (n_it > 0) { tmem_ld16(tmem_dK + lane_addr + cg * 16, t); tmem_wait_ld(); }
 #pragma unroll
-            for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(stage + swz(lane, g)) = pack8(v + g * 8);
-            if (n_it > 0) {
-#pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_dK + lane_addr + c * 32, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[c * 32 + i] = __uint_as_float(r[i]) * p.scale;
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(stage + 4096 + swz(lane, g)) = pack8(v + g * 8);
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-                tma_store_4d(&tmdV, stage, 0, k0 + warp * 32, h, b);
-                tma_store_4d(&tmdK, stage + 4096, 0, k0 + warp * 32, h, b);
-                tma_store_commit();
-                tma_store_wait<0>();
+            for (int i = 0; i < 16; ++i) v[i] = n_it > 0 ? __uint_as_float(t[i]) * p.scale : 0.f;
+            if (key < p.T) {
+                *reinterpret_cast<uint4*>(p.dk + off) = pack8(v);
+                *reinterpret_cast<uint4*>(p.dk + off + 8) = pack8(v + 8);
             }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, CME_ERR_TIMEOUT);
-    if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem_base, BWD_TMEM_COLS); }
+    if (warp == BWD_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, BWD_TMEM_COLS); }
 }
 
-// dq[b, h, t, :] = dq_accum[bh, t, :] * scale  (bf16, strided destination)
+// dq[b, h, t, :] = scale * sum over key blocks of the partial dQ slices (bf16, strided destination).
+// Causal: only key blocks at or before the query's block contributed (and were written).
 __global__ void dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int T, int nh,
-                                  long long sb, long long sh, long long st, float scale, long long rows) {
+                                  long long sb, long long sh, long long st, float scale, long long rows, int nkb,
+                                  int causal) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per 8 elements
     if (i >= rows * (HD / 8)) return;
     const long long r = i / (HD / 8);
     const int c = (int)(i % (HD / 8)) * 8;
     const int bh = (int)(r / T), t = (int)(r % T);
+    const int last = causal ? min(nkb - 1, t / BKV) : nkb - 1;
     float f[8];
-    const float4 a = *reinterpret_cast<const float4*>(acc + r * HD + c);
-    const float4 b2 = *reinterpret_cast<const float4*>(acc + r * HD + c + 4);
-    f[0] = a.x * scale; f[1] = a.y * scale; f[2] = a.z * scale; f[3] = a.w * scale;
-    f[4] = b2.x * scale; f[5] = b2.y * scale; f[6] = b2.z * scale; f[7] = b2.w * scale;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = 0.f;
+    for (int kb = 0; kb <= last; ++kb) {
+        const float* src = acc + ((long long)kb * rows + r) * HD + c;
+        const float4 a = *reinterpret_cast<const float4*>(src);
+        const float4 b2 = *reinterpret_cast<const float4*>(src + 4);
+        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+        f[4] += b2.x; f[5] += b2.y; f[6] += b2.z; f[7] += b2.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= scale;
     *reinterpret_cast<uint4*>(dq + (long long)(bh / nh) * sb + (long long)(bh % nh) * sh + (long long)t * st + c) = pack8(f);
 }
 
@@ -576,6 +614,21 @@ int make_map4(CUtensorMap* out, const void* base, int T, int nh, int nb, long lo
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CME_REQUIRE(r == CUDA_SUCCESS, CME_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed (%d) T=%d nh=%d nb=%d st=%lld",
                 (int)r, T, nh, nb, st);
+    return CME_OK;
+}
+
+// fp32 map over the dQ accumulator [nbh, T, 64]: box (32 columns = 128 bytes, 128 rows, 1), 128-byte swizzle.
+int make_map_dq(CUtensorMap* out, const void* base, int T, int nbh) {
+    EncodeTiledFn enc = encoder();
+    CME_REQUIRE(enc != nullptr, CME_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)T, (cuuint64_t)nbh};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 4, (cuuint64_t)T * HD * 4};
+    cuuint32_t box[3] = {32, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CME_REQUIRE(r == CUDA_SUCCESS, CME_ERR_CUDA, "attention: dQ tensor map failed (%d)", (int)r);
     return CME_OK;
 }
 
@@ -635,26 +688,26 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
     int rc;
     if ((rc = attention_delta_launch(a, st))) return rc;
     const long long rows = (long long)a->nb * a->nh * a->T;
-    CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
-    CUtensorMap mq, mk, mv, mdo, mdk, mdv;
+    CUtensorMap mq, mk, mv, mdo, mdq;
     if ((rc = make_map4(&mq, a->q, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mk, a->k, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mv, a->v, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mdo, a->d_o, a->T, a->nh, a->nb, a->ost, a->osh, a->osb, 128))) return rc;
-    if ((rc = make_map4(&mdk, a->dk, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 32))) return rc;
-    if ((rc = make_map4(&mdv, a->dv, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 32))) return rc;
+    if ((rc = make_map_dq(&mdq, a->dq_accum, a->T, a->nb * a->nh))) return rc;
+    CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
     static bool attr = false;
     if (!attr) {
         CME_CUDA(cudaFuncSetAttribute(attn_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
         attr = true;
     }
-    BwdParams p{a->T, a->nh, a->causal, a->scale, a->scale * LOG2E, a->lse, a->delta, a->dq_accum, g_attn_status};
+    BwdParams p{a->T, a->nh, a->causal, a->scale, a->scale * LOG2E, a->lse, a->delta, a->dq_accum,
+                (__nv_bfloat16*)a->dk, (__nv_bfloat16*)a->dv, a->sb, a->sh, a->st, g_attn_status};
     dim3 grid(cme_cdiv(a->T, BKV), a->nb * a->nh);
-    attn_bwd_tc_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+    attn_bwd_tc_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, mdo, mdq, p);
     CME_LAUNCH_CHECK();
     const long long nthreads = rows * (HD / 8);
     dq_convert_kernel<<<cme_cdiv(nthreads, 256), 256, 0, st>>>(a->dq_accum, (__nv_bfloat16*)a->dq, a->T, a->nh, a->sb,
-                                                              a->sh, a->st, a->scale, rows);
+                                                              a->sh, a->st, a->scale, rows, 1, 0);
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
