@@ -220,17 +220,46 @@ __global__ void pos_bwd_kernel(const T* __restrict__ dout, T* __restrict__ dpos,
     for (int b = 0; b < B; ++b) s += to_f32<T>(dout[(long long)b * T_ * D + i]);
     dpos[i] = from_f32<T>(s);
 }
-// Small vocabularies: one block per vocabulary row scans the token list and sums matching rows in a fixed
-// order (deterministic, no atomics).  dtok[v, :] (+)= sum_{bt : tokens[bt] == v} dout[bt, :]
+// Small vocabularies: one block (8 warps) per vocabulary row.  Each warp scans its own contiguous eighth of the
+// token list with ballots and sums the matching rows of dout in token order; the eight partial rows are then added
+// in warp order.  Deterministic (no atomics) and the scan is 32 tokens per instruction.
+//     dtok[v, :] (+)= sum_{bt : tokens[bt] == v} dout[bt, :]
 template <typename T>
-__global__ void tok_bwd_scan_kernel(const int* __restrict__ tokens, const T* __restrict__ dout, T* __restrict__ dtok,
-                                    int BT, int D, int accumulate) {
-    const int v = blockIdx.x;
+__global__ void __launch_bounds__(256)
+tok_bwd_scan_kernel(const int* __restrict__ tokens, const T* __restrict__ dout, T* __restrict__ dtok, int BT, int D,
+                    int accumulate) {
+    extern __shared__ float part[];              // [8][D]
+    const int v = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per = (BT + 7) / 8, t0 = warp * per, t1 = min(BT, t0 + per);
+    for (int c0 = 0; c0 < D; c0 += 32 * 8) {     // 8 columns per lane per pass
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int base = t0; base < t1; base += 32) {
+            const int bt = base + lane;
+            unsigned hit = __ballot_sync(0xffffffffu, bt < t1 && tokens[bt] == v);
+            while (hit) {
+                const int src = base + __ffs(hit) - 1;
+                hit &= hit - 1;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int c = c0 + lane + 32 * j;
+                    if (c < D) acc[j] += to_f32<T>(dout[(long long)src * D + c]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + lane + 32 * j;
+            if (c < D) part[warp * D + c] = acc[j];
+        }
+    }
+    __syncthreads();
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float s = accumulate ? to_f32<T>(dtok[(long long)v * D + c]) : 0.f;
-        for (int bt = 0; bt < BT; ++bt)
-            if (tokens[bt] == v) s += to_f32<T>(dout[(long long)bt * D + c]);
-        dtok[(long long)v * D + c] = from_f32<T>(s);
+        float s2 = accumulate ? to_f32<T>(dtok[(long long)v * D + c]) : 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s2 += part[w * D + c];
+        dtok[(long long)v * D + c] = from_f32<T>(s2);
     }
 }
 // Large vocabularies: one warp per token, atomic adds into the (already initialised) table gradient.
@@ -417,16 +446,17 @@ CME_API int cme_embedding_bwd(int dtype, const int* tokens, const void* dout, vo
     cudaStream_t st = (cudaStream_t)stream;
     CME_REQUIRE(BT > 0 && D > 0 && T > 0 && BT % T == 0, CME_ERR_SHAPE, "embedding backward: bad shape");
     const size_t esz = dtype == CME_BF16 ? 2 : 4;
-    const bool scan = (long long)V * BT <= (1ll << 22);
+    const bool scan = (long long)V * BT <= (1ll << 22) && D <= 1536;
     if (dtok) {
         if (scan) {
-            const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : 64);
+            const size_t sm = (size_t)8 * D * sizeof(float);
+            CME_REQUIRE(sm <= 48 * 1024, CME_ERR_LIMIT, "embedding backward: hidden size %d too large for the scan path", D);
             if (dtype == CME_BF16)
-                tok_bwd_scan_kernel<__nv_bfloat16><<<V, threads, 0, st>>>(tokens, (const __nv_bfloat16*)dout,
-                                                                          (__nv_bfloat16*)dtok, BT, D, accumulate);
+                tok_bwd_scan_kernel<__nv_bfloat16><<<V, 256, sm, st>>>(tokens, (const __nv_bfloat16*)dout,
+                                                                       (__nv_bfloat16*)dtok, BT, D, accumulate);
             else
-                tok_bwd_scan_kernel<float><<<V, threads, 0, st>>>(tokens, (const float*)dout, (float*)dtok, BT, D,
-                                                                  accumulate);
+                tok_bwd_scan_kernel<float><<<V, 256, sm, st>>>(tokens, (const float*)dout, (float*)dtok, BT, D,
+                                                               accumulate);
         } else {
             if (!accumulate) CME_CUDA(cudaMemsetAsync(dtok, 0, (size_t)V * D * esz, st));
             if (dtype == CME_BF16)
