@@ -343,10 +343,11 @@ class CmeAttn(ctypes.Structure):
         ("lse", ctypes.c_void_p),
         ("d_o", ctypes.c_void_p), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
         ("delta", ctypes.c_void_p), ("dq_accum", ctypes.c_void_p),
+        ("ws", ctypes.c_void_p), ("ws_bytes", ctypes.c_longlong),
     ]
 
 
-_BACKENDS = {"auto": 0, "tc": 1, "simt": 2}
+_BACKENDS = {"auto": 0, "tc": 1, "simt": 2, "gemm": 3}
 
 
 def _attn_desc(q, B, H, T, layout, causal):
@@ -359,6 +360,14 @@ def _attn_desc(q, B, H, T, layout, causal):
     else:
         a.nb, a.nh, a.sb, a.sh, a.st = B, H, T * D, HD, D
     a.osb, a.osh, a.ost = a.sb, a.sh, a.st
+    if layout == "flat" and T <= 512 and q.dtype == torch.bfloat16:      # scratch of the batched-GEMM path
+        l = lib()
+        l.cme_attention_gemm_ws_bytes.restype = ctypes.c_longlong
+        nbytes = int(l.cme_attention_gemm_ws_bytes(B * H, T))
+        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=q.device)
+        a._ws_keepalive = ws
+        a.ws = (ws.data_ptr() + 255) // 256 * 256
+        a.ws_bytes = nbytes
     return a
 
 

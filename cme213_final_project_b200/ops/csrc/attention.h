@@ -25,10 +25,15 @@ struct CmeAttn {
     const void* d_o; void* dq; void* dk; void* dv;
     float* delta;                // [nb*nh, T] scratch: rowsum(dO * O)
     float* dq_accum;             // fp32 scratch [nb*nh*T*HD] for the tcgen05 backward (may be null)
+    void* ws; long long ws_bytes;    // scratch of attention_gemm_ws_bytes() for the batched-GEMM path (may be null)
 };
 
 int attention_simt_fwd(const CmeAttn* a, cudaStream_t st);
 int attention_simt_bwd(const CmeAttn* a, cudaStream_t st);
+int attention_gemm_supported(const CmeAttn* a);
+int attention_gemm_fwd(const CmeAttn* a, cudaStream_t st);
+int attention_gemm_bwd(const CmeAttn* a, cudaStream_t st);
+long long attention_gemm_ws_bytes(int nb, int T);
 int attention_tc_supported(const CmeAttn* a);
 int attention_tc_fwd(const CmeAttn* a, cudaStream_t st);
 int attention_tc_bwd(const CmeAttn* a, cudaStream_t st);

@@ -285,16 +285,22 @@ int attention_simt_bwd(const CmeAttn* a, cudaStream_t st) {
     return a->dtype == CME_BF16 ? bwd_t<__nv_bfloat16>(a, st) : bwd_t<float>(a, st);
 }
 
-// backend: 0 auto (tensor-core kernel when it takes the shape), 1 tensor-core only, 2 SIMT only
+// backend: 0 auto (fused tensor-core kernel, else batched-GEMM path, else SIMT), 1 fused tensor-core only,
+//          2 SIMT only, 3 batched-GEMM path only
 CME_API int cme_attention_fwd(const CmeAttn* a, int backend, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
-    if (backend != 2 && attention_tc_supported(a)) return attention_tc_fwd(a, st);
+    if ((backend == 0 || backend == 1) && attention_tc_supported(a)) return attention_tc_fwd(a, st);
     CME_REQUIRE(backend != 1, CME_ERR_SHAPE, "attention shape not supported by the tensor-core kernel");
+    if ((backend == 0 || backend == 3) && attention_gemm_supported(a)) return attention_gemm_fwd(a, st);
+    CME_REQUIRE(backend != 3, CME_ERR_SHAPE, "attention shape not supported by the batched-GEMM path");
     return attention_simt_fwd(a, st);
 }
 CME_API int cme_attention_bwd(const CmeAttn* a, int backend, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
-    if (backend != 2 && attention_tc_supported(a)) return attention_tc_bwd(a, st);
+    if ((backend == 0 || backend == 1) && attention_tc_supported(a)) return attention_tc_bwd(a, st);
     CME_REQUIRE(backend != 1, CME_ERR_SHAPE, "attention shape not supported by the tensor-core kernel");
+    if ((backend == 0 || backend == 3) && attention_gemm_supported(a)) return attention_gemm_bwd(a, st);
+    CME_REQUIRE(backend != 3, CME_ERR_SHAPE, "attention shape not supported by the batched-GEMM path");
     return attention_simt_bwd(a, st);
 }
+CME_API long long cme_attention_gemm_ws_bytes(int nb, int T) { return attention_gemm_ws_bytes(nb, T); }

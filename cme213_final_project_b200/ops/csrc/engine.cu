@@ -76,6 +76,7 @@ struct Engine {
     // backward temporaries
     char *dxa, *dxb, *dff, *dln, *dqkv, *dattn;
     float *delta, *dq_accum, *ln_scratch, *col_scratch;
+    void* attn_ws; long long attn_ws_bytes;
     void* gemm_ws; long long gemm_ws_bytes;
 
     char* P(long long off) const { return params + off * (long long)es; }
@@ -121,6 +122,8 @@ size_t carve(Engine& e, char* base) {
     e.dattn = take(BT * D * es);
     e.delta = (float*)take((size_t)e.BH * d.T * 4);
     e.dq_accum = (float*)take(BT * D * 4);
+    e.attn_ws_bytes = (d.head_flat && d.T <= 512) ? attention_gemm_ws_bytes(e.BH, d.T) : 0;
+    e.attn_ws = e.attn_ws_bytes ? take((size_t)e.attn_ws_bytes) : nullptr;
     const size_t widest = FF > D ? FF : D;
     e.ln_scratch = (float*)take((size_t)cme_layernorm_bwd_blocks((int)BT) * 2 * D * 4);
     e.col_scratch = (float*)take((size_t)(cme_colsum_splits((int)BT, (int)D) + cme_colsum_splits((int)BT, (int)FF)) *
@@ -167,6 +170,7 @@ void fill_attn(const Engine& e, int l, CmeAttn& a) {
     if (d.head_flat) { a.osb = (long long)d.T * HD; a.osh = 0; a.ost = HD; }
     else { a.osb = (long long)d.T * D; a.osh = HD; a.ost = D; }
     a.lse = e.la[l].lse; a.delta = e.delta; a.dq_accum = e.dq_accum;
+    a.ws = e.attn_ws; a.ws_bytes = e.attn_ws_bytes;
 }
 
 #define TRY(expr) do { int rc__ = (expr); if (rc__) return rc__; } while (0)

@@ -87,3 +87,20 @@ def test_fused_qkv_row_pitch():
     ops._check(ops.lib().cme_attention_fwd(ctypes.byref(a), 1, ops._stream()))
     torch.cuda.synchronize()
     assert (out.float() - ref.float()).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("H,HD", [(4, 32), (4, 64), (4, 128)])
+def test_batched_gemm_path_on_the_reference_shapes(H, HD):
+    """Flat head view, T = 64: QK^T / softmax / PV as batched tcgen05 GEMMs, against the SIMT kernels."""
+    from cme213_final_project_b200 import ops
+    B, T, D = 8, 64, H * HD
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, k, v, do = (torch.randn(B * T, D, generator=g, device="cuda").to(torch.bfloat16) for _ in range(4))
+    o_ref, lse_ref = ops.attention_fwd(q, k, v, B, H, T, "flat", False, backend="simt")
+    o, lse = ops.attention_fwd(q, k, v, B, H, T, "flat", False, backend="gemm")
+    assert (o.float() - o_ref.float()).abs().max().item() < 3e-2
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+    ref = ops.attention_bwd(q, k, v, o_ref, lse_ref, do, B, H, T, "flat", False, backend="simt")
+    got = ops.attention_bwd(q, k, v, o, lse, do, B, H, T, "flat", False, backend="gemm")
+    for a, b in zip(got, ref):
+        assert (a.float() - b.float()).abs().max().item() < 4e-2 * max(1.0, b.float().abs().max().item())
