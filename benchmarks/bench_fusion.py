@@ -1,0 +1,95 @@
+"""Fused vs unfused pipelines, device-timed: bias + activation, residual + LayerNorm forward, LayerNorm backward +
+residual-gradient add, activation backward + bias gradient, plus achieved DRAM bandwidth against the measured peak.
+
+Role of the reference's fusion A/B benchmark (FINAL_CLEAN_CODE_/tests/test_fusion_benchmark.cu:54-296 and
+profile_fusion_kernels.cu; numbers in FINAL_CLEAN_CODE/results/final_clean_main_table.csv:57-65 and
+roofline_fusion.csv).  Inputs are sized above the 126 MB L2 by default so the DRAM figures mean something;
+`--reference-shapes` uses the reference's 2048 x {128, 512} matrices instead (L2-resident on a B200).
+
+    python benchmarks/bench_fusion.py [--rows 65536 --cols 3072] [--reference-shapes] [--json out.json]
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from cme213_final_project_b200 import ops                                   # noqa: E402
+from cme213_final_project_b200.utils.timers import L2Flusher, time_kernel   # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--cols", type=int, default=3072)
+    ap.add_argument("--ln-cols", type=int, default=768)
+    ap.add_argument("--reference-shapes", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json")
+    a = ap.parse_args()
+    rows, cols, lnc = (2048, 512, 128) if a.reference_shapes else (a.rows, a.cols, a.ln_cols)
+    peak = 6536.4
+    pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak = json.load(open(pk)).get("hbm_gbs", peak)
+    fl = L2Flusher("cuda")
+    bf = torch.bfloat16
+    out = []
+
+    def rec(name, fused, unfused, nbytes):
+        f, u = statistics.median(fused), statistics.median(unfused)
+        r = {"op": name, "fused_ms": f, "unfused_ms": u, "speedup": u / f, "fused_gbs": nbytes / f / 1e6,
+             "frac_of_measured_hbm": nbytes / f / 1e6 / peak}
+        out.append(r)
+        print(json.dumps(r), flush=True)
+
+    x, res = torch.randn(rows, cols, device="cuda").to(bf), torch.randn(rows, cols, device="cuda").to(bf)
+    bias = torch.randn(cols, device="cuda").to(bf)
+    fused = time_kernel(lambda: ops.bias_act_residual(x, bias, "relu"), 3, a.iters, fl)
+
+    def unf():
+        t, _ = ops.bias_act_residual(x, bias, None)
+        ops.bias_act_residual(t, None, "relu")
+    rec("bias+relu", fused, time_kernel(unf, 3, a.iters, fl), 2 * x.numel() * 2)
+    fused = time_kernel(lambda: ops.bias_act_residual(x, bias, "gelu", res), 3, a.iters, fl)
+
+    def unf2():
+        t, _ = ops.bias_act_residual(x, bias, None)
+        t, _ = ops.bias_act_residual(t, None, "gelu")
+        ops.add(t, res)
+    rec("bias+gelu+residual", fused, time_kernel(unf2, 3, a.iters, fl), 3 * x.numel() * 2)
+    dout = torch.randn(rows, cols, device="cuda").to(bf)
+    fused = time_kernel(lambda: ops.dact_colsum(dout, x, "relu"), 3, a.iters, fl)
+
+    def unf3():
+        g = ops.relu_bwd(x, dout)
+        ops.dact_colsum(g)
+    rec("relu-bwd+bias-bwd", fused, time_kernel(unf3, 3, a.iters, fl), 3 * x.numel() * 2)
+
+    h, r2 = torch.randn(rows, lnc, device="cuda").to(bf), torch.randn(rows, lnc, device="cuda").to(bf)
+    g, b = torch.ones(lnc, device="cuda").to(bf), torch.zeros(lnc, device="cuda").to(bf)
+    fused = time_kernel(lambda: ops.layernorm_fwd(h, g, b, 1e-5, residual=r2, save_sum=True), 3, a.iters, fl)
+
+    def unf4():
+        s = ops.add(h, r2)
+        ops.layernorm_fwd(s, g, b, 1e-5)
+    rec("residual+layernorm fwd", fused, time_kernel(unf4, 3, a.iters, fl), 4 * h.numel() * 2)
+    y, mean, rstd, s = ops.layernorm_fwd(h, g, b, 1e-5, residual=r2, save_sum=True)
+    dy = torch.randn(rows, lnc, device="cuda").to(bf)
+    fused = time_kernel(lambda: ops.layernorm_bwd(dy, s, g, mean, rstd, dres=r2), 3, a.iters, fl)
+
+    def unf5():
+        dx, _, _ = ops.layernorm_bwd(dy, s, g, mean, rstd)
+        ops.add(dx, r2)
+    rec("layernorm-bwd+residual", fused, time_kernel(unf5, 3, a.iters, fl), 4 * h.numel() * 2)
+    fused = time_kernel(lambda: ops.layernorm_fwd(h, g, b, 1e-5), 3, a.iters, fl)
+    rec("layernorm fwd", fused, fused, 2 * h.numel() * 2)
+    if a.json:
+        json.dump(out, open(a.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -264,6 +264,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: everything above (barrier init, TMEM allocation, descriptor prefetch) may run
+    // while the previous kernel of the stream is still finishing; its results are only touched after this point.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int tiles_mn = p.tiles_m * p.tiles_n;
     const int total_tiles = tiles_mn * p.batch * p.splits;
@@ -540,7 +543,17 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
         CME_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
         attr_set = true;
     }
-    kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ta, tb, tc, tx, ep);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<BN>::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CME_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, ep));
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
@@ -616,7 +629,7 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
                 // 4 MMAs per k-block; epilogue / pipeline fill ~ 6 k-blocks of the widest tile per unit;
                 // a split adds one fp32 write + read of the output per split
                 double est = waves * ((kb + 2.0) * 4.0 * cost[i] + 6.0 * 4.0 * bns[i] / 2.0);
-                if (s > 1) est += 400.0 + (double)s * g->M * g->N * g->batch / g_num_sms / 16.0;
+                if (s > 1) est += 6000.0 + (double)s * g->M * g->N * g->batch / g_num_sms / 16.0;   // + one more launch
                 if (est < best) { best = est; best_bn = bns[i]; best_s = s; }
             }
         }

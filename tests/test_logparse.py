@@ -1,0 +1,37 @@
+"""Log-line parsing, run validity and repeat statistics
+(FINAL_CLEAN_CODE_/scripts/summarize_single_gpu_bench.py:17-68)."""
+from cme213_final_project_b200 import checkpoint as ckpt
+from cme213_final_project_b200.utils import logfmt
+from cme213_final_project_b200.utils.logparse import (compare_trajectories, parse_run, parse_trajectory,
+                                                      summarize_repeats)
+
+
+def test_epoch_line_round_trip_and_validity():
+    text = "\n".join([logfmt.epoch_line(1, 3.19, 100, 82.0, 2494000.0, 1, False, 0, 0, 0),
+                      logfmt.epoch_line(2, 3.01, 100, 80.0, 2560000.0, 4, True, 0.011, 2.64, 1.5e-5)])
+    r = parse_run(text)
+    assert r.valid and len(r.epochs) == 2 and r.last.tok_s == 2560000 and r.last.grad_finish_ms == 2.64
+    assert r.last.checksum_span == 1.5e-5 and r.epochs[0].grad_sync_ms is None
+    assert not parse_run("nothing here").valid
+    bad = parse_run(logfmt.epoch_line(1, float("nan"), 10, 5.0, 1.0, 1, False, 0, 0, 0))
+    assert not bad.valid and bad.reason == "non-finite loss"
+    assert not parse_run(text + "\nloss went to inf at step 3").valid
+    assert parse_run(text + "\ninfo: training finished").valid
+
+
+def test_repeat_statistics_drop_the_cold_run():
+    s = summarize_repeats([600e3, 3.8e6, 3.9e6, 4.0e6], [True, True, True, True])
+    assert s["warm_runs"] == 3 and abs(s["mean"] - 3.9e6) < 1 and s["all_valid"] and s["cv"] < 0.03
+    s = summarize_repeats([1.0, 2.0, 3.0], [True, False, True])
+    assert s["valid_runs"] == 2 and s["warm_runs"] == 1 and not s["all_valid"]
+
+
+def test_trajectory_parse_and_compare():
+    st = ckpt.ParamStats(1.5, 2.5, 0.5, 0x1234)
+    a = "\n".join(ckpt.trajectory_line(1, i + 1, 4.0 - 0.1 * i, st, (0.0, 0.0, 0.0)) for i in range(3))
+    b = "\n".join(ckpt.trajectory_line(1, i + 1, 4.0 - 0.1 * i + 1e-4, st, (1e-6, 0.0, 0.0)) for i in range(3))
+    ta, tb = parse_trajectory(a), parse_trajectory(b)
+    assert len(ta) == 3 and ta[0]["hash"] == "0000000000001234" and ta[2]["step"] == 3
+    c = compare_trajectories(ta, tb)
+    assert c["ok"] and c["max_sum_span"] == 1e-6
+    assert not compare_trajectories(ta, tb[:2])["ok"]
