@@ -168,8 +168,11 @@ __device__ __forceinline__ void load8_guard(const __nv_bfloat16* rowp, int n, in
 }
 
 // Fused epilogue arithmetic on 32 columns of one row (bf16 outputs).  `pre` receives the pre-activation.
+// `in_raw` (when `in_ok`) holds the 32 bf16 of this row's primary input operand for these columns -- the activation
+// input of the derivative (dact) or else the residual -- loaded one step ahead by the caller, so the global-memory
+// latency of those row reads overlaps the previous step's arithmetic.
 __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, float* pre, bool row_ok, long long offc,
-                                              long long offr, long long offa, int n) {
+                                              long long offr, long long offa, int n, const uint4* in_raw, bool in_ok) {
     if (p.bias) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -195,7 +198,7 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             float x[8];
-            load8_guard(X, n + g * 8, p.N, row_ok, x);
+            if (in_ok) unpack8(in_raw[g], x); else load8_guard(X, n + g * 8, p.N, row_ok, x);
 #pragma unroll
             for (int q = 0; q < 8; ++q)
                 acc[g * 8 + q] = (p.dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
@@ -207,7 +210,7 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             float x[8];
-            load8_guard(R, n + g * 8, p.N, row_ok, x);
+            if (in_ok && !p.dact) unpack8(in_raw[g], x); else load8_guard(R, n + g * 8, p.N, row_ok, x);
 #pragma unroll
             for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
         }
@@ -224,7 +227,7 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
     }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool SIMPLE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const EpiParams p) {
@@ -371,7 +374,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const long long offc = zoff * p.strideC + (long long)row * p.ldc;
             const long long offr = (long long)bidx * p.strideC + (long long)row * p.ldres;
             const long long offa = (long long)bidx * p.strideC + (long long)row * p.ldaux;
+            // primary input operand of the epilogue (read per thread along its own row), prefetched in halves
+            const __nv_bfloat16* in_row =
+                p.c_f32 ? nullptr
+                        : (p.dact ? reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + offa
+                                  : (p.residual ? reinterpret_cast<const __nv_bfloat16*>(p.residual) + offr : nullptr));
+            uint4 in_cur[4];
+            bool cur_ok = false;
+            auto load_in = [&](int nn, uint4* dst) {
+                if (in_row && row < p.M && nn + 32 <= p.N) {
+                    const uint4* src = reinterpret_cast<const uint4*>(in_row + nn);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) dst[g] = __ldg(src + g);
+                }
+            };
             const uint32_t tmem_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+            if constexpr (SIMPLE) {
+                // Plain bf16 output (no fused arithmetic): the TMEM loads of chunk c+1 are in flight while chunk c is
+                // converted and staged, and the accumulator is handed back to the MMA warp as soon as the last load
+                // has landed in registers, before the stores are issued.
+                uint32_t ra[64], rb[64];
+                int nchunks = (p.N - n0 + 63) / 64;
+                nchunks = nchunks < BN / 64 ? nchunks : BN / 64;
+                tmem_ld32(tmem_row, ra);
+                tmem_ld32(tmem_row + 32, ra + 32);
+#pragma unroll
+                for (int c2 = 0; c2 < BN / 64; ++c2) {
+                    if (c2 < nchunks) {
+                        uint32_t* cur = (c2 & 1) ? rb : ra;
+                        uint32_t* nxt = (c2 & 1) ? ra : rb;
+                        tmem_wait_ld();
+                        if (c2 + 1 < nchunks) {
+                            tmem_ld32(tmem_row + (c2 + 1) * 64, nxt);
+                            tmem_ld32(tmem_row + (c2 + 1) * 64 + 32, nxt + 32);
+                        } else {
+                            tc_fence_before();
+                            mbar_arrive(&tempty_bar[buf]);          // accumulator fully read
+                        }
+                        uint8_t* sb = staging + quarter * 8192 + (store_cnt & 1) * 4096;
+                        if (lane == 0) tma_store_wait_read<1>();
+                        __syncwarp();
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const uint4 v = make_uint4(
+                                f2_to_bf2(__uint_as_float(cur[8 * q]), __uint_as_float(cur[8 * q + 1])),
+                                f2_to_bf2(__uint_as_float(cur[8 * q + 2]), __uint_as_float(cur[8 * q + 3])),
+                                f2_to_bf2(__uint_as_float(cur[8 * q + 4]), __uint_as_float(cur[8 * q + 5])),
+                                f2_to_bf2(__uint_as_float(cur[8 * q + 6]), __uint_as_float(cur[8 * q + 7])));
+                            *reinterpret_cast<uint4*>(sb + lane * 128 + ((q ^ (lane & 7)) * 16)) = v;
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(&tmC, sb, n0 + c2 * 64, m0 + quarter * 32, (int)zoff);
+                            tma_store_commit();
+                        }
+                        ++store_cnt;
+                    }
+                }
+                continue;
+            }
             if (!p.tma_store) {
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
@@ -423,12 +485,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int c2 = 0; c2 < BN / 64; ++c2) {
                     const int n = n0 + c2 * 64;
                     if (n >= p.N) break;
-                    uint8_t* sbC = staging + quarter * 8192 + (p.aux_out ? 0 : (store_cnt & 1) * 4096);
-                    uint8_t* sbX = staging + quarter * 8192 + 4096;
-                    if (lane == 0) {
-                        if (p.aux_out) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
-                    }
+                    if (c2 == 0) { load_in(n, in_cur); cur_ok = in_row && row_ok && n + 32 <= p.N; }
+                    uint8_t* sbC = staging + quarter * 8192 + (store_cnt & 1) * 4096;
+                    if (lane == 0) tma_store_wait_read<1>();
                     __syncwarp();
+                    __nv_bfloat16* Xrow = p.aux_out ? reinterpret_cast<__nv_bfloat16*>(p.aux_out) + offa : nullptr;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         uint32_t r[32];
@@ -437,20 +498,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         float acc[32], pre[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-                        epilogue_math(p, acc, pre, row_ok, offc, offr, offa, n + h * 32);
+                        // start the next half's input reads before this half's arithmetic
+                        uint4 in_nxt[4];
+                        const int nn = n + h * 32 + 32;
+                        const bool nxt_ok = in_row && row_ok && nn + 32 <= p.N && nn < n0 + BN;
+                        if (nxt_ok) load_in(nn, in_nxt);
+                        epilogue_math(p, acc, pre, row_ok, offc, offr, offa, n + h * 32, in_cur, cur_ok);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) in_cur[g] = in_nxt[g];
+                        cur_ok = nxt_ok;
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
                             const int q = h * 4 + g;
                             *reinterpret_cast<uint4*>(sbC + lane * 128 + ((q ^ (lane & 7)) * 16)) = pack8(acc + g * 8);
-                            if (p.aux_out)
-                                *reinterpret_cast<uint4*>(sbX + lane * 128 + ((q ^ (lane & 7)) * 16)) = pack8(pre + g * 8);
+                            // the pre-activation goes straight to global memory: 16 bytes per store, 64 contiguous
+                            // bytes per thread and chunk (two full sectors), no second staging buffer to wait on
+                            if (Xrow) {
+                                const int col = n + h * 32 + g * 8;
+                                if (row_ok && col + 8 <= p.N) {
+                                    *reinterpret_cast<uint4*>(Xrow + col) = pack8(pre + g * 8);
+                                } else if (row_ok) {
+#pragma unroll
+                                    for (int e2 = 0; e2 < 8; ++e2)
+                                        if (col + e2 < p.N) Xrow[col + e2] = __float2bfloat16_rn(pre[g * 8 + e2]);
+                                }
+                            }
                         }
                     }
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
                         tma_store_3d(&tmC, sbC, n, m0 + quarter * 32, (int)zoff);
-                        if (p.aux_out) tma_store_3d(&tmX, sbX, n, m0 + quarter * 32, bidx);
                         tma_store_commit();
                     }
                     ++store_cnt;
@@ -534,10 +612,10 @@ int make_tmap(CUtensorMap* out, const void* base, long long inner, long long row
 int g_num_sms = 0;
 int* g_status = nullptr;     // device status word shared by all launches on this device
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool SIMPLE>
 int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
                const EpiParams& ep, int grid, cudaStream_t st) {
-    auto kern = gemm_tc_kernel<BN, A_MN, B_MN>;
+    auto kern = gemm_tc_kernel<BN, A_MN, B_MN, SIMPLE>;
     static bool attr_set = false;
     if (!attr_set) {
         CME_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
@@ -558,13 +636,13 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
     return CME_OK;
 }
 
-template <int BN>
+template <int BN, bool SIMPLE>
 int launch_bn(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
               const CUtensorMap& tx, const EpiParams& ep, int grid, cudaStream_t st) {
-    if (!a_mn && !b_mn) return launch_cfg<BN, false, false>(ta, tb, tc, tx, ep, grid, st);
-    if (!a_mn && b_mn) return launch_cfg<BN, false, true>(ta, tb, tc, tx, ep, grid, st);
-    if (a_mn && !b_mn) return launch_cfg<BN, true, false>(ta, tb, tc, tx, ep, grid, st);
-    return launch_cfg<BN, true, true>(ta, tb, tc, tx, ep, grid, st);
+    if (!a_mn && !b_mn) return launch_cfg<BN, false, false, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
+    if (!a_mn && b_mn) return launch_cfg<BN, false, true, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
+    if (a_mn && !b_mn) return launch_cfg<BN, true, false, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
+    return launch_cfg<BN, true, true, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
 }
 
 }  // namespace
@@ -693,9 +771,17 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     const long long total = tiles * splits;
     const int grid = (int)(total < g_num_sms ? total : g_num_sms);
     const bool a_mn = g->a_trans != 0, b_mn = g->b_trans == 0;
-    if (bn == 256) rc = launch_bn<256>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
-    else if (bn == 128) rc = launch_bn<128>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
-    else rc = launch_bn<64>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+    const bool simple = ep.tma_store && !ep.c_f32 && !ep.bias && !ep.residual && !ep.aux_out && !ep.aux_in &&
+                        !ep.act && !ep.dact && !ep.accumulate;
+    if (simple) {
+        if (bn == 256) rc = launch_bn<256, true>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+        else if (bn == 128) rc = launch_bn<128, true>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+        else rc = launch_bn<64, true>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+    } else {
+        if (bn == 256) rc = launch_bn<256, false>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+        else if (bn == 128) rc = launch_bn<128, false>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+        else rc = launch_bn<64, false>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+    }
     if (rc) return rc;
     if (splits > 1) {
         const long long per = (long long)g->batch * g->M * g->N;

@@ -133,15 +133,14 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
     extern __shared__ float sm[];     // [LN_WARPS][2][D]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if constexpr (VEC) {
+        // Each warp keeps its partial d(gamma) / d(beta) rows in shared memory (its own [2][D] slice), so only the
+        // row being processed lives in registers and several blocks fit on an SM.
         const int nvec = D / W;
-        float g[LN_MAX_VEC][W], dg[LN_MAX_VEC][W], db[LN_MAX_VEC][W];
-#pragma unroll
-        for (int i = 0; i < LN_MAX_VEC; ++i) {
-            const int v = lane + 32 * i;
-#pragma unroll
-            for (int j = 0; j < W; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; g[i][j] = 0.f; }
-            if (v < nvec) load_vec<T>(gamma + v * W, g[i]);
-        }
+        constexpr int SLOTS = LN_MAX_VEC * W * 32;          // per-warp accumulator slots (>= D), bank-conflict free
+        float* wdg = sm + (size_t)warp * 2 * SLOTS;
+        float* wdb = wdg + SLOTS;
+        for (int c = lane; c < 2 * SLOTS; c += 32) wdg[c] = 0.f;
+        __syncwarp();
         for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
             const long long off = (long long)row * D;
             const float mu = mean[row], rs = rstd[row];
@@ -151,17 +150,19 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
             for (int i = 0; i < LN_MAX_VEC; ++i) {
                 const int v = lane + 32 * i;
                 if (v < nvec) {
-                    float xv[W], dv[W];
+                    float xv[W], dv[W], g[W];
                     load_vec<T>(x + off + v * W, xv);
                     load_vec<T>(dy + off + v * W, dv);
+                    load_vec<T>(gamma + v * W, g);
 #pragma unroll
                     for (int j = 0; j < W; ++j) {
                         xh[i][j] = (xv[j] - mu) * rs;
-                        dyg[i][j] = dv[j] * g[i][j];
+                        dyg[i][j] = dv[j] * g[j];
                         s1 += dyg[i][j];
                         s2 += dyg[i][j] * xh[i][j];
-                        dg[i][j] += dv[j] * xh[i][j];
-                        db[i][j] += dv[j];
+                        // slot (i*W + j)*32 + lane: consecutive lanes hit consecutive banks
+                        wdg[(i * W + j) * 32 + lane] += dv[j] * xh[i][j];
+                        wdb[(i * W + j) * 32 + lane] += dv[j];
                     }
                 }
             }
@@ -181,17 +182,6 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
                         for (int j = 0; j < W; ++j) o[j] += t[j];
                     }
                     store_vec<T>(dx + off + v * W, o);
-                }
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < LN_MAX_VEC; ++i) {
-            const int v = lane + 32 * i;
-            if (v < nvec) {
-#pragma unroll
-                for (int j = 0; j < W; ++j) {
-                    sm[(warp * 2 + 0) * D + v * W + j] = dg[i][j];
-                    sm[(warp * 2 + 1) * D + v * W + j] = db[i][j];
                 }
             }
         }
@@ -225,8 +215,17 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
     __syncthreads();
     for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) {
         float s = 0.f;
+        if constexpr (VEC) {
+            constexpr int SLOTS = LN_MAX_VEC * W * 32;
+            const int which = c >= D, col = c - which * D;
+            const int v = col / W, j = col % W;
+            const int slot = ((v >> 5) * W + j) * 32 + (v & 31);
 #pragma unroll
-        for (int w = 0; w < LN_WARPS; ++w) s += sm[w * 2 * D + c];
+            for (int w = 0; w < LN_WARPS; ++w) s += sm[(size_t)w * 2 * SLOTS + which * SLOTS + slot];
+        } else {
+#pragma unroll
+            for (int w = 0; w < LN_WARPS; ++w) s += sm[w * 2 * D + c];
+        }
         partial[(long long)blockIdx.x * 2 * D + c] = s;
     }
 }
@@ -241,8 +240,18 @@ ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int D, T*
     const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + cx;
     float s = 0.f;
-    if (c < 2 * D)
-        for (int b = ry; b < nblocks; b += 8) s += partial[(long long)b * 2 * D + c];
+    if (c < 2 * D) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;      // independent chains: the loads of four blocks overlap
+        int b = ry;
+        for (; b + 24 < nblocks; b += 32) {
+            s0 += partial[(long long)b * 2 * D + c];
+            s1 += partial[(long long)(b + 8) * 2 * D + c];
+            s2 += partial[(long long)(b + 16) * 2 * D + c];
+            s3 += partial[(long long)(b + 24) * 2 * D + c];
+        }
+        for (; b < nblocks; b += 8) s0 += partial[(long long)b * 2 * D + c];
+        s = (s0 + s1) + (s2 + s3);
+    }
     sm[ry][cx] = s;
     __syncthreads();
     if (ry == 0 && c < 2 * D) {
@@ -276,7 +285,8 @@ int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, co
              cudaStream_t st) {
     constexpr int W = VecOf<T>::N;
     const bool vec = (D % W == 0) && (D / W <= 32 * LN_MAX_VEC);
-    const size_t smem = (size_t)LN_WARPS * 2 * D * sizeof(float);
+    const size_t smem = vec ? (size_t)LN_WARPS * 2 * LN_MAX_VEC * W * 32 * sizeof(float)
+                            : (size_t)LN_WARPS * 2 * D * sizeof(float);
     if (vec) {
         auto k = ln_bwd_kernel<T, true>;
         if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
