@@ -33,13 +33,34 @@ constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
 
-template <int BN> struct Cfg {
-    static constexpr int B_TILE_BYTES = BN * BK * 2;
+// PAIR: two CTAs of a cluster share one 256 x BN tile.  Each stages 128 rows of A and BN/2 columns of B, the
+// leader issues cta_group::2 MMAs, and each holds its own 128 accumulator rows.  Per SM that is 2/3 of the
+// shared-memory fill traffic of a 128 x 256 tile for the same tensor work.
+// Epilogue shared memory: per epilogue warp a ring of NB buffers of 32 rows x 128 bytes.  A buffer receives the
+// warp's slice of the epilogue's input operand by TMA (residual, activation input of a derivative, or the old C),
+// is overwritten in place with the result and is then the source of the TMA store.  While the main loops keep
+// hundreds of KB per SM in flight, a new request to L2 takes microseconds, so the fused epilogues fetch NB - 1
+// chunks ahead (across tile boundaries), and the bias of the next tile is read while the current one is processed.
+// The plain epilogue only stores (NB = 2).
+constexpr int SMEM_LIMIT = 232448;     // 227 KB per CTA
+template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
+    static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN;       // B columns staged by this CTA
+    static constexpr int B_TILE_BYTES = BN_LOCAL * BK * 2;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-    static constexpr int STAGING_BYTES = 4 * 2 * 4096;     // per epilogue warp: two 32-row x 128-byte buffers
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    // run-time epilogue: 3; compile-time variants: 4 when a chunk has a TMA-fed input or takes two buffers
+    // (pre-activation output), else 2 -- which leaves the main loop one more stage
+    static constexpr int NB = SIMPLE ? 2 : SPEC < 0 ? 3 : (((SPEC >> 8) & 3) != 0 || ((SPEC >> 10) & 1) != 0) ? 4 : 2;
+    static constexpr int AUX_ALLOW = (NB - 2) / 2;    // bulk groups that may still be reading when a chunk takes 2 buffers
+    static constexpr int WARP_RING_BYTES = NB * 4096;
+    static constexpr int STAGING_BYTES = 4 * WARP_RING_BYTES;
+    static constexpr int BIAS_BYTES = SIMPLE ? 0 : 3 * 256 * 2;          // three tiles' worth, shared by the warps
+    static constexpr int BAR_BYTES = 512;
+    static constexpr int FIXED_BYTES = STAGING_BYTES + BIAS_BYTES + 1024 /*align slack*/ + BAR_BYTES;
+    static constexpr int FIT = (SMEM_LIMIT - FIXED_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES = FIT > 8 ? 8 : FIT;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIXED_BYTES;
+    static_assert(STAGES >= 3, "too few main-loop stages");
 };
 
 struct EpiParams {
@@ -52,6 +73,8 @@ struct EpiParams {
     void* aux_out; const void* aux_in; long long ldaux;
     int act, dact, accumulate;
     int tma_store;                 // outputs go through shared memory and TMA tile stores
+    int in_kind;                   // operand delivered by TMA through tmI: 0 none, 1 aux_in, 2 residual, 3 old C
+    int aux_ring;                  // aux_out leaves through the ring + tmX (else direct 16-byte stores)
     int* status;
 };
 
@@ -167,80 +190,119 @@ __device__ __forceinline__ void load8_guard(const __nv_bfloat16* rowp, int n, in
     }
 }
 
+// Which parts of the fused epilogue a kernel contains.  SPEC < 0: decided at run time from the parameters (one
+// kernel holds every combination -- large code whose instruction fetches miss in the caches while L2 is saturated
+// by the main loops).  SPEC >= 0: a bit set fixed at compile time, so the hot loop holds only what it executes:
+//   bit 0 bias | bits 1-2 act | bits 3-4 dact | bit 5 residual | bit 6 accumulate | bit 7 aux_out |
+//   bits 8-9 in_kind | bit 10 aux_ring
+constexpr int spec_pack(bool bias, int act, int dact, bool res, bool accum, bool aux, int in_kind, bool aux_ring) {
+    return int(bias) | (act << 1) | (dact << 3) | (int(res) << 5) | (int(accum) << 6) | (int(aux) << 7) |
+           (in_kind << 8) | (int(aux_ring) << 10);
+}
+template <int SPEC> struct Spec {
+    static constexpr bool RT = SPEC < 0;
+    __device__ __forceinline__ static bool bias(const EpiParams& p) { return RT ? p.bias != nullptr : (SPEC & 1) != 0; }
+    __device__ __forceinline__ static int act(const EpiParams& p) { return RT ? p.act : (SPEC >> 1) & 3; }
+    __device__ __forceinline__ static int dact(const EpiParams& p) { return RT ? p.dact : (SPEC >> 3) & 3; }
+    __device__ __forceinline__ static bool residual(const EpiParams& p) {
+        return RT ? p.residual != nullptr : ((SPEC >> 5) & 1) != 0;
+    }
+    __device__ __forceinline__ static bool accumulate(const EpiParams& p) {
+        return RT ? p.accumulate != 0 : ((SPEC >> 6) & 1) != 0;
+    }
+    __device__ __forceinline__ static bool aux_out(const EpiParams& p) {
+        return RT ? p.aux_out != nullptr : ((SPEC >> 7) & 1) != 0;
+    }
+    __device__ __forceinline__ static int in_kind(const EpiParams& p) { return RT ? p.in_kind : (SPEC >> 8) & 3; }
+    __device__ __forceinline__ static bool aux_ring(const EpiParams& p) {
+        return RT ? p.aux_ring != 0 : ((SPEC >> 10) & 1) != 0;
+    }
+};
+
 // Fused epilogue arithmetic on 32 columns of one row (bf16 outputs).  `pre` receives the pre-activation.
-// `in_raw` (when `in_ok`) holds the 32 bf16 of this row's primary input operand for these columns -- the activation
-// input of the derivative (dact) or else the residual -- loaded one step ahead by the caller, so the global-memory
-// latency of those row reads overlaps the previous step's arithmetic.
+// `bias8` points at the 32 bias values of these columns in shared memory.  `in_raw` holds the 32 bf16 of this row
+// of the operand named by `in_kind` (1 activation input of the derivative, 2 residual, 3 old C), fetched by TMA
+// well ahead of use; any further operand is read from global memory here.
+template <int SPEC>
 __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, float* pre, bool row_ok, long long offc,
-                                              long long offr, long long offa, int n, const uint4* in_raw, bool in_ok) {
-    if (p.bias) {
+                                              long long offr, long long offa, int n, const __nv_bfloat16* bias8,
+                                              const uint4* in_raw, int in_kind) {
+    using S = Spec<SPEC>;
+    const int act = S::act(p), dact = S::dact(p);
+    if (S::bias(p)) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             float b[8];
-            load8_guard(p.bias, n + g * 8, p.N, true, b);
+            unpack8(*reinterpret_cast<const uint4*>(bias8 + g * 8), b);
 #pragma unroll
             for (int q = 0; q < 8; ++q) acc[g * 8 + q] += b[q];
         }
     }
-    if (p.aux_out) {
+    if (S::aux_out(p)) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) pre[j] = acc[j];
     }
-    if (p.act == CME_ACT_RELU) {
+    if (act == CME_ACT_RELU) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
-    } else if (p.act == CME_ACT_GELU) {
+    } else if (act == CME_ACT_GELU) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = gelu_fast(acc[j]);
     }
-    if (p.dact) {
+    if (dact) {
         const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + offa;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             float x[8];
-            if (in_ok) unpack8(in_raw[g], x); else load8_guard(X, n + g * 8, p.N, row_ok, x);
+            if (in_kind == 1) unpack8(in_raw[g], x); else load8_guard(X, n + g * 8, p.N, row_ok, x);
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-                acc[g * 8 + q] = (p.dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
+                acc[g * 8 + q] = (dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
                                                           : acc[g * 8 + q] * dgelu_fast(x[q]);
         }
     }
-    if (p.residual) {
+    if (S::residual(p)) {
         const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.residual) + offr;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             float x[8];
-            if (in_ok && !p.dact) unpack8(in_raw[g], x); else load8_guard(R, n + g * 8, p.N, row_ok, x);
+            if (in_kind == 2) unpack8(in_raw[g], x); else load8_guard(R, n + g * 8, p.N, row_ok, x);
 #pragma unroll
             for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
         }
     }
-    if (p.accumulate) {
+    if (S::accumulate(p)) {
         const __nv_bfloat16* Cp = reinterpret_cast<const __nv_bfloat16*>(p.C) + offc;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             float x[8];
-            load8_guard(Cp, n + g * 8, p.N, row_ok, x);
+            if (in_kind == 3) unpack8(in_raw[g], x); else load8_guard(Cp, n + g * 8, p.N, row_ok, x);
 #pragma unroll
             for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
         }
     }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool SIMPLE>
+template <int BN, bool A_MN, bool B_MN, bool SIMPLE, bool PAIR, int SPEC>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const EpiParams p) {
-    using C = Cfg<BN>;
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+               const __grid_constant__ CUtensorMap tmI, const EpiParams p) {
+    using C = Cfg<BN, PAIR, SIMPLE, SPEC>;
+    using S = Spec<SPEC>;
+    static_assert(!PAIR || BN == 256, "CTA pairs use 256-wide tiles");
+    static_assert(!SIMPLE || SPEC < 0, "the plain epilogue has no compile-time variants");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* staging = smem + C::STAGES * C::STAGE_BYTES;       // 1024-byte aligned
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::STAGING_BYTES);
+    __nv_bfloat16* bias_smem = reinterpret_cast<__nv_bfloat16*>(staging + C::STAGING_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::STAGING_BYTES + C::BIAS_BYTES);
     uint64_t* full_bar = bars;                       // [STAGES]  TMA -> MMA
     uint64_t* empty_bar = bars + C::STAGES;          // [STAGES]  MMA -> TMA
     uint64_t* tfull_bar = bars + 2 * C::STAGES;      // [2]       MMA -> epilogue
     uint64_t* tempty_bar = bars + 2 * C::STAGES + 2; // [2]       epilogue -> MMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+    uint64_t* in_bar = bars + 2 * C::STAGES + 4;     // [4 warps][NB]  TMA input loads -> epilogue warp
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + 4 * C::NB);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -253,20 +315,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull_bar[b], 1);
-            mbar_init(&tempty_bar[b], 128);
+            mbar_init(&tempty_bar[b], PAIR ? 8 : 4);        // one arrival per epilogue warp (of both CTAs)
         }
+        for (int b = 0; b < 4 * C::NB; ++b) mbar_init(&in_bar[b], 1);
         fence_barrier_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, C::TMEM_COLS);
-        tmem_relinquish();
+        if constexpr (PAIR) { tmem_alloc_pair(tmem_slot, C::TMEM_COLS); tmem_relinquish_pair(); }
+        else                { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
     }
     tc_fence_before();
-    __syncthreads();
+    // In a pair, the peer's barriers and TMEM must exist before anything is signalled across.
+    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+    const int tile0 = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);
+    const int tile_step = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
+    constexpr int BMT = PAIR ? 2 * BM : BM;                  // rows of one scheduled tile
     // Programmatic dependent launch: everything above (barrier init, TMEM allocation, descriptor prefetch) may run
     // while the previous kernel of the stream is still finishing; its results are only touched after this point.
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -280,10 +348,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = tile0; tile < total_tiles && ok; tile += tile_step) {
                 const int mn = tile % tiles_mn, rest = tile / tiles_mn;
                 const int bidx = rest % p.batch, split = rest / p.batch;
-                const int m0 = (mn % p.tiles_m) * BM, n0 = (mn / p.tiles_m) * BN;
+                const int m0 = (mn % p.tiles_m) * BMT + int(cta_rank) * BM;
+                const int n0 = (mn / p.tiles_m) * BN + int(cta_rank) * C::BN_LOCAL;
                 const int kb0 = split * p.kb_per_split;
                 const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
                 const int za = p.a_batched ? bidx : 0, zb = p.b_batched ? bidx : 0;
@@ -291,20 +360,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* sA = smem + stage * C::STAGE_BYTES;
                     uint8_t* sB = sA + A_TILE_BYTES;
-                    mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_BYTES);
-                    if (!A_MN) {
-                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, m0, za);
-                    } else {
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are credited to the leader's barrier, which its MMA thread waits on
+                        if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * C::STAGE_BYTES);
+                        const uint32_t fb = mapa_u32(&full_bar[stage], 0);
+                        if (!A_MN) {
+                            tma_load_3d_pair(sA, &tmA, fb, kb * BK, m0, za);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j)
-                            tma_load_3d(sA + j * (64 * BK * 2), &tmA, &full_bar[stage], m0 + j * 64, kb * BK, za);
-                    }
-                    if (!B_MN) {
-                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, n0, zb);
-                    } else {
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_3d_pair(sA + j * (64 * BK * 2), &tmA, fb, m0 + j * 64, kb * BK, za);
+                        }
+                        if (!B_MN) {
+                            tma_load_3d_pair(sB, &tmB, fb, kb * BK, n0, zb);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_3d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK, zb);
+                            for (int j = 0; j < C::BN_LOCAL / 64; ++j)
+                                tma_load_3d_pair(sB + j * (64 * BK * 2), &tmB, fb, n0 + j * 64, kb * BK, zb);
+                        }
+                    } else {
+                        mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_BYTES);
+                        if (!A_MN) {
+                            tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, m0, za);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_3d(sA + j * (64 * BK * 2), &tmA, &full_bar[stage], m0 + j * 64, kb * BK, za);
+                        }
+                        if (!B_MN) {
+                            tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, n0, zb);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j)
+                                tma_load_3d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK, zb);
+                        }
                     }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -316,13 +405,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(1 /*bf16*/, A_MN, B_MN, BM, BN);
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = make_idesc(1 /*bf16*/, A_MN, B_MN, BMT, BN);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            for (int tile = tile0; tile < total_tiles && ok; tile += tile_step, ++it) {
                 const int rest = tile / tiles_mn;
                 const int split = rest / p.batch;
                 const int kb0 = split * p.kb_per_split;
@@ -345,12 +434,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                                  : make_smem_desc(sA + k * UMMA_K * 2, 0, 1024);
                         const uint64_t db = B_MN ? make_smem_desc(sB + k * UMMA_K * 128, BK * 128, 1024)
                                                  : make_smem_desc(sB + k * UMMA_K * 2, 0, 1024);
-                        mma_f16_ss(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if constexpr (PAIR) mma_f16_ss_pair(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        else                mma_f16_ss(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
-                    mma_commit(&empty_bar[stage]);      // stage is free once these MMAs have read it
+                    // stage is free (in both CTAs of a pair) once these MMAs have read it
+                    if constexpr (PAIR) mma_commit_pair(&empty_bar[stage], 3); else mma_commit(&empty_bar[stage]);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
-                if (ok) mma_commit(&tfull_bar[buf]);    // accumulator complete
+                if (ok) {                               // accumulator complete
+                    if constexpr (PAIR) mma_commit_pair(&tfull_bar[buf], 3); else mma_commit(&tfull_bar[buf]);
+                }
             }
         }
     } else {
@@ -361,12 +454,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int it = 0;
         uint32_t store_cnt = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        // the accumulator goes back to the (leader's) MMA thread: one arrival per warp
+        auto acc_release = [&](int b) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(&tempty_bar[b], 0));
+                else                mbar_arrive(&tempty_bar[b]);
+            }
+        };
+        // Ring of this warp's epilogue buffers and the cursor of the input prefetch (fused bf16 epilogues only).  The
+        // cursor runs over (tile, 64-column chunk) in the order the warp will consume them, NB - 1 chunks ahead, and
+        // crosses tile boundaries, so the first chunks of a tile are already in flight while its main loop runs.
+        uint8_t* ring = staging + quarter * C::WARP_RING_BYTES;
+        uint64_t* my_in_bar = in_bar + quarter * C::NB;
+        // Bias values of three consecutive tiles, [3][256].  Every epilogue warp writes the same values (and reads
+        // only after its own writes); three slots because a warp may finish tile i + 1, and park the bias of tile
+        // i + 2, while another is still reading that of tile i.
+        __nv_bfloat16* bias_w = bias_smem;
+        const bool ring_epi = !SIMPLE && (SPEC >= 0 || (p.tma_store && !p.c_f32));
+        const int in_kind = ring_epi ? S::in_kind(p) : 0;
+        uint32_t slot = 0;                              // ring buffers handed out so far
+        int f_tile = tile0, f_c = 0;
+        uint32_t f_cnt = 0;
+        auto fetch_next = [&]() {
+            if (f_tile >= total_tiles) return;
+            const int fmn = f_tile % tiles_mn, fb = (f_tile / tiles_mn) % p.batch;
+            const int fm0 = (fmn % p.tiles_m) * BMT + int(cta_rank) * BM + quarter * 32, fn0 = (fmn / p.tiles_m) * BN;
+            int nchf = (p.N - fn0 + 63) / 64;
+            nchf = nchf < BN / 64 ? nchf : BN / 64;
+            if (lane == 0) {
+                const uint32_t b = f_cnt % C::NB;
+                mbar_arrive_expect_tx(&my_in_bar[b], 4096);
+                tma_load_3d(ring + b * 4096, &tmI, &my_in_bar[b], fn0 + f_c * 64, fm0, fb);
+            }
+            ++f_cnt;
+            if (++f_c == nchf) { f_c = 0; f_tile += tile_step; }
+        };
+        if (in_kind) {
+            for (int i = 0; i < C::NB - 1; ++i) fetch_next();
+        }
+        const bool stage_bias = !SIMPLE && ring_epi && S::bias(p);
+        auto bias_fetch = [&](int t) {                  // this lane's 8 bias values of tile t (zeros past N)
+            float b8[8];
+            const int tn0 = ((t % tiles_mn) / p.tiles_m) * BN;
+            load8_guard(p.bias, tn0 + lane * 8, p.N, true, b8);
+            return pack8(b8);
+        };
+        if (stage_bias && tile0 < total_tiles) {
+            *reinterpret_cast<uint4*>(bias_w + lane * 8) = bias_fetch(tile0);
+            __syncwarp();
+        }
+        for (int tile = tile0; tile < total_tiles && ok; tile += tile_step, ++it) {
             const int mn = tile % tiles_mn, rest = tile / tiles_mn;
             const int bidx = rest % p.batch, split = rest / p.batch;
-            const int m0 = (mn % p.tiles_m) * BM, n0 = (mn / p.tiles_m) * BN;
+            const int m0 = (mn % p.tiles_m) * BMT + int(cta_rank) * BM, n0 = (mn / p.tiles_m) * BN;
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
+            const __nv_bfloat16* bias_s = bias_w + (it % 3) * 256;
+            // the next tile's bias values are requested now and parked in shared memory after this tile's chunks
+            uint4 bias_next = make_uint4(0, 0, 0, 0);
+            const bool have_next = stage_bias && tile + tile_step < total_tiles;
+            if (have_next) bias_next = bias_fetch(tile + tile_step);
             if (!mbar_wait(&tfull_bar[buf], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
@@ -374,20 +523,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const long long offc = zoff * p.strideC + (long long)row * p.ldc;
             const long long offr = (long long)bidx * p.strideC + (long long)row * p.ldres;
             const long long offa = (long long)bidx * p.strideC + (long long)row * p.ldaux;
-            // primary input operand of the epilogue (read per thread along its own row), prefetched in halves
-            const __nv_bfloat16* in_row =
-                p.c_f32 ? nullptr
-                        : (p.dact ? reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + offa
-                                  : (p.residual ? reinterpret_cast<const __nv_bfloat16*>(p.residual) + offr : nullptr));
-            uint4 in_cur[4];
-            bool cur_ok = false;
-            auto load_in = [&](int nn, uint4* dst) {
-                if (in_row && row < p.M && nn + 32 <= p.N) {
-                    const uint4* src = reinterpret_cast<const uint4*>(in_row + nn);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) dst[g] = __ldg(src + g);
-                }
-            };
             const uint32_t tmem_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
             if constexpr (SIMPLE) {
                 // Plain bf16 output (no fused arithmetic): the TMEM loads of chunk c+1 are in flight while chunk c is
@@ -408,10 +543,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             tmem_ld32(tmem_row + (c2 + 1) * 64, nxt);
                             tmem_ld32(tmem_row + (c2 + 1) * 64 + 32, nxt + 32);
                         } else {
-                            tc_fence_before();
-                            mbar_arrive(&tempty_bar[buf]);          // accumulator fully read
+                            acc_release(buf);                       // accumulator fully read
                         }
-                        uint8_t* sb = staging + quarter * 8192 + (store_cnt & 1) * 4096;
+                        uint8_t* sb = staging + quarter * C::WARP_RING_BYTES + (store_cnt & 1) * 4096;
                         if (lane == 0) tma_store_wait_read<1>();
                         __syncwarp();
 #pragma unroll
@@ -434,7 +568,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 continue;
             }
-            if (!p.tma_store) {
+            if (SPEC < 0 && !p.tma_store) {
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
@@ -448,7 +582,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         epilogue_chunk(p, acc, offc, offr, offa, n, min(32, p.N - n), vec_ok);
                     }
                 }
-            } else if (p.c_f32) {
+            } else if (SPEC < 0 && p.c_f32) {
                 // fp32 output (split-K partials, fp32 C): 32 columns = one 128-byte staging row per TMA store
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
@@ -463,7 +597,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         for (int j = 0; j < 32; ++j)
                             if (row < p.M && n + j < p.N) r[j] = __float_as_uint(__uint_as_float(r[j]) + Cp[n + j]);
                     }
-                    uint8_t* sb = staging + quarter * 8192 + (store_cnt & 1) * 4096;
+                    uint8_t* sb = staging + quarter * C::WARP_RING_BYTES + (store_cnt & 1) * 4096;
                     if (lane == 0) tma_store_wait_read<1>();
                     __syncwarp();
 #pragma unroll
@@ -479,41 +613,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     ++store_cnt;
                 }
             } else {
-                // bf16 output: 64 columns = one 128-byte staging row per TMA store
+                // bf16 output, fused epilogue: per 64-column chunk one ring buffer (two when the pre-activation also
+                // leaves through the ring).  With a TMA-fed input the buffer already holds this warp's 32 x 64 slice
+                // of it; every thread replaces its own 16-byte groups in place with the result.
                 const bool row_ok = row < p.M;
+                const bool aux_ring = S::aux_ring(p);
+                __nv_bfloat16* Xrow = (S::aux_out(p) && !aux_ring) ? reinterpret_cast<__nv_bfloat16*>(p.aux_out) + offa
+                                                                   : nullptr;
 #pragma unroll 1
                 for (int c2 = 0; c2 < BN / 64; ++c2) {
                     const int n = n0 + c2 * 64;
                     if (n >= p.N) break;
-                    if (c2 == 0) { load_in(n, in_cur); cur_ok = in_row && row_ok && n + 32 <= p.N; }
-                    uint8_t* sbC = staging + quarter * 8192 + (store_cnt & 1) * 4096;
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
-                    __nv_bfloat16* Xrow = p.aux_out ? reinterpret_cast<__nv_bfloat16*>(p.aux_out) + offa : nullptr;
+                    uint8_t* sbC = ring + (slot % C::NB) * 4096;
+                    uint8_t* sbX = ring + ((slot + 1) % C::NB) * 4096;
+                    if (in_kind) {
+                        if (!mbar_wait(&my_in_bar[slot % C::NB], (slot / C::NB) & 1, abort_flag)) { ok = false; break; }
+                    }
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         uint32_t r[32];
                         tmem_ld32(tmem_row + c2 * 64 + h * 32, r);
+                        uint4 in_raw[4];
+                        if (in_kind) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g)
+                                in_raw[g] = *reinterpret_cast<const uint4*>(sbC + lane * 128 +
+                                                                            (((h * 4 + g) ^ (lane & 7)) * 16));
+                        }
                         tmem_wait_ld();
                         float acc[32], pre[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-                        // start the next half's input reads before this half's arithmetic
-                        uint4 in_nxt[4];
-                        const int nn = n + h * 32 + 32;
-                        const bool nxt_ok = in_row && row_ok && nn + 32 <= p.N && nn < n0 + BN;
-                        if (nxt_ok) load_in(nn, in_nxt);
-                        epilogue_math(p, acc, pre, row_ok, offc, offr, offa, n + h * 32, in_cur, cur_ok);
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) in_cur[g] = in_nxt[g];
-                        cur_ok = nxt_ok;
+                        epilogue_math<SPEC>(p, acc, pre, row_ok, offc, offr, offa, n + h * 32,
+                                            bias_s + c2 * 64 + h * 32, in_raw, in_kind);
+                        if (h == 0 && !in_kind) {
+                            // buffers written by plain stores: their previous TMA stores must have been read out.
+                            // One bulk group per chunk; the aux variant takes two buffers per chunk.
+                            if (lane == 0) {
+                                if (aux_ring) tma_store_wait_read<C::AUX_ALLOW>();
+                                else tma_store_wait_read<C::NB - 1>();
+                            }
+                            __syncwarp();
+                        }
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
                             const int q = h * 4 + g;
                             *reinterpret_cast<uint4*>(sbC + lane * 128 + ((q ^ (lane & 7)) * 16)) = pack8(acc + g * 8);
-                            // the pre-activation goes straight to global memory: 16 bytes per store, 64 contiguous
-                            // bytes per thread and chunk (two full sectors), no second staging buffer to wait on
-                            if (Xrow) {
+                            if (aux_ring) {
+                                *reinterpret_cast<uint4*>(sbX + lane * 128 + ((q ^ (lane & 7)) * 16)) =
+                                    pack8(pre + g * 8);
+                            } else if (Xrow) {
                                 const int col = n + h * 32 + g * 8;
                                 if (row_ok && col + 8 <= p.N) {
                                     *reinterpret_cast<uint4*>(Xrow + col) = pack8(pre + g * 8);
@@ -529,23 +678,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) {
                         tma_store_3d(&tmC, sbC, n, m0 + quarter * 32, (int)zoff);
+                        if (aux_ring) tma_store_3d(&tmX, sbX, n, m0 + quarter * 32, bidx);
                         tma_store_commit();
                     }
-                    ++store_cnt;
+                    slot += aux_ring ? 2 : 1;
+                    if (in_kind) {
+                        // refill the buffer stored one chunk ago with the chunk NB - 1 ahead
+                        if (lane == 0) tma_store_wait_read<1>();
+                        __syncwarp();
+                        fetch_next();
+                    }
                 }
+                if (!ok) break;
             }
-            tc_fence_before();
-            mbar_arrive(&tempty_bar[buf]);
+            if (have_next) {
+                *reinterpret_cast<uint4*>(bias_w + ((it + 1) % 3) * 256 + lane * 8) = bias_next;
+                __syncwarp();
+            }
+            acc_release(buf);
+        }
+        if (!ok && in_kind) {
+            // input copies may still be in flight: give them time to land before shared memory is released
+            for (int i = 0; i < 2000; ++i) __nanosleep(500);
         }
         if (p.tma_store && lane == 0) tma_store_wait<0>();   // stores complete before shared memory goes away
     }
 
+    __syncwarp();
     tc_fence_before();
-    __syncthreads();
+    // A pair leaves together: neither CTA may exit while the other can still signal its barriers or read its tiles.
+    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, CME_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, C::TMEM_COLS);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, C::TMEM_COLS); else tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
 }
 
@@ -612,37 +778,73 @@ int make_tmap(CUtensorMap* out, const void* base, long long inner, long long row
 int g_num_sms = 0;
 int* g_status = nullptr;     // device status word shared by all launches on this device
 
-template <int BN, bool A_MN, bool B_MN, bool SIMPLE>
+int g_max_pairs = -1;        // co-resident CTA pairs of the pair kernels on this device (0: cluster launch unusable)
+
+template <int BN, bool A_MN, bool B_MN, bool SIMPLE, bool PAIR, int SPEC = -1>
 int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
-               const EpiParams& ep, int grid, cudaStream_t st) {
-    auto kern = gemm_tc_kernel<BN, A_MN, B_MN, SIMPLE>;
+               const CUtensorMap& ti, const EpiParams& ep, int grid, cudaStream_t st) {
+    auto kern = gemm_tc_kernel<BN, A_MN, B_MN, SIMPLE, PAIR, SPEC>;
     static bool attr_set = false;
     if (!attr_set) {
-        CME_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
+        CME_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, PAIR, SIMPLE, SPEC>::SMEM_BYTES));
         attr_set = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = Cfg<BN>::SMEM_BYTES;
+    cfg.dynamicSmemBytes = Cfg<BN, PAIR, SIMPLE, SPEC>::SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    CME_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, ep));
+    if (PAIR) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
+    CME_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, ti, ep));
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
 
-template <int BN, bool SIMPLE>
+template <int BN, bool SIMPLE, bool PAIR, int SPEC = -1>
 int launch_bn(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-              const CUtensorMap& tx, const EpiParams& ep, int grid, cudaStream_t st) {
-    if (!a_mn && !b_mn) return launch_cfg<BN, false, false, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
-    if (!a_mn && b_mn) return launch_cfg<BN, false, true, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
-    if (a_mn && !b_mn) return launch_cfg<BN, true, false, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
-    return launch_cfg<BN, true, true, SIMPLE>(ta, tb, tc, tx, ep, grid, st);
+              const CUtensorMap& tx, const CUtensorMap& ti, const EpiParams& ep, int grid, cudaStream_t st) {
+    if (!a_mn && !b_mn) return launch_cfg<BN, false, false, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
+    if (!a_mn && b_mn) return launch_cfg<BN, false, true, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
+    if (a_mn && !b_mn) return launch_cfg<BN, true, false, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
+    return launch_cfg<BN, true, true, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
+}
+
+// Epilogue combinations with a compile-time kernel (CTA-pair tiles only): the ones a transformer layer uses.
+constexpr int SPEC_BIAS = spec_pack(true, 0, 0, false, false, false, 0, false);
+constexpr int SPEC_BIAS_RES = spec_pack(true, 0, 0, true, false, false, 2, false);
+constexpr int SPEC_BIAS_GELU_AUX = spec_pack(true, CME_ACT_GELU, 0, false, false, true, 0, true);
+constexpr int SPEC_DGELU = spec_pack(false, 0, CME_ACT_GELU, false, false, false, 1, false);
+constexpr int SPEC_BIAS_RELU = spec_pack(true, CME_ACT_RELU, 0, false, false, false, 0, false);
+constexpr int SPEC_DRELU = spec_pack(false, 0, CME_ACT_RELU, false, false, false, 1, false);
+
+// How many CTA pairs of the pair kernel can be resident at once (the persistent grid must not exceed it: a pair
+// that is not resident would only start when another has finished all of its tiles).
+int query_max_pairs() {
+    auto kern = gemm_tc_kernel<256, false, false, true, true, -1>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256, true, true>::SMEM_BYTES) !=
+        cudaSuccess) { cudaGetLastError(); return 0; }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * g_num_sms);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<256, true, true>::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
 }
 
 }  // namespace
@@ -681,40 +883,59 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         int rc = cme_gemm_status_word(&dummy);
         if (rc) return rc;
     }
-    const int tiles_m = cme_cdiv(g->M, BM);
+    if (g_max_pairs < 0) {
+        const char* e = getenv("CME213_GEMM_PAIR");
+        g_max_pairs = (e && e[0] == '0') ? 0 : query_max_pairs();
+    }
+    int tiles_m = cme_cdiv(g->M, BM);
     const int num_kb = cme_cdiv(g->K, BK);
     // Tile width and K splits: minimise  waves x k-blocks per unit x cost(bn)  (+ fixed per-tile and
     // per-split overheads).  cost(bn) per 16-deep MMA is max(tensor time bn/2, shared-memory read time
     // (128 + bn)/4) in clocks: 128 / 64 / 48 for bn = 256 / 128 / 64.
     const bool plain_epi = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;
+    // force_bn: 64 / 128 / 256 = tile width on one CTA; 512 = the 256 x 256 tile on a CTA pair
     int bn = g->force_bn, splits = g->force_splits;
+    bool pair = false;
+    if (bn == 512) { bn = 256; pair = true; }
     if (!bn || !splits) {
         double best = 1e30;
         int best_bn = 128, best_s = 1;
-        const int bns[3] = {256, 128, 64};
-        const double cost[3] = {128.0, 80.0, 64.0};     // narrower tiles re-read A more often than they compute
-        for (int i = 0; i < 3; ++i) {
-            if (g->force_bn && bns[i] != g->force_bn) continue;
+        bool best_pair = false;
+        const int bns[4] = {256, 256, 128, 64};
+        // clocks per 16-deep MMA step and SM: the 128-row tiles are limited by how fast shared memory can be
+        // refilled from L2 ((128 + bn) x 32 bytes per step), the pair tile (128 + 128 per SM) by the tensor pipe
+        const double cost[4] = {136.0, 168.0, 100.0, 72.0};
+        for (int i = 0; i < 4; ++i) {
+            const bool pr = i == 0;
+            if (pr && (g_max_pairs <= 0 || g->M <= BM)) continue;
+            if (g->force_bn && (g->force_bn == 512 ? !pr : (pr || bns[i] != g->force_bn))) continue;
             if (bns[i] > 64 && g->N <= bns[i] / 2) continue;            // tile mostly padding
-            const long long t = (long long)tiles_m * cme_cdiv(g->N, bns[i]) * g->batch;
+            const long long t = (long long)cme_cdiv(g->M, pr ? 2 * BM : BM) * cme_cdiv(g->N, bns[i]) * g->batch;
+            const int slots = pr ? g_max_pairs : g_num_sms;
             for (int s = 1; s <= 16; ++s) {
                 if (g->force_splits && s != g->force_splits) continue;
                 if (s > 1 && (!plain_epi || !g->workspace || num_kb / s < 4 ||
                               (long long)s * g->batch * g->M * g->N * 4 > g->workspace_bytes)) break;
                 const long long units = t * s;
-                const double waves = (double)((units + g_num_sms - 1) / g_num_sms);
+                const double waves = (double)((units + slots - 1) / slots);
                 const double kb = (double)cme_cdiv(num_kb, s);
                 // 4 MMAs per k-block; epilogue / pipeline fill ~ 6 k-blocks of the widest tile per unit;
                 // a split adds one fp32 write + read of the output per split
                 double est = waves * ((kb + 2.0) * 4.0 * cost[i] + 6.0 * 4.0 * bns[i] / 2.0);
                 if (s > 1) est += 6000.0 + (double)s * g->M * g->N * g->batch / g_num_sms / 16.0;   // + one more launch
-                if (est < best) { best = est; best_bn = bns[i]; best_s = s; }
+                if (est < best) { best = est; best_bn = bns[i]; best_s = s; best_pair = pr; }
             }
         }
-        if (!bn) bn = best_bn;
+        if (!bn) { bn = best_bn; pair = best_pair; }
         if (!splits) splits = best_s;
     }
-    CME_REQUIRE(bn == 64 || bn == 128 || bn == 256, CME_ERR_SHAPE, "tile width must be 64, 128 or 256");
+    CME_REQUIRE(bn == 64 || bn == 128 || bn == 256, CME_ERR_SHAPE, "tile width must be 64, 128, 256 or 512 (pair)");
+    CME_REQUIRE(!pair || g_max_pairs > 0, CME_ERR_SHAPE, "CTA-pair tiles are not available on this device");
+    if (pair) tiles_m = cme_cdiv(g->M, 2 * BM);
+    static const bool trace = getenv("CME213_GEMM_TRACE") != nullptr;
+    if (trace)
+        fprintf(stderr, "[gemm] M=%d N=%d K=%d batch=%d at=%d bt=%d -> bn=%d pair=%d splits=%d\n", g->M, g->N, g->K,
+                g->batch, g->a_trans, g->b_trans, bn, (int)pair, splits);
     const int tiles_n = cme_cdiv(g->N, bn);
     const long long tiles = (long long)tiles_m * tiles_n * g->batch;
     if (splits > 1) {
@@ -732,7 +953,8 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     else             rc = make_tmap(&ta, g->A, g->M, g->K, g->lda, g->strideA ? g->batch : 1, g->strideA, BK);
     if (rc) return rc;
     // B: stored [N, K] (b_trans) is K-major -> map (K, N), box (64, bn); stored [K, N] -> map (N, K), box (64, 64)
-    if (g->b_trans) rc = make_tmap(&tb, g->B, g->K, g->N, g->ldb, g->strideB ? g->batch : 1, g->strideB, bn);
+    if (g->b_trans) rc = make_tmap(&tb, g->B, g->K, g->N, g->ldb, g->strideB ? g->batch : 1, g->strideB,
+                                   pair ? bn / 2 : bn);
     else            rc = make_tmap(&tb, g->B, g->N, g->K, g->ldb, g->strideB ? g->batch : 1, g->strideB, BK);
     if (rc) return rc;
 
@@ -751,7 +973,7 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         ep.act = g->act; ep.dact = g->dact; ep.accumulate = g->accumulate;
     }
     // Outputs through shared-memory staging + TMA tile stores when rows are 16-byte addressable.
-    CUtensorMap tc = ta, tx = ta;
+    CUtensorMap tc = ta, tx = ta, ti = ta;
     {
         const int es = ep.c_f32 ? 4 : 2;
         auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
@@ -766,21 +988,52 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
                 if (rc) return rc;
             }
             ep.tma_store = 1;
+            // The operand the fused epilogue reads per output element comes in by TMA, chunk by chunk, ahead of use.
+            if (!ep.c_f32) {
+                const void* ib = nullptr;
+                long long ild = 0;
+                int kind = 0;
+                if (ep.dact) { ib = ep.aux_in; ild = ep.ldaux; kind = 1; }
+                else if (ep.residual) { ib = ep.residual; ild = ep.ldres; kind = 2; }
+                else if (ep.accumulate) { ib = ep.C; ild = ep.ldc; kind = 3; }
+                if (kind && al16(ib) && (ild * 2) % 16 == 0 && (g->batch == 1 || (ep.strideC * 2) % 16 == 0)) {
+                    rc = make_tmap(&ti, ib, g->N, g->M, ild, g->batch, g->batch > 1 ? ep.strideC : 0, 32);
+                    if (rc) return rc;
+                    ep.in_kind = kind;
+                }
+                ep.aux_ring = ep.aux_out && !ep.in_kind;
+            }
         }
     }
     const long long total = tiles * splits;
-    const int grid = (int)(total < g_num_sms ? total : g_num_sms);
+    const int grid = pair ? 2 * (int)(total < g_max_pairs ? total : g_max_pairs)
+                          : (int)(total < g_num_sms ? total : g_num_sms);
     const bool a_mn = g->a_trans != 0, b_mn = g->b_trans == 0;
     const bool simple = ep.tma_store && !ep.c_f32 && !ep.bias && !ep.residual && !ep.aux_out && !ep.aux_in &&
                         !ep.act && !ep.dact && !ep.accumulate;
     if (simple) {
-        if (bn == 256) rc = launch_bn<256, true>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
-        else if (bn == 128) rc = launch_bn<128, true>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
-        else rc = launch_bn<64, true>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+        if (pair) rc = launch_bn<256, true, true>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
+        else if (bn == 256) rc = launch_bn<256, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
+        else if (bn == 128) rc = launch_bn<128, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
+        else rc = launch_bn<64, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
     } else {
-        if (bn == 256) rc = launch_bn<256, false>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
-        else if (bn == 128) rc = launch_bn<128, false>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
-        else rc = launch_bn<64, false>(a_mn, b_mn, ta, tb, tc, tx, ep, grid, stream);
+        const int spec = (ep.tma_store && !ep.c_f32)
+                             ? spec_pack(ep.bias != nullptr, ep.act, ep.dact, ep.residual != nullptr, ep.accumulate != 0,
+                                         ep.aux_out != nullptr, ep.in_kind, ep.aux_ring != 0)
+                             : -1;
+#define CME_SPEC_CASE(SP) \
+    if (pair && spec == SP) rc = launch_bn<256, false, true, SP>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream); else
+        CME_SPEC_CASE(SPEC_BIAS)
+        CME_SPEC_CASE(SPEC_BIAS_RES)
+        CME_SPEC_CASE(SPEC_BIAS_GELU_AUX)
+        CME_SPEC_CASE(SPEC_DGELU)
+        CME_SPEC_CASE(SPEC_BIAS_RELU)
+        CME_SPEC_CASE(SPEC_DRELU)
+#undef CME_SPEC_CASE
+        if (pair) rc = launch_bn<256, false, true>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
+        else if (bn == 256) rc = launch_bn<256, false, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
+        else if (bn == 128) rc = launch_bn<128, false, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
+        else rc = launch_bn<64, false, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
     }
     if (rc) return rc;
     if (splits > 1) {
