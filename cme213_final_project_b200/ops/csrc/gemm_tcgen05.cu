@@ -194,7 +194,7 @@ __device__ __forceinline__ void load8_guard(const __nv_bfloat16* rowp, int n, in
 // kernel holds every combination -- large code whose instruction fetches miss in the caches while L2 is saturated
 // by the main loops).  SPEC >= 0: a bit set fixed at compile time, so the hot loop holds only what it executes:
 //   bit 0 bias | bits 1-2 act | bits 3-4 dact | bit 5 residual | bit 6 accumulate | bit 7 aux_out |
-//   bits 8-9 in_kind | bit 10 aux_ring
+//   bits 8-9 in_kind | bit 10 aux_ring | bit 11 fp32 output (split-K partials; nothing else set)
 constexpr int spec_pack(bool bias, int act, int dact, bool res, bool accum, bool aux, int in_kind, bool aux_ring) {
     return int(bias) | (act << 1) | (dact << 3) | (int(res) << 5) | (int(accum) << 6) | (int(aux) << 7) |
            (in_kind << 8) | (int(aux_ring) << 10);
@@ -216,6 +216,9 @@ template <int SPEC> struct Spec {
     __device__ __forceinline__ static int in_kind(const EpiParams& p) { return RT ? p.in_kind : (SPEC >> 8) & 3; }
     __device__ __forceinline__ static bool aux_ring(const EpiParams& p) {
         return RT ? p.aux_ring != 0 : ((SPEC >> 10) & 1) != 0;
+    }
+    __device__ __forceinline__ static bool c_f32(const EpiParams& p) {
+        return RT ? p.c_f32 != 0 : ((SPEC >> 11) & 1) != 0;
     }
 };
 
@@ -472,7 +475,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // only after its own writes); three slots because a warp may finish tile i + 1, and park the bias of tile
         // i + 2, while another is still reading that of tile i.
         __nv_bfloat16* bias_w = bias_smem;
-        const bool ring_epi = !SIMPLE && (SPEC >= 0 || (p.tma_store && !p.c_f32));
+        const bool ring_epi = !SIMPLE && (SPEC >= 0 ? !S::c_f32(p) : (p.tma_store && !p.c_f32));
         const int in_kind = ring_epi ? S::in_kind(p) : 0;
         uint32_t slot = 0;                              // ring buffers handed out so far
         int f_tile = tile0, f_c = 0;
@@ -582,7 +585,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         epilogue_chunk(p, acc, offc, offr, offa, n, min(32, p.N - n), vec_ok);
                     }
                 }
-            } else if (SPEC < 0 && p.c_f32) {
+            } else if (S::c_f32(p)) {
                 // fp32 output (split-K partials, fp32 C): 32 columns = one 128-byte staging row per TMA store
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
@@ -591,7 +594,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     uint32_t r[32];
                     tmem_ld32(tmem_row + c * 32, r);
                     tmem_wait_ld();
-                    if (p.accumulate) {
+                    if (SPEC < 0 && p.accumulate) {
                         const float* Cp = reinterpret_cast<const float*>(p.C) + offc;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
@@ -736,6 +739,38 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ P, int splits, lo
     }
 }
 
+// Same, four consecutive columns per thread (N, ldc and strideC multiples of 4): 16-byte reads of every partial.
+__global__ void splitk_reduce_vec4_kernel(const float4* __restrict__ P, int splits, long long per_split4, void* Cout,
+                                          int c_f32, int accumulate, int M, int N4, long long ldc, long long strideC,
+                                          int batch) {
+    const long long total = (long long)batch * M * N4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        float4 s = P[i];
+        for (int k = 1; k < splits; ++k) {
+            const float4 v = P[k * per_split4 + i];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        const long long mn4 = (long long)M * N4;
+        const long long b = i / mn4, rem = i - b * mn4;
+        const long long r = rem / N4, c = (rem - r * N4) * 4;
+        const long long off = b * strideC + r * ldc + c;
+        if (c_f32) {
+            float4* C = reinterpret_cast<float4*>(reinterpret_cast<float*>(Cout) + off);
+            if (accumulate) { const float4 o = *C; s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w; }
+            *C = s;
+        } else {
+            uint2* C = reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Cout) + off);
+            if (accumulate) {
+                const uint2 o = *C;
+                const float2 a = bf2_to_f2(o.x), d = bf2_to_f2(o.y);
+                s.x += a.x; s.y += a.y; s.z += d.x; s.w += d.y;
+            }
+            *C = make_uint2(f2_to_bf2(s.x, s.y), f2_to_bf2(s.z, s.w));
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
@@ -827,6 +862,8 @@ constexpr int SPEC_BIAS_GELU_AUX = spec_pack(true, CME_ACT_GELU, 0, false, false
 constexpr int SPEC_DGELU = spec_pack(false, 0, CME_ACT_GELU, false, false, false, 1, false);
 constexpr int SPEC_BIAS_RELU = spec_pack(true, CME_ACT_RELU, 0, false, false, false, 0, false);
 constexpr int SPEC_DRELU = spec_pack(false, 0, CME_ACT_RELU, false, false, false, 1, false);
+constexpr int SPEC_RES = spec_pack(false, 0, 0, true, false, false, 2, false);
+constexpr int SPEC_F32 = 1 << 11;
 
 // How many CTA pairs of the pair kernel can be resident at once (the persistent grid must not exceed it: a pair
 // that is not resident would only start when another has finished all of its tiles).
@@ -1017,10 +1054,12 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         else if (bn == 128) rc = launch_bn<128, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
         else rc = launch_bn<64, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
     } else {
-        const int spec = (ep.tma_store && !ep.c_f32)
-                             ? spec_pack(ep.bias != nullptr, ep.act, ep.dact, ep.residual != nullptr, ep.accumulate != 0,
-                                         ep.aux_out != nullptr, ep.in_kind, ep.aux_ring != 0)
-                             : -1;
+        int spec = -1;
+        if (ep.tma_store && !ep.c_f32)
+            spec = spec_pack(ep.bias != nullptr, ep.act, ep.dact, ep.residual != nullptr, ep.accumulate != 0,
+                             ep.aux_out != nullptr, ep.in_kind, ep.aux_ring != 0);
+        else if (ep.tma_store && ep.c_f32 && !ep.accumulate)
+            spec = SPEC_F32;
 #define CME_SPEC_CASE(SP) \
     if (pair && spec == SP) rc = launch_bn<256, false, true, SP>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream); else
         CME_SPEC_CASE(SPEC_BIAS)
@@ -1029,6 +1068,8 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         CME_SPEC_CASE(SPEC_DGELU)
         CME_SPEC_CASE(SPEC_BIAS_RELU)
         CME_SPEC_CASE(SPEC_DRELU)
+        CME_SPEC_CASE(SPEC_RES)
+        CME_SPEC_CASE(SPEC_F32)
 #undef CME_SPEC_CASE
         if (pair) rc = launch_bn<256, false, true>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
         else if (bn == 256) rc = launch_bn<256, false, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
@@ -1038,10 +1079,22 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     if (rc) return rc;
     if (splits > 1) {
         const long long per = (long long)g->batch * g->M * g->N;
-        const int blocks = (int)((per + 255) / 256 < 4096 ? (per + 255) / 256 : 4096);
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(g->workspace), splits, per,
-                                                         g->C, g->c_dtype == CME_F32, g->accumulate, g->M, g->N,
-                                                         g->ldc, g->strideC, g->batch);
+        const bool f32 = g->c_dtype == CME_F32;
+        const bool vec = g->N % 4 == 0 && g->ldc % 4 == 0 && (g->batch == 1 || g->strideC % 4 == 0) &&
+                         (reinterpret_cast<uintptr_t>(g->C) & (f32 ? 15 : 7)) == 0 &&
+                         (reinterpret_cast<uintptr_t>(g->workspace) & 15) == 0;
+        if (vec) {
+            const long long per4 = per / 4;
+            const int blocks = (int)((per4 + 255) / 256 < 8 * g_num_sms ? (per4 + 255) / 256 : 8 * g_num_sms);
+            splitk_reduce_vec4_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(g->workspace), splits,
+                                                                  per4, g->C, f32, g->accumulate, g->M, g->N / 4,
+                                                                  g->ldc, g->strideC, g->batch);
+        } else {
+            const int blocks = (int)((per + 255) / 256 < 4096 ? (per + 255) / 256 : 4096);
+            splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(g->workspace), splits, per,
+                                                             g->C, f32, g->accumulate, g->M, g->N, g->ldc, g->strideC,
+                                                             g->batch);
+        }
         CME_LAUNCH_CHECK();
     }
     return CME_OK;
