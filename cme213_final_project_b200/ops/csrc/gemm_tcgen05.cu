@@ -8,10 +8,11 @@
 // writes fp32 partials to a workspace and a second kernel sums them in a fixed order, so weight
 // gradients are bit-reproducible.
 //
-// Structure per CTA (192 threads, 1 CTA per SM):
+// Structure per CTA (192 threads -- 320 with eight epilogue warps for the arithmetic-heavy epilogues; 1 CTA per SM):
 //   warp 0      one lane issues TMA tile loads into a ring of shared-memory stages
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma (128 x BN x 16 per instruction)
 //   warps 2..5  epilogue: tcgen05.ld of their 32-lane quarter of the accumulator, fused epilogue, stores
+//   (warps 6..9  a second epilogue set on the same four quarters, taking every other 64-column chunk)
 // Operands may be K-major or MN-major in global memory; MN-major tiles are fetched as 64-wide column
 // groups so that shared memory holds the canonical 128-byte-swizzled layout either way.
 // Every mbarrier wait is bounded: on expiry the CTA sets the abort flag, leaves its loops, reports
@@ -31,7 +32,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 192;          // TMA warp + MMA warp + 4 epilogue warps
+constexpr int NUM_THREADS_WIDE = 320;     // ... + 8 epilogue warps (two per scheduler) for the arithmetic-heavy epilogues
 
 // PAIR: two CTAs of a cluster share one 256 x BN tile.  Each stages 128 rows of A and BN/2 columns of B, the
 // leader issues cta_group::2 MMAs, and each holds its own 128 accumulator rows.  Per SM that is 2/3 of the
@@ -48,12 +50,17 @@ template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
     static constexpr int B_TILE_BYTES = BN_LOCAL * BK * 2;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-    // run-time epilogue: 3; compile-time variants: 4 when a chunk has a TMA-fed input or takes two buffers
-    // (pre-activation output), else 2 -- which leaves the main loop one more stage
-    static constexpr int NB = SIMPLE ? 2 : SPEC < 0 ? 3 : (((SPEC >> 8) & 3) != 0 || ((SPEC >> 10) & 1) != 0) ? 4 : 2;
+    // Compile-time variants with a TMA-fed input or a second (pre-activation) output run eight epilogue warps, two
+    // per warp scheduler, each set taking every other 64-column chunk: their dependent chains (TMEM load, shared
+    // memory, MUFU) then overlap instead of leaving the scheduler idle.  Two buffers per warp there; three for the
+    // run-time epilogue; two where the epilogue only stores.
+    static constexpr bool WIDE = !SIMPLE && SPEC >= 0 && (((SPEC >> 8) & 3) != 0 || ((SPEC >> 10) & 1) != 0);
+    static constexpr int EPI_WARPS = WIDE ? 8 : 4;
+    static constexpr int THREADS = WIDE ? NUM_THREADS_WIDE : NUM_THREADS;
+    static constexpr int NB = SIMPLE ? 2 : SPEC < 0 ? 3 : 2;
     static constexpr int AUX_ALLOW = (NB - 2) / 2;    // bulk groups that may still be reading when a chunk takes 2 buffers
     static constexpr int WARP_RING_BYTES = NB * 4096;
-    static constexpr int STAGING_BYTES = 4 * WARP_RING_BYTES;
+    static constexpr int STAGING_BYTES = EPI_WARPS * WARP_RING_BYTES;
     static constexpr int BIAS_BYTES = SIMPLE ? 0 : 3 * 256 * 2;          // three tiles' worth, shared by the warps
     static constexpr int BAR_BYTES = 512;
     static constexpr int FIXED_BYTES = STAGING_BYTES + BIAS_BYTES + 1024 /*align slack*/ + BAR_BYTES;
@@ -287,7 +294,7 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
 }
 
 template <int BN, bool A_MN, bool B_MN, bool SIMPLE, bool PAIR, int SPEC>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__((Cfg<BN, PAIR, SIMPLE, SPEC>::THREADS), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
                const __grid_constant__ CUtensorMap tmI, const EpiParams p) {
@@ -305,7 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t* tfull_bar = bars + 2 * C::STAGES;      // [2]       MMA -> epilogue
     uint64_t* tempty_bar = bars + 2 * C::STAGES + 2; // [2]       epilogue -> MMA
     uint64_t* in_bar = bars + 2 * C::STAGES + 4;     // [4 warps][NB]  TMA input loads -> epilogue warp
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + 4 * C::NB);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + C::EPI_WARPS * C::NB);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -318,9 +325,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull_bar[b], 1);
-            mbar_init(&tempty_bar[b], PAIR ? 8 : 4);        // one arrival per epilogue warp (of both CTAs)
+            mbar_init(&tempty_bar[b], (PAIR ? 2 : 1) * C::EPI_WARPS);   // one arrival per epilogue warp (of both CTAs)
         }
-        for (int b = 0; b < 4 * C::NB; ++b) mbar_init(&in_bar[b], 1);
+        for (int b = 0; b < C::EPI_WARPS * C::NB; ++b) mbar_init(&in_bar[b], 1);
         fence_barrier_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
@@ -469,8 +476,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // Ring of this warp's epilogue buffers and the cursor of the input prefetch (fused bf16 epilogues only).  The
         // cursor runs over (tile, 64-column chunk) in the order the warp will consume them, NB - 1 chunks ahead, and
         // crosses tile boundaries, so the first chunks of a tile are already in flight while its main loop runs.
-        uint8_t* ring = staging + quarter * C::WARP_RING_BYTES;
-        uint64_t* my_in_bar = in_bar + quarter * C::NB;
+        constexpr int ESETS = C::EPI_WARPS / 4;         // warp sets; set s takes the chunks c with c % ESETS == s
+        const int eset = (warp - 2) >> 2;
+        const int wslot = eset * 4 + quarter;
+        uint8_t* ring = staging + wslot * C::WARP_RING_BYTES;
+        uint64_t* my_in_bar = in_bar + wslot * C::NB;
         // Bias values of three consecutive tiles, [3][256].  Every epilogue warp writes the same values (and reads
         // only after its own writes); three slots because a warp may finish tile i + 1, and park the bias of tile
         // i + 2, while another is still reading that of tile i.
@@ -478,21 +488,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const bool ring_epi = !SIMPLE && (SPEC >= 0 ? !S::c_f32(p) : (p.tma_store && !p.c_f32));
         const int in_kind = ring_epi ? S::in_kind(p) : 0;
         uint32_t slot = 0;                              // ring buffers handed out so far
-        int f_tile = tile0, f_c = 0;
+        int f_tile = tile0, f_c = eset;
         uint32_t f_cnt = 0;
         auto fetch_next = [&]() {
+            int fmn = 0, fn0 = 0;
+            while (f_tile < total_tiles) {              // next tile that has a chunk for this warp set
+                fmn = f_tile % tiles_mn;
+                fn0 = (fmn / p.tiles_m) * BN;
+                int nchf = (p.N - fn0 + 63) / 64;
+                nchf = nchf < BN / 64 ? nchf : BN / 64;
+                if (f_c < nchf) break;
+                f_c = eset;
+                f_tile += tile_step;
+            }
             if (f_tile >= total_tiles) return;
-            const int fmn = f_tile % tiles_mn, fb = (f_tile / tiles_mn) % p.batch;
-            const int fm0 = (fmn % p.tiles_m) * BMT + int(cta_rank) * BM + quarter * 32, fn0 = (fmn / p.tiles_m) * BN;
-            int nchf = (p.N - fn0 + 63) / 64;
-            nchf = nchf < BN / 64 ? nchf : BN / 64;
+            const int fb = (f_tile / tiles_mn) % p.batch;
+            const int fm0 = (fmn % p.tiles_m) * BMT + int(cta_rank) * BM + quarter * 32;
             if (lane == 0) {
                 const uint32_t b = f_cnt % C::NB;
                 mbar_arrive_expect_tx(&my_in_bar[b], 4096);
                 tma_load_3d(ring + b * 4096, &tmI, &my_in_bar[b], fn0 + f_c * 64, fm0, fb);
             }
             ++f_cnt;
-            if (++f_c == nchf) { f_c = 0; f_tile += tile_step; }
+            f_c += ESETS;
         };
         if (in_kind) {
             for (int i = 0; i < C::NB - 1; ++i) fetch_next();
@@ -548,7 +566,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         } else {
                             acc_release(buf);                       // accumulator fully read
                         }
-                        uint8_t* sb = staging + quarter * C::WARP_RING_BYTES + (store_cnt & 1) * 4096;
+                        uint8_t* sb = ring + (store_cnt & 1) * 4096;
                         if (lane == 0) tma_store_wait_read<1>();
                         __syncwarp();
 #pragma unroll
@@ -600,7 +618,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         for (int j = 0; j < 32; ++j)
                             if (row < p.M && n + j < p.N) r[j] = __float_as_uint(__uint_as_float(r[j]) + Cp[n + j]);
                     }
-                    uint8_t* sb = staging + quarter * C::WARP_RING_BYTES + (store_cnt & 1) * 4096;
+                    uint8_t* sb = ring + (store_cnt & 1) * 4096;
                     if (lane == 0) tma_store_wait_read<1>();
                     __syncwarp();
 #pragma unroll
@@ -624,7 +642,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 __nv_bfloat16* Xrow = (S::aux_out(p) && !aux_ring) ? reinterpret_cast<__nv_bfloat16*>(p.aux_out) + offa
                                                                    : nullptr;
 #pragma unroll 1
-                for (int c2 = 0; c2 < BN / 64; ++c2) {
+                for (int c2 = eset; c2 < BN / 64; c2 += ESETS) {
                     const int n = n0 + c2 * 64;
                     if (n >= p.N) break;
                     uint8_t* sbC = ring + (slot % C::NB) * 4096;
@@ -826,7 +844,7 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.blockDim = dim3(Cfg<BN, PAIR, SIMPLE, SPEC>::THREADS);
     cfg.dynamicSmemBytes = Cfg<BN, PAIR, SIMPLE, SPEC>::SMEM_BYTES;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];

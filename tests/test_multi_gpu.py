@@ -60,7 +60,7 @@ def test_bounded_wait_reports_instead_of_hanging():
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_peer_memory_collectives_and_fused_sync():
-    n = min(torch.cuda.device_count(), 4)
+    n = min(torch.cuda.device_count(), 8)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "tests", "mp_fused_check.py")]
