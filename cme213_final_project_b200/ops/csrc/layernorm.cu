@@ -122,6 +122,101 @@ ln_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ 
     }
 }
 
+template <typename T> __device__ __forceinline__ void unpack_raw(const uint4& r, float* f);
+template <> __device__ __forceinline__ void unpack_raw<float>(const uint4& r, float* f) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+}
+template <> __device__ __forceinline__ void unpack_raw<__nv_bfloat16>(const uint4& r, float* f) { unpack8(r, f); }
+
+// Backward for rows that fit NV 16-byte vectors per lane (D = W * 32 * NV at most).  One warp per row, grid-stride.
+// The row stays in registers as raw 16-byte words between the two passes (statistics, then dx), the warp's partial
+// d(gamma) / d(beta) live in its own shared-memory slice (slot (i*W + j)*32 + lane: conflict-free), and the grid is
+// sized to what is resident at once, so every block runs the same number of rounds.
+template <typename T, int NV>
+__global__ void __launch_bounds__(LN_WARPS * 32, NV <= 3 ? 3 : 2)
+ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                  const float* __restrict__ mean, const float* __restrict__ rstd, const T* __restrict__ dres,
+                  T* __restrict__ dx, float* __restrict__ partial /*[gridDim.x][2][D]*/, int rows, int D) {
+    constexpr int W = VecOf<T>::N;
+    constexpr int SLOTS = NV * W * 32;
+    extern __shared__ float sm[];     // [LN_WARPS][2][SLOTS]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nvec = D / W;
+    float* wdg = sm + (size_t)warp * 2 * SLOTS;
+    float* wdb = wdg + SLOTS;
+    for (int c = lane; c < 2 * SLOTS; c += 32) wdg[c] = 0.f;
+    uint4 graw[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int v = lane + 32 * i;
+        graw[i] = v < nvec ? *reinterpret_cast<const uint4*>(gamma + v * W) : make_uint4(0, 0, 0, 0);
+    }
+    __syncwarp();
+    for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
+        const long long off = (long long)row * D;
+        uint4 xr[NV], dr[NV], rr[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                xr[i] = *reinterpret_cast<const uint4*>(x + off + v * W);
+                dr[i] = *reinterpret_cast<const uint4*>(dy + off + v * W);
+                if (dres) rr[i] = *reinterpret_cast<const uint4*>(dres + off + v * W);
+            }
+        }
+        const float mu = mean[row], rs = rstd[row];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (lane + 32 * i < nvec) {
+                float xv[W], dv[W], g[W];
+                unpack_raw<T>(xr[i], xv);
+                unpack_raw<T>(dr[i], dv);
+                unpack_raw<T>(graw[i], g);
+#pragma unroll
+                for (int j = 0; j < W; ++j) {
+                    const float xh = (xv[j] - mu) * rs, d = dv[j] * g[j];
+                    s1 += d;
+                    s2 += d * xh;
+                    wdg[(i * W + j) * 32 + lane] += dv[j] * xh;
+                    wdb[(i * W + j) * 32 + lane] += dv[j];
+                }
+            }
+        }
+        s1 = warp_sum(s1) / D;
+        s2 = warp_sum(s2) / D;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                float xv[W], dv[W], g[W], o[W];
+                unpack_raw<T>(xr[i], xv);
+                unpack_raw<T>(dr[i], dv);
+                unpack_raw<T>(graw[i], g);
+#pragma unroll
+                for (int j = 0; j < W; ++j) o[j] = rs * (dv[j] * g[j] - s1 - (xv[j] - mu) * rs * s2);
+                if (dres) {
+                    float t[W];
+                    unpack_raw<T>(rr[i], t);
+#pragma unroll
+                    for (int j = 0; j < W; ++j) o[j] += t[j];
+                }
+                store_vec<T>(dx + off + v * W, o);
+            }
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) {
+        const int which = c >= D, col = c - which * D;
+        const int v = col / W, j = col % W;
+        const int slot = ((v >> 5) * W + j) * 32 + (v & 31);
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < LN_WARPS; ++w) s += sm[(size_t)w * 2 * SLOTS + which * SLOTS + slot];
+        partial[(long long)blockIdx.x * 2 * D + c] = s;
+    }
+}
+
 // dx = rstd * (dy*g - mean(dy*g) - xhat * mean(dy*g*xhat)) [+ dres];  per-block partial dgamma / dbeta.
 // Grid-stride over rows; each lane owns fixed columns so its partial sums stay in registers.
 template <typename T, bool VEC>
@@ -231,25 +326,25 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
 }
 
 // dgamma[c] (+)= sum_b partial[b][0][c];  dbeta[c] (+)= sum_b partial[b][1][c]
-// Block (32 columns x 8 block-groups): each thread sums every 8th partial, then a fixed-order shared-memory
-// reduction over the 8 groups (deterministic).
+// Block (16 columns x 16 block-groups): each thread sums every 16th partial, then a fixed-order shared-memory
+// reduction over the 16 groups (deterministic).
 template <typename T>
 __global__ void __launch_bounds__(256)
 ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int D, T* dgamma, T* dbeta, int accumulate) {
-    __shared__ float sm[8][33];
-    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + cx;
+    __shared__ float sm[16][17];
+    const int cx = threadIdx.x & 15, ry = threadIdx.x >> 4;
+    const int c = blockIdx.x * 16 + cx;
     float s = 0.f;
     if (c < 2 * D) {
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;      // independent chains: the loads of four blocks overlap
         int b = ry;
-        for (; b + 24 < nblocks; b += 32) {
+        for (; b + 48 < nblocks; b += 64) {
             s0 += partial[(long long)b * 2 * D + c];
-            s1 += partial[(long long)(b + 8) * 2 * D + c];
-            s2 += partial[(long long)(b + 16) * 2 * D + c];
-            s3 += partial[(long long)(b + 24) * 2 * D + c];
+            s1 += partial[(long long)(b + 16) * 2 * D + c];
+            s2 += partial[(long long)(b + 32) * 2 * D + c];
+            s3 += partial[(long long)(b + 48) * 2 * D + c];
         }
-        for (; b < nblocks; b += 8) s0 += partial[(long long)b * 2 * D + c];
+        for (; b < nblocks; b += 16) s0 += partial[(long long)b * 2 * D + c];
         s = (s0 + s1) + (s2 + s3);
     }
     sm[ry][cx] = s;
@@ -257,7 +352,7 @@ ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int D, T*
     if (ry == 0 && c < 2 * D) {
         float t = 0.f;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) t += sm[r][cx];
+        for (int r = 0; r < 16; ++r) t += sm[r][cx];
         T* dst = (c < D) ? dgamma + c : dbeta + (c - D);
         *dst = from_f32<T>(accumulate ? to_f32<T>(*dst) + t : t);
     }
@@ -279,27 +374,56 @@ int ln_fwd_t(const void* a, const void* b, void* r, const void* g, const void* b
     return CME_OK;
 }
 
+template <typename T, int NV>
+int ln_bwd_vec_launch(const T* dy, const T* x, const T* g, const float* mean, const float* rstd, const T* dres, T* dx,
+                      float* scratch, int max_blocks, int rows, int D, int* used_blocks, cudaStream_t st) {
+    constexpr int W = VecOf<T>::N;
+    const size_t smem = (size_t)LN_WARPS * 2 * NV * W * 32 * sizeof(float);
+    auto k = ln_bwd_vec_kernel<T, NV>;
+    static int resident = 0;          // blocks of this instantiation that fit on the device at once
+    if (!resident) {
+        int dev = 0, sms = 0, per_sm = 0;
+        CME_CUDA(cudaGetDevice(&dev));
+        CME_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        CME_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, LN_WARPS * 32, smem));
+        resident = sms * (per_sm > 0 ? per_sm : 1);
+    }
+    int nb = cme_cdiv(rows, LN_WARPS);
+    if (nb > resident) {
+        // same number of rounds for every block: ceil(groups / rounds) blocks
+        const int rounds = cme_cdiv(nb, resident);
+        nb = cme_cdiv(nb, rounds);
+    }
+    if (nb > max_blocks) nb = max_blocks;
+    k<<<nb, LN_WARPS * 32, smem, st>>>(dy, x, g, mean, rstd, dres, dx, scratch, rows, D);
+    *used_blocks = nb;
+    return CME_OK;
+}
+
 template <typename T>
 int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, const float* rstd, const void* dres,
              void* dx, void* dgamma, void* dbeta, float* scratch, int nblocks, int rows, int D, int accumulate,
              cudaStream_t st) {
     constexpr int W = VecOf<T>::N;
     const bool vec = (D % W == 0) && (D / W <= 32 * LN_MAX_VEC);
-    const size_t smem = vec ? (size_t)LN_WARPS * 2 * LN_MAX_VEC * W * 32 * sizeof(float)
-                            : (size_t)LN_WARPS * 2 * D * sizeof(float);
     if (vec) {
-        auto k = ln_bwd_kernel<T, true>;
-        if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<nblocks, LN_WARPS * 32, smem, st>>>((const T*)dy, (const T*)x, (const T*)g, mean, rstd, (const T*)dres,
-                                                (T*)dx, scratch, rows, D);
+        const int nv = cme_cdiv(D / W, 32);
+        int rc;
+#define CME_LN_NV(N) rc = ln_bwd_vec_launch<T, N>((const T*)dy, (const T*)x, (const T*)g, mean, rstd, (const T*)dres, \
+                                                 (T*)dx, scratch, nblocks, rows, D, &nblocks, st)
+        if (nv == 1) CME_LN_NV(1); else if (nv == 2) CME_LN_NV(2); else if (nv == 3) CME_LN_NV(3); else CME_LN_NV(4);
+#undef CME_LN_NV
+        if (rc) return rc;
     } else {
+        const size_t smem = (size_t)LN_WARPS * 2 * D * sizeof(float);
         auto k = ln_bwd_kernel<T, false>;
         if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         k<<<nblocks, LN_WARPS * 32, smem, st>>>((const T*)dy, (const T*)x, (const T*)g, mean, rstd, (const T*)dres,
                                                 (T*)dx, scratch, rows, D);
     }
     CME_LAUNCH_CHECK();
-    ln_bwd_finalize_kernel<T><<<cme_cdiv(2 * D, 32), 256, 0, st>>>(scratch, nblocks, D, (T*)dgamma, (T*)dbeta,
+    ln_bwd_finalize_kernel<T><<<cme_cdiv(2 * D, 16), 256, 0, st>>>(scratch, nblocks, D, (T*)dgamma, (T*)dbeta,
                                                                   accumulate);
     CME_LAUNCH_CHECK();
     return CME_OK;
