@@ -129,11 +129,12 @@ template <> __device__ __forceinline__ void unpack_raw<float>(const uint4& r, fl
 template <> __device__ __forceinline__ void unpack_raw<__nv_bfloat16>(const uint4& r, float* f) { unpack8(r, f); }
 
 // Backward for rows that fit NV 16-byte vectors per lane (D = W * 32 * NV at most).  One warp per row, grid-stride.
-// The row stays in registers as raw 16-byte words between the two passes (statistics, then dx), the warp's partial
-// d(gamma) / d(beta) live in its own shared-memory slice (slot (i*W + j)*32 + lane: conflict-free), and the grid is
-// sized to what is resident at once, so every block runs the same number of rounds.
+// Each lane owns fixed columns: the row stays in registers as raw 16-byte words between the two passes (statistics,
+// then dx) and the lane's partial d(gamma) / d(beta) accumulate in registers over all rows of the warp; they reach the warp's
+// shared-memory slice (slot (i*W + j)*32 + lane: conflict-free) once at the end.  The grid is sized to what is
+// resident at once, so every block runs the same number of rounds.
 template <typename T, int NV>
-__global__ void __launch_bounds__(LN_WARPS * 32, NV <= 3 ? 3 : 2)
+__global__ void __launch_bounds__(LN_WARPS * 32, NV <= 2 ? 3 : 2)
 ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                   const float* __restrict__ mean, const float* __restrict__ rstd, const T* __restrict__ dres,
                   T* __restrict__ dx, float* __restrict__ partial /*[gridDim.x][2][D]*/, int rows, int D) {
@@ -144,14 +145,16 @@ ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
     const int nvec = D / W;
     float* wdg = sm + (size_t)warp * 2 * SLOTS;
     float* wdb = wdg + SLOTS;
-    for (int c = lane; c < 2 * SLOTS; c += 32) wdg[c] = 0.f;
+    float adg[NV][W], adb[NV][W];
     uint4 graw[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int v = lane + 32 * i;
-        graw[i] = v < nvec ? *reinterpret_cast<const uint4*>(gamma + v * W) : make_uint4(0, 0, 0, 0);
+        graw[i] = make_uint4(0, 0, 0, 0);
+        if (v < nvec) graw[i] = *reinterpret_cast<const uint4*>(gamma + v * W);
+#pragma unroll
+        for (int j = 0; j < W; ++j) adg[i][j] = adb[i][j] = 0.f;
     }
-    __syncwarp();
     for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
         const long long off = (long long)row * D;
         uint4 xr[NV], dr[NV], rr[NV];
@@ -177,9 +180,9 @@ ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
                 for (int j = 0; j < W; ++j) {
                     const float xh = (xv[j] - mu) * rs, d = dv[j] * g[j];
                     s1 += d;
-                    s2 += d * xh;
-                    wdg[(i * W + j) * 32 + lane] += dv[j] * xh;
-                    wdb[(i * W + j) * 32 + lane] += dv[j];
+                    s2 = fmaf(d, xh, s2);
+                    adg[i][j] = fmaf(dv[j], xh, adg[i][j]);
+                    adb[i][j] += dv[j];
                 }
             }
         }
@@ -194,7 +197,7 @@ ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
                 unpack_raw<T>(dr[i], dv);
                 unpack_raw<T>(graw[i], g);
 #pragma unroll
-                for (int j = 0; j < W; ++j) o[j] = rs * (dv[j] * g[j] - s1 - (xv[j] - mu) * rs * s2);
+                for (int j = 0; j < W; ++j) o[j] = rs * (fmaf(-(xv[j] - mu) * rs, s2, dv[j] * g[j]) - s1);
                 if (dres) {
                     float t[W];
                     unpack_raw<T>(rr[i], t);
@@ -203,6 +206,15 @@ ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
                 }
                 store_vec<T>(dx + off + v * W, o);
             }
+        }
+    }
+    // the warp's partial sums go to its shared-memory slice once, after its last row
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+            wdg[(i * W + j) * 32 + lane] = adg[i][j];
+            wdb[(i * W + j) * 32 + lane] = adb[i][j];
         }
     }
     __syncthreads();
