@@ -1,740 +1,22 @@
-// bf16 GEMM on the 5th-generation tensor cores: TMA-fed, mbarrier-pipelined, accumulators in TMEM,
-// persistent over output tiles with a double-buffered accumulator so the epilogue of tile i overlaps the
-// main loop of tile i+1.
-//
-// Replaces every GEMM variant of the reference (FINAL_CLEAN_CODE_/src/kernels/gemm.cu:483-1998: NN / TN /
-// NT, accumulate twins, atomic split-K, strided-batched) and the cuBLAS / cuBLASLt wrappers (:111-481).
-// The reference's split-K adds partial sums with atomicAdd into a zeroed C (:1028-1144); here split-K
-// writes fp32 partials to a workspace and a second kernel sums them in a fixed order, so weight
-// gradients are bit-reproducible.
-//
-// Structure per CTA (192 threads -- 320 with eight epilogue warps for the arithmetic-heavy epilogues; 1 CTA per SM):
-//   warp 0      one lane issues TMA tile loads into a ring of shared-memory stages
-//   warp 1      allocates TMEM; one lane issues tcgen05.mma (128 x BN x 16 per instruction)
-//   warps 2..5  epilogue: tcgen05.ld of their 32-lane quarter of the accumulator, fused epilogue, stores
-//   (warps 6..9  a second epilogue set on the same four quarters, taking every other 64-column chunk)
-// Operands may be K-major or MN-major in global memory; MN-major tiles are fetched as 64-wide column
-// groups so that shared memory holds the canonical 128-byte-swizzled layout either way.
-// Every mbarrier wait is bounded: on expiry the CTA sets the abort flag, leaves its loops, reports
-// through the status word, frees its TMEM and returns.
-#include "gemm.h"
-#include "sm100_ptx.cuh"
+// Host side of the tcgen05 GEMM: tile / split-K planning, tensor maps, dispatch to the kernel instantiation that
+// matches the layout and the fused epilogue, split-K reduction kernels and the status word.  The kernel itself is in
+// gemm_tcgen05_kernel.cuh; its instantiations live in gemm_tc_inst_*.cu.
+#include "gemm_tcgen05_kernel.cuh"
 
-#include <cuda.h>
 #include <dlfcn.h>
 #include <mutex>
 
-using namespace sm100;
+using namespace gemm_tc;
+
+// Instantiated elsewhere (one line per launcher; each covers the four operand layouts).
+#define CME_GEMM_TC_EXTERN(BN, SIMPLE, PAIR, SPEC)                                                                  \
+    extern template int gemm_tc::launch_bn<BN, SIMPLE, PAIR, SPEC>(bool, bool, const CUtensorMap&, const CUtensorMap&, \
+                                                                   const CUtensorMap&, const CUtensorMap&,             \
+                                                                   const CUtensorMap&, const EpiParams&, int, cudaStream_t);
+#include "gemm_tc_inst_list.h"
+#undef CME_GEMM_TC_EXTERN
 
 namespace {
-
-constexpr int BM = 128;
-constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
-constexpr int A_TILE_BYTES = BM * BK * 2;
-constexpr int NUM_THREADS = 192;          // TMA warp + MMA warp + 4 epilogue warps
-constexpr int NUM_THREADS_WIDE = 320;     // ... + 8 epilogue warps (two per scheduler) for the arithmetic-heavy epilogues
-
-// PAIR: two CTAs of a cluster share one 256 x BN tile.  Each stages 128 rows of A and BN/2 columns of B, the
-// leader issues cta_group::2 MMAs, and each holds its own 128 accumulator rows.  Per SM that is 2/3 of the
-// shared-memory fill traffic of a 128 x 256 tile for the same tensor work.
-// Epilogue shared memory: per epilogue warp a ring of NB buffers of 32 rows x 128 bytes.  A buffer receives the
-// warp's slice of the epilogue's input operand by TMA (residual, activation input of a derivative, or the old C),
-// is overwritten in place with the result and is then the source of the TMA store.  While the main loops keep
-// hundreds of KB per SM in flight, a new request to L2 takes microseconds, so the fused epilogues fetch NB - 1
-// chunks ahead (across tile boundaries), and the bias of the next tile is read while the current one is processed.
-// The plain epilogue only stores (NB = 2).
-constexpr int SMEM_LIMIT = 232448;     // 227 KB per CTA
-template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
-    static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN;       // B columns staged by this CTA
-    static constexpr int B_TILE_BYTES = BN_LOCAL * BK * 2;
-    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-    // Compile-time variants with a TMA-fed input or a second (pre-activation) output run eight epilogue warps, two
-    // per warp scheduler, each set taking every other 64-column chunk: their dependent chains (TMEM load, shared
-    // memory, MUFU) then overlap instead of leaving the scheduler idle.  Two buffers per warp there; three for the
-    // run-time epilogue; two where the epilogue only stores.
-    static constexpr bool WIDE = !SIMPLE && SPEC >= 0 && (((SPEC >> 8) & 3) != 0 || ((SPEC >> 10) & 1) != 0);
-    static constexpr int EPI_WARPS = WIDE ? 8 : 4;
-    static constexpr int THREADS = WIDE ? NUM_THREADS_WIDE : NUM_THREADS;
-    static constexpr int NB = SIMPLE ? 2 : SPEC < 0 ? 3 : 2;
-    static constexpr int AUX_ALLOW = (NB - 2) / 2;    // bulk groups that may still be reading when a chunk takes 2 buffers
-    static constexpr int WARP_RING_BYTES = NB * 4096;
-    static constexpr int STAGING_BYTES = EPI_WARPS * WARP_RING_BYTES;
-    static constexpr int BIAS_BYTES = SIMPLE ? 0 : 3 * 256 * 2;          // three tiles' worth, shared by the warps
-    static constexpr int BAR_BYTES = 512;
-    static constexpr int FIXED_BYTES = STAGING_BYTES + BIAS_BYTES + 1024 /*align slack*/ + BAR_BYTES;
-    static constexpr int FIT = (SMEM_LIMIT - FIXED_BYTES) / STAGE_BYTES;
-    static constexpr int STAGES = FIT > 8 ? 8 : FIT;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIXED_BYTES;
-    static_assert(STAGES >= 3, "too few main-loop stages");
-};
-
-struct EpiParams {
-    int M, N, K, batch;
-    int tiles_m, tiles_n, splits, kb_per_split, num_kb;
-    int a_batched, b_batched;
-    void* C; long long ldc, strideC; int c_f32;
-    const __nv_bfloat16* bias;
-    const void* residual; long long ldres;
-    void* aux_out; const void* aux_in; long long ldaux;
-    int act, dact, accumulate;
-    int tma_store;                 // outputs go through shared memory and TMA tile stores
-    int in_kind;                   // operand delivered by TMA through tmI: 0 none, 1 aux_in, 2 residual, 3 old C
-    int aux_ring;                  // aux_out leaves through the ring + tmX (else direct 16-byte stores)
-    int* status;
-};
-
-__device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, long long row_off_c,
-                                               long long row_off_res, long long row_off_aux, int n, int ncols,
-                                               bool vec_ok) {
-    // acc: 32 fp32 values of one output row, columns [n, n+32); ncols = how many are inside N.
-    if (p.bias) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (j < ncols) acc[j] += __bfloat162float(p.bias[n + j]);
-    }
-    const bool full = vec_ok && ncols == 32;
-    if (p.c_f32) {
-        float* C = reinterpret_cast<float*>(p.C) + row_off_c + n;
-        if (p.accumulate) {
-            if (full) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    float4 o = *reinterpret_cast<const float4*>(C + j);
-                    acc[j] += o.x; acc[j + 1] += o.y; acc[j + 2] += o.z; acc[j + 3] += o.w;
-                }
-            } else {
-                _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) acc[j] += C[j];
-            }
-        }
-        if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(C + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-        } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) C[j] = acc[j];
-        }
-        return;
-    }
-    __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off_c + n;
-    if (p.aux_out) {
-        __nv_bfloat16* X = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + row_off_aux + n;
-        if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) *reinterpret_cast<Bf16x8*>(X + j) = pack8(acc + j);
-        } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) X[j] = __float2bfloat16_rn(acc[j]);
-        }
-    }
-    if (p.act == CME_ACT_RELU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
-    } else if (p.act == CME_ACT_GELU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = gelu_fast(acc[j]);
-    }
-    if (p.dact) {
-        const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + row_off_aux + n;
-        float x[32];
-        if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) unpack8(*reinterpret_cast<const Bf16x8*>(X + j), x + j);
-        } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) x[j] = (j < ncols) ? __bfloat162float(X[j]) : 0.f;
-        }
-        if (p.dact == CME_ACT_RELU) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] = x[j] > 0.f ? acc[j] : 0.f;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] *= dgelu_fast(x[j]);
-        }
-    }
-    if (p.residual) {
-        const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.residual) + row_off_res + n;
-        if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-                float r[8];
-                unpack8(*reinterpret_cast<const Bf16x8*>(R + j), r);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) acc[j + q] += r[q];
-            }
-        } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) acc[j] += __bfloat162float(R[j]);
-        }
-    }
-    if (p.accumulate) {
-        if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-                float r[8];
-                unpack8(*reinterpret_cast<const Bf16x8*>(C + j), r);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) acc[j + q] += r[q];
-            }
-        } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) acc[j] += __bfloat162float(C[j]);
-        }
-    }
-    if (full) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) *reinterpret_cast<Bf16x8*>(C + j) = pack8(acc + j);
-    } else {
-        _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) C[j] = __float2bfloat16_rn(acc[j]);
-    }
-}
-
-
-// Guarded 8-wide bf16 row read: vector when the group is inside the matrix, scalar at the ragged edge.
-__device__ __forceinline__ void load8_guard(const __nv_bfloat16* rowp, int n, int N, bool row_ok, float* f) {
-    if (row_ok && n + 8 <= N) {
-        unpack8(*reinterpret_cast<const Bf16x8*>(rowp + n), f);
-    } else {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) f[q] = (row_ok && n + q < N) ? __bfloat162float(rowp[n + q]) : 0.f;
-    }
-}
-
-// Which parts of the fused epilogue a kernel contains.  SPEC < 0: decided at run time from the parameters (one
-// kernel holds every combination -- large code whose instruction fetches miss in the caches while L2 is saturated
-// by the main loops).  SPEC >= 0: a bit set fixed at compile time, so the hot loop holds only what it executes:
-//   bit 0 bias | bits 1-2 act | bits 3-4 dact | bit 5 residual | bit 6 accumulate | bit 7 aux_out |
-//   bits 8-9 in_kind | bit 10 aux_ring | bit 11 fp32 output (split-K partials; nothing else set)
-constexpr int spec_pack(bool bias, int act, int dact, bool res, bool accum, bool aux, int in_kind, bool aux_ring) {
-    return int(bias) | (act << 1) | (dact << 3) | (int(res) << 5) | (int(accum) << 6) | (int(aux) << 7) |
-           (in_kind << 8) | (int(aux_ring) << 10);
-}
-template <int SPEC> struct Spec {
-    static constexpr bool RT = SPEC < 0;
-    __device__ __forceinline__ static bool bias(const EpiParams& p) { return RT ? p.bias != nullptr : (SPEC & 1) != 0; }
-    __device__ __forceinline__ static int act(const EpiParams& p) { return RT ? p.act : (SPEC >> 1) & 3; }
-    __device__ __forceinline__ static int dact(const EpiParams& p) { return RT ? p.dact : (SPEC >> 3) & 3; }
-    __device__ __forceinline__ static bool residual(const EpiParams& p) {
-        return RT ? p.residual != nullptr : ((SPEC >> 5) & 1) != 0;
-    }
-    __device__ __forceinline__ static bool accumulate(const EpiParams& p) {
-        return RT ? p.accumulate != 0 : ((SPEC >> 6) & 1) != 0;
-    }
-    __device__ __forceinline__ static bool aux_out(const EpiParams& p) {
-        return RT ? p.aux_out != nullptr : ((SPEC >> 7) & 1) != 0;
-    }
-    __device__ __forceinline__ static int in_kind(const EpiParams& p) { return RT ? p.in_kind : (SPEC >> 8) & 3; }
-    __device__ __forceinline__ static bool aux_ring(const EpiParams& p) {
-        return RT ? p.aux_ring != 0 : ((SPEC >> 10) & 1) != 0;
-    }
-    __device__ __forceinline__ static bool c_f32(const EpiParams& p) {
-        return RT ? p.c_f32 != 0 : ((SPEC >> 11) & 1) != 0;
-    }
-};
-
-// Fused epilogue arithmetic on 32 columns of one row (bf16 outputs).  `pre` receives the pre-activation.
-// `bias8` points at the 32 bias values of these columns in shared memory.  `in_raw` holds the 32 bf16 of this row
-// of the operand named by `in_kind` (1 activation input of the derivative, 2 residual, 3 old C), fetched by TMA
-// well ahead of use; any further operand is read from global memory here.
-template <int SPEC>
-__device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, float* pre, bool row_ok, long long offc,
-                                              long long offr, long long offa, int n, const __nv_bfloat16* bias8,
-                                              const uint4* in_raw, int in_kind) {
-    using S = Spec<SPEC>;
-    const int act = S::act(p), dact = S::dact(p);
-    if (S::bias(p)) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            float b[8];
-            unpack8(*reinterpret_cast<const uint4*>(bias8 + g * 8), b);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += b[q];
-        }
-    }
-    if (S::aux_out(p)) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) pre[j] = acc[j];
-    }
-    if (act == CME_ACT_RELU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
-    } else if (act == CME_ACT_GELU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = gelu_fast(acc[j]);
-    }
-    if (dact) {
-        const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + offa;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            float x[8];
-            if (in_kind == 1) unpack8(in_raw[g], x); else load8_guard(X, n + g * 8, p.N, row_ok, x);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                acc[g * 8 + q] = (dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
-                                                          : acc[g * 8 + q] * dgelu_fast(x[q]);
-        }
-    }
-    if (S::residual(p)) {
-        const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.residual) + offr;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            float x[8];
-            if (in_kind == 2) unpack8(in_raw[g], x); else load8_guard(R, n + g * 8, p.N, row_ok, x);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
-        }
-    }
-    if (S::accumulate(p)) {
-        const __nv_bfloat16* Cp = reinterpret_cast<const __nv_bfloat16*>(p.C) + offc;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            float x[8];
-            if (in_kind == 3) unpack8(in_raw[g], x); else load8_guard(Cp, n + g * 8, p.N, row_ok, x);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
-        }
-    }
-}
-
-template <int BN, bool A_MN, bool B_MN, bool SIMPLE, bool PAIR, int SPEC>
-__global__ void __launch_bounds__((Cfg<BN, PAIR, SIMPLE, SPEC>::THREADS), 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
-               const __grid_constant__ CUtensorMap tmI, const EpiParams p) {
-    using C = Cfg<BN, PAIR, SIMPLE, SPEC>;
-    using S = Spec<SPEC>;
-    static_assert(!PAIR || BN == 256, "CTA pairs use 256-wide tiles");
-    static_assert(!SIMPLE || SPEC < 0, "the plain epilogue has no compile-time variants");
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* staging = smem + C::STAGES * C::STAGE_BYTES;       // 1024-byte aligned
-    __nv_bfloat16* bias_smem = reinterpret_cast<__nv_bfloat16*>(staging + C::STAGING_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::STAGING_BYTES + C::BIAS_BYTES);
-    uint64_t* full_bar = bars;                       // [STAGES]  TMA -> MMA
-    uint64_t* empty_bar = bars + C::STAGES;          // [STAGES]  MMA -> TMA
-    uint64_t* tfull_bar = bars + 2 * C::STAGES;      // [2]       MMA -> epilogue
-    uint64_t* tempty_bar = bars + 2 * C::STAGES + 2; // [2]       epilogue -> MMA
-    uint64_t* in_bar = bars + 2 * C::STAGES + 4;     // [4 warps][NB]  TMA input loads -> epilogue warp
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + C::EPI_WARPS * C::NB);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        *abort_flag = 0;
-        for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&tfull_bar[b], 1);
-            mbar_init(&tempty_bar[b], (PAIR ? 2 : 1) * C::EPI_WARPS);   // one arrival per epilogue warp (of both CTAs)
-        }
-        for (int b = 0; b < C::EPI_WARPS * C::NB; ++b) mbar_init(&in_bar[b], 1);
-        fence_barrier_init();
-        prefetch_tmap(&tmA);
-        prefetch_tmap(&tmB);
-    }
-    if (warp == 1) {
-        if constexpr (PAIR) { tmem_alloc_pair(tmem_slot, C::TMEM_COLS); tmem_relinquish_pair(); }
-        else                { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
-    }
-    tc_fence_before();
-    // In a pair, the peer's barriers and TMEM must exist before anything is signalled across.
-    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
-    const int tile0 = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);
-    const int tile_step = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
-    constexpr int BMT = PAIR ? 2 * BM : BM;                  // rows of one scheduled tile
-    // Programmatic dependent launch: everything above (barrier init, TMEM allocation, descriptor prefetch) may run
-    // while the previous kernel of the stream is still finishing; its results are only touched after this point.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    const int tiles_mn = p.tiles_m * p.tiles_n;
-    const int total_tiles = tiles_mn * p.batch * p.splits;
-
-    if (warp == 0) {
-        // ------------------------------- TMA producer -------------------------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = tile0; tile < total_tiles && ok; tile += tile_step) {
-                const int mn = tile % tiles_mn, rest = tile / tiles_mn;
-                const int bidx = rest % p.batch, split = rest / p.batch;
-                const int m0 = (mn % p.tiles_m) * BMT + int(cta_rank) * BM;
-                const int n0 = (mn / p.tiles_m) * BN + int(cta_rank) * C::BN_LOCAL;
-                const int kb0 = split * p.kb_per_split;
-                const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
-                const int za = p.a_batched ? bidx : 0, zb = p.b_batched ? bidx : 0;
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
-                    uint8_t* sA = smem + stage * C::STAGE_BYTES;
-                    uint8_t* sB = sA + A_TILE_BYTES;
-                    if constexpr (PAIR) {
-                        // both CTAs' bytes are credited to the leader's barrier, which its MMA thread waits on
-                        if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * C::STAGE_BYTES);
-                        const uint32_t fb = mapa_u32(&full_bar[stage], 0);
-                        if (!A_MN) {
-                            tma_load_3d_pair(sA, &tmA, fb, kb * BK, m0, za);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < BM / 64; ++j)
-                                tma_load_3d_pair(sA + j * (64 * BK * 2), &tmA, fb, m0 + j * 64, kb * BK, za);
-                        }
-                        if (!B_MN) {
-                            tma_load_3d_pair(sB, &tmB, fb, kb * BK, n0, zb);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < C::BN_LOCAL / 64; ++j)
-                                tma_load_3d_pair(sB + j * (64 * BK * 2), &tmB, fb, n0 + j * 64, kb * BK, zb);
-                        }
-                    } else {
-                        mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_BYTES);
-                        if (!A_MN) {
-                            tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, m0, za);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < BM / 64; ++j)
-                                tma_load_3d(sA + j * (64 * BK * 2), &tmA, &full_bar[stage], m0 + j * 64, kb * BK, za);
-                        }
-                        if (!B_MN) {
-                            tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, n0, zb);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < BN / 64; ++j)
-                                tma_load_3d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK, zb);
-                        }
-                    }
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-                }
-            }
-            if (!ok) {
-                // Give copies that are still in flight time to land before shared memory is released.
-                for (int i = 0; i < 2000; ++i) __nanosleep(500);
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------- MMA issuer ---------------------------------
-        if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc = make_idesc(1 /*bf16*/, A_MN, B_MN, BMT, BN);
-            int stage = 0;
-            uint32_t phase = 0;
-            int it = 0;
-            bool ok = true;
-            for (int tile = tile0; tile < total_tiles && ok; tile += tile_step, ++it) {
-                const int rest = tile / tiles_mn;
-                const int split = rest / p.batch;
-                const int kb0 = split * p.kb_per_split;
-                const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
-                const int buf = it & 1;
-                const uint32_t acc_phase = (it >> 1) & 1;
-                if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sA = smem_u32(smem + stage * C::STAGE_BYTES);
-                    const uint32_t sB = sA + A_TILE_BYTES;
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // K-major: step 16 elements (32 bytes) inside the 128-byte row.
-                        // MN-major: step 16 k-rows of 128 bytes; 64-wide groups are BK*128 bytes apart.
-                        const uint64_t da = A_MN ? make_smem_desc(sA + k * UMMA_K * 128, BK * 128, 1024)
-                                                 : make_smem_desc(sA + k * UMMA_K * 2, 0, 1024);
-                        const uint64_t db = B_MN ? make_smem_desc(sB + k * UMMA_K * 128, BK * 128, 1024)
-                                                 : make_smem_desc(sB + k * UMMA_K * 2, 0, 1024);
-                        if constexpr (PAIR) mma_f16_ss_pair(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                        else                mma_f16_ss(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                    }
-                    // stage is free (in both CTAs of a pair) once these MMAs have read it
-                    if constexpr (PAIR) mma_commit_pair(&empty_bar[stage], 3); else mma_commit(&empty_bar[stage]);
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-                }
-                if (ok) {                               // accumulator complete
-                    if constexpr (PAIR) mma_commit_pair(&tfull_bar[buf], 3); else mma_commit(&tfull_bar[buf]);
-                }
-            }
-        }
-    } else {
-        // ------------------------------- epilogue -----------------------------------
-        const int quarter = warp & 3;                   // TMEM lanes [32*quarter, 32*quarter+32)
-        const bool vec_ok = (p.N % 8 == 0) && (p.ldc % 8 == 0) &&
-                            (!p.residual || p.ldres % 8 == 0) && ((!p.aux_in && !p.aux_out) || p.ldaux % 8 == 0);
-        int it = 0;
-        uint32_t store_cnt = 0;
-        bool ok = true;
-        // the accumulator goes back to the (leader's) MMA thread: one arrival per warp
-        auto acc_release = [&](int b) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(&tempty_bar[b], 0));
-                else                mbar_arrive(&tempty_bar[b]);
-            }
-        };
-        // Ring of this warp's epilogue buffers and the cursor of the input prefetch (fused bf16 epilogues only).  The
-        // cursor runs over (tile, 64-column chunk) in the order the warp will consume them, NB - 1 chunks ahead, and
-        // crosses tile boundaries, so the first chunks of a tile are already in flight while its main loop runs.
-        constexpr int ESETS = C::EPI_WARPS / 4;         // warp sets; set s takes the chunks c with c % ESETS == s
-        const int eset = (warp - 2) >> 2;
-        const int wslot = eset * 4 + quarter;
-        uint8_t* ring = staging + wslot * C::WARP_RING_BYTES;
-        uint64_t* my_in_bar = in_bar + wslot * C::NB;
-        // Bias values of three consecutive tiles, [3][256].  Every epilogue warp writes the same values (and reads
-        // only after its own writes); three slots because a warp may finish tile i + 1, and park the bias of tile
-        // i + 2, while another is still reading that of tile i.
-        __nv_bfloat16* bias_w = bias_smem;
-        const bool ring_epi = !SIMPLE && (SPEC >= 0 ? !S::c_f32(p) : (p.tma_store && !p.c_f32));
-        const int in_kind = ring_epi ? S::in_kind(p) : 0;
-        uint32_t slot = 0;                              // ring buffers handed out so far
-        int f_tile = tile0, f_c = eset;
-        uint32_t f_cnt = 0;
-        auto fetch_next = [&]() {
-            int fmn = 0, fn0 = 0;
-            while (f_tile < total_tiles) {              // next tile that has a chunk for this warp set
-                fmn = f_tile % tiles_mn;
-                fn0 = (fmn / p.tiles_m) * BN;
-                int nchf = (p.N - fn0 + 63) / 64;
-                nchf = nchf < BN / 64 ? nchf : BN / 64;
-                if (f_c < nchf) break;
-                f_c = eset;
-                f_tile += tile_step;
-            }
-            if (f_tile >= total_tiles) return;
-            const int fb = (f_tile / tiles_mn) % p.batch;
-            const int fm0 = (fmn % p.tiles_m) * BMT + int(cta_rank) * BM + quarter * 32;
-            if (lane == 0) {
-                const uint32_t b = f_cnt % C::NB;
-                mbar_arrive_expect_tx(&my_in_bar[b], 4096);
-                tma_load_3d(ring + b * 4096, &tmI, &my_in_bar[b], fn0 + f_c * 64, fm0, fb);
-            }
-            ++f_cnt;
-            f_c += ESETS;
-        };
-        if (in_kind) {
-            for (int i = 0; i < C::NB - 1; ++i) fetch_next();
-        }
-        const bool stage_bias = !SIMPLE && ring_epi && S::bias(p);
-        auto bias_fetch = [&](int t) {                  // this lane's 8 bias values of tile t (zeros past N)
-            float b8[8];
-            const int tn0 = ((t % tiles_mn) / p.tiles_m) * BN;
-            load8_guard(p.bias, tn0 + lane * 8, p.N, true, b8);
-            return pack8(b8);
-        };
-        if (stage_bias && tile0 < total_tiles) {
-            *reinterpret_cast<uint4*>(bias_w + lane * 8) = bias_fetch(tile0);
-            __syncwarp();
-        }
-        for (int tile = tile0; tile < total_tiles && ok; tile += tile_step, ++it) {
-            const int mn = tile % tiles_mn, rest = tile / tiles_mn;
-            const int bidx = rest % p.batch, split = rest / p.batch;
-            const int m0 = (mn % p.tiles_m) * BMT + int(cta_rank) * BM, n0 = (mn / p.tiles_m) * BN;
-            const int buf = it & 1;
-            const uint32_t acc_phase = (it >> 1) & 1;
-            const __nv_bfloat16* bias_s = bias_w + (it % 3) * 256;
-            // the next tile's bias values are requested now and parked in shared memory after this tile's chunks
-            uint4 bias_next = make_uint4(0, 0, 0, 0);
-            const bool have_next = stage_bias && tile + tile_step < total_tiles;
-            if (have_next) bias_next = bias_fetch(tile + tile_step);
-            if (!mbar_wait(&tfull_bar[buf], acc_phase, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
-            const long long zoff = (long long)(split * p.batch + bidx);
-            const long long offc = zoff * p.strideC + (long long)row * p.ldc;
-            const long long offr = (long long)bidx * p.strideC + (long long)row * p.ldres;
-            const long long offa = (long long)bidx * p.strideC + (long long)row * p.ldaux;
-            const uint32_t tmem_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
-            if constexpr (SIMPLE) {
-                // Plain bf16 output (no fused arithmetic): the TMEM loads of chunk c+1 are in flight while chunk c is
-                // converted and staged, and the accumulator is handed back to the MMA warp as soon as the last load
-                // has landed in registers, before the stores are issued.
-                uint32_t ra[64], rb[64];
-                int nchunks = (p.N - n0 + 63) / 64;
-                nchunks = nchunks < BN / 64 ? nchunks : BN / 64;
-                tmem_ld32(tmem_row, ra);
-                tmem_ld32(tmem_row + 32, ra + 32);
-#pragma unroll
-                for (int c2 = 0; c2 < BN / 64; ++c2) {
-                    if (c2 < nchunks) {
-                        uint32_t* cur = (c2 & 1) ? rb : ra;
-                        uint32_t* nxt = (c2 & 1) ? ra : rb;
-                        tmem_wait_ld();
-                        if (c2 + 1 < nchunks) {
-                            tmem_ld32(tmem_row + (c2 + 1) * 64, nxt);
-                            tmem_ld32(tmem_row + (c2 + 1) * 64 + 32, nxt + 32);
-                        } else {
-                            acc_release(buf);                       // accumulator fully read
-                        }
-                        uint8_t* sb = ring + (store_cnt & 1) * 4096;
-                        if (lane == 0) tma_store_wait_read<1>();
-                        __syncwarp();
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const uint4 v = make_uint4(
-                                f2_to_bf2(__uint_as_float(cur[8 * q]), __uint_as_float(cur[8 * q + 1])),
-                                f2_to_bf2(__uint_as_float(cur[8 * q + 2]), __uint_as_float(cur[8 * q + 3])),
-                                f2_to_bf2(__uint_as_float(cur[8 * q + 4]), __uint_as_float(cur[8 * q + 5])),
-                                f2_to_bf2(__uint_as_float(cur[8 * q + 6]), __uint_as_float(cur[8 * q + 7])));
-                            *reinterpret_cast<uint4*>(sb + lane * 128 + ((q ^ (lane & 7)) * 16)) = v;
-                        }
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) {
-                            tma_store_3d(&tmC, sb, n0 + c2 * 64, m0 + quarter * 32, (int)zoff);
-                            tma_store_commit();
-                        }
-                        ++store_cnt;
-                    }
-                }
-                continue;
-            }
-            if (SPEC < 0 && !p.tma_store) {
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_row + c * 32, r);
-                    tmem_wait_ld();
-                    const int n = n0 + c * 32;
-                    if (row < p.M && n < p.N) {
-                        float acc[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-                        epilogue_chunk(p, acc, offc, offr, offa, n, min(32, p.N - n), vec_ok);
-                    }
-                }
-            } else if (S::c_f32(p)) {
-                // fp32 output (split-K partials, fp32 C): 32 columns = one 128-byte staging row per TMA store
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    const int n = n0 + c * 32;
-                    if (n >= p.N) break;
-                    uint32_t r[32];
-                    tmem_ld32(tmem_row + c * 32, r);
-                    tmem_wait_ld();
-                    if (SPEC < 0 && p.accumulate) {
-                        const float* Cp = reinterpret_cast<const float*>(p.C) + offc;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (row < p.M && n + j < p.N) r[j] = __float_as_uint(__uint_as_float(r[j]) + Cp[n + j]);
-                    }
-                    uint8_t* sb = ring + (store_cnt & 1) * 4096;
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
-#pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        *reinterpret_cast<uint4*>(sb + lane * 128 + ((q ^ (lane & 7)) * 16)) =
-                            make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_3d(&tmC, sb, n, m0 + quarter * 32, (int)zoff);
-                        tma_store_commit();
-                    }
-                    ++store_cnt;
-                }
-            } else {
-                // bf16 output, fused epilogue: per 64-column chunk one ring buffer (two when the pre-activation also
-                // leaves through the ring).  With a TMA-fed input the buffer already holds this warp's 32 x 64 slice
-                // of it; every thread replaces its own 16-byte groups in place with the result.
-                const bool row_ok = row < p.M;
-                const bool aux_ring = S::aux_ring(p);
-                __nv_bfloat16* Xrow = (S::aux_out(p) && !aux_ring) ? reinterpret_cast<__nv_bfloat16*>(p.aux_out) + offa
-                                                                   : nullptr;
-#pragma unroll 1
-                for (int c2 = eset; c2 < BN / 64; c2 += ESETS) {
-                    const int n = n0 + c2 * 64;
-                    if (n >= p.N) break;
-                    uint8_t* sbC = ring + (slot % C::NB) * 4096;
-                    uint8_t* sbX = ring + ((slot + 1) % C::NB) * 4096;
-                    if (in_kind) {
-                        if (!mbar_wait(&my_in_bar[slot % C::NB], (slot / C::NB) & 1, abort_flag)) { ok = false; break; }
-                    }
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem_row + c2 * 64 + h * 32, r);
-                        uint4 in_raw[4];
-                        if (in_kind) {
-#pragma unroll
-                            for (int g = 0; g < 4; ++g)
-                                in_raw[g] = *reinterpret_cast<const uint4*>(sbC + lane * 128 +
-                                                                            (((h * 4 + g) ^ (lane & 7)) * 16));
-                        }
-                        tmem_wait_ld();
-                        float acc[32], pre[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-                        epilogue_math<SPEC>(p, acc, pre, row_ok, offc, offr, offa, n + h * 32,
-                                            bias_s + c2 * 64 + h * 32, in_raw, in_kind);
-                        if (h == 0 && !in_kind) {
-                            // buffers written by plain stores: their previous TMA stores must have been read out.
-                            // One bulk group per chunk; the aux variant takes two buffers per chunk.
-                            if (lane == 0) {
-                                if (aux_ring) tma_store_wait_read<C::AUX_ALLOW>();
-                                else tma_store_wait_read<C::NB - 1>();
-                            }
-                            __syncwarp();
-                        }
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            const int q = h * 4 + g;
-                            *reinterpret_cast<uint4*>(sbC + lane * 128 + ((q ^ (lane & 7)) * 16)) = pack8(acc + g * 8);
-                            if (aux_ring) {
-                                *reinterpret_cast<uint4*>(sbX + lane * 128 + ((q ^ (lane & 7)) * 16)) =
-                                    pack8(pre + g * 8);
-                            } else if (Xrow) {
-                                const int col = n + h * 32 + g * 8;
-                                if (row_ok && col + 8 <= p.N) {
-                                    *reinterpret_cast<uint4*>(Xrow + col) = pack8(pre + g * 8);
-                                } else if (row_ok) {
-#pragma unroll
-                                    for (int e2 = 0; e2 < 8; ++e2)
-                                        if (col + e2 < p.N) Xrow[col + e2] = __float2bfloat16_rn(pre[g * 8 + e2]);
-                                }
-                            }
-                        }
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_3d(&tmC, sbC, n, m0 + quarter * 32, (int)zoff);
-                        if (aux_ring) tma_store_3d(&tmX, sbX, n, m0 + quarter * 32, bidx);
-                        tma_store_commit();
-                    }
-                    slot += aux_ring ? 2 : 1;
-                    if (in_kind) {
-                        // refill the buffer stored one chunk ago with the chunk NB - 1 ahead
-                        if (lane == 0) tma_store_wait_read<1>();
-                        __syncwarp();
-                        fetch_next();
-                    }
-                }
-                if (!ok) break;
-            }
-            if (have_next) {
-                *reinterpret_cast<uint4*>(bias_w + ((it + 1) % 3) * 256 + lane * 8) = bias_next;
-                __syncwarp();
-            }
-            acc_release(buf);
-        }
-        if (!ok && in_kind) {
-            // input copies may still be in flight: give them time to land before shared memory is released
-            for (int i = 0; i < 2000; ++i) __nanosleep(500);
-        }
-        if (p.tma_store && lane == 0) tma_store_wait<0>();   // stores complete before shared memory goes away
-    }
-
-    __syncwarp();
-    tc_fence_before();
-    // A pair leaves together: neither CTA may exit while the other can still signal its barriers or read its tiles.
-    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, CME_ERR_TIMEOUT);
-    if (warp == 1) {
-        tc_fence_after();
-        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, C::TMEM_COLS); else tmem_dealloc(tmem_base, C::TMEM_COLS);
-    }
-}
 
 // Sums split-K partials in a fixed order and applies the accumulate flag:  C (+)= sum_s P[s].
 __global__ void splitk_reduce_kernel(const float* __restrict__ P, int splits, long long per_split, void* Cout,
@@ -832,56 +114,6 @@ int g_num_sms = 0;
 int* g_status = nullptr;     // device status word shared by all launches on this device
 
 int g_max_pairs = -1;        // co-resident CTA pairs of the pair kernels on this device (0: cluster launch unusable)
-
-template <int BN, bool A_MN, bool B_MN, bool SIMPLE, bool PAIR, int SPEC = -1>
-int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
-               const CUtensorMap& ti, const EpiParams& ep, int grid, cudaStream_t st) {
-    auto kern = gemm_tc_kernel<BN, A_MN, B_MN, SIMPLE, PAIR, SPEC>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        CME_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, PAIR, SIMPLE, SPEC>::SMEM_BYTES));
-        attr_set = true;
-    }
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(Cfg<BN, PAIR, SIMPLE, SPEC>::THREADS);
-    cfg.dynamicSmemBytes = Cfg<BN, PAIR, SIMPLE, SPEC>::SMEM_BYTES;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (PAIR) {
-        attr[1].id = cudaLaunchAttributeClusterDimension;
-        attr[1].val.clusterDim.x = 2;
-        attr[1].val.clusterDim.y = 1;
-        attr[1].val.clusterDim.z = 1;
-        cfg.numAttrs = 2;
-    }
-    CME_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, ti, ep));
-    CME_LAUNCH_CHECK();
-    return CME_OK;
-}
-
-template <int BN, bool SIMPLE, bool PAIR, int SPEC = -1>
-int launch_bn(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-              const CUtensorMap& tx, const CUtensorMap& ti, const EpiParams& ep, int grid, cudaStream_t st) {
-    if (!a_mn && !b_mn) return launch_cfg<BN, false, false, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
-    if (!a_mn && b_mn) return launch_cfg<BN, false, true, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
-    if (a_mn && !b_mn) return launch_cfg<BN, true, false, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
-    return launch_cfg<BN, true, true, SIMPLE, PAIR, SPEC>(ta, tb, tc, tx, ti, ep, grid, st);
-}
-
-// Epilogue combinations with a compile-time kernel (CTA-pair tiles only): the ones a transformer layer uses.
-constexpr int SPEC_BIAS = spec_pack(true, 0, 0, false, false, false, 0, false);
-constexpr int SPEC_BIAS_RES = spec_pack(true, 0, 0, true, false, false, 2, false);
-constexpr int SPEC_BIAS_GELU_AUX = spec_pack(true, CME_ACT_GELU, 0, false, false, true, 0, true);
-constexpr int SPEC_DGELU = spec_pack(false, 0, CME_ACT_GELU, false, false, false, 1, false);
-constexpr int SPEC_BIAS_RELU = spec_pack(true, CME_ACT_RELU, 0, false, false, false, 0, false);
-constexpr int SPEC_DRELU = spec_pack(false, 0, CME_ACT_RELU, false, false, false, 1, false);
-constexpr int SPEC_RES = spec_pack(false, 0, 0, true, false, false, 2, false);
-constexpr int SPEC_F32 = 1 << 11;
 
 // How many CTA pairs of the pair kernel can be resident at once (the persistent grid must not exceed it: a pair
 // that is not resident would only start when another has finished all of its tiles).
@@ -1066,34 +298,25 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     const bool a_mn = g->a_trans != 0, b_mn = g->b_trans == 0;
     const bool simple = ep.tma_store && !ep.c_f32 && !ep.bias && !ep.residual && !ep.aux_out && !ep.aux_in &&
                         !ep.act && !ep.dact && !ep.accumulate;
-    if (simple) {
-        if (pair) rc = launch_bn<256, true, true>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
-        else if (bn == 256) rc = launch_bn<256, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
-        else if (bn == 128) rc = launch_bn<128, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
-        else rc = launch_bn<64, true, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
-    } else {
-        int spec = -1;
+    int spec = -1;
+    if (!simple) {
         if (ep.tma_store && !ep.c_f32)
             spec = spec_pack(ep.bias != nullptr, ep.act, ep.dact, ep.residual != nullptr, ep.accumulate != 0,
                              ep.aux_out != nullptr, ep.in_kind, ep.aux_ring != 0);
         else if (ep.tma_store && ep.c_f32 && !ep.accumulate)
             spec = SPEC_F32;
-#define CME_SPEC_CASE(SP) \
-    if (pair && spec == SP) rc = launch_bn<256, false, true, SP>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream); else
-        CME_SPEC_CASE(SPEC_BIAS)
-        CME_SPEC_CASE(SPEC_BIAS_RES)
-        CME_SPEC_CASE(SPEC_BIAS_GELU_AUX)
-        CME_SPEC_CASE(SPEC_DGELU)
-        CME_SPEC_CASE(SPEC_BIAS_RELU)
-        CME_SPEC_CASE(SPEC_DRELU)
-        CME_SPEC_CASE(SPEC_RES)
-        CME_SPEC_CASE(SPEC_F32)
-#undef CME_SPEC_CASE
-        if (pair) rc = launch_bn<256, false, true>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
-        else if (bn == 256) rc = launch_bn<256, false, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
-        else if (bn == 128) rc = launch_bn<128, false, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
-        else rc = launch_bn<64, false, false>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
     }
+    // the instantiation with this tile, pairing and compile-time epilogue; else the run-time epilogue of that tile
+    rc = -1;
+    for (int attempt = 0; attempt < 2 && rc == -1; ++attempt) {
+        const int want = attempt == 0 ? spec : -1;
+#define CME_GEMM_TC_EXTERN(BN, SIMPLE, PAIR, SPEC)                                              \
+    if (rc == -1 && bn == BN && simple == SIMPLE && pair == PAIR && want == SPEC)               \
+        rc = launch_bn<BN, SIMPLE, PAIR, SPEC>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
+#include "gemm_tc_inst_list.h"
+#undef CME_GEMM_TC_EXTERN
+    }
+    CME_REQUIRE(rc != -1, CME_ERR_SHAPE, "gemm: no kernel instantiation for tile %d pair %d", bn, (int)pair);
     if (rc) return rc;
     if (splits > 1) {
         const long long per = (long long)g->batch * g->M * g->N;
