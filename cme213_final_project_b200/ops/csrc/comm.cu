@@ -77,7 +77,8 @@ __device__ __forceinline__ void mc_st(void* mc, uint4 v) {
 }
 
 // Flag layout per rank: [slot][MAX_RANKS] words; slot = 2 * bucket + phase.  Local bookkeeping (not symmetric):
-// ctl[3 * bucket + 0] = epoch of the last completed call, + 1 = CTAs done with the data phase, + 2 = abort marker.
+// ctl[3 * bucket + 0] = epoch of the last completed call, + 1 = CTAs of the current call done with the data phase,
+// + 2 = CTAs of the current call past the closing barrier (both counts return to zero when the call completes).
 //
 // Arrive: tell every peer that this rank reached `phase` of `bucket` in epoch `e`.  One thread per peer.
 __device__ __forceinline__ void signal_peers(const Peers& P, int slot, uint32_t e) {
@@ -216,7 +217,8 @@ __global__ void __launch_bounds__(COMM_THREADS) allreduce_kernel(const ArArgs a)
     __shared__ int s_last;
     if (threadIdx.x == 0) {
         const uint32_t done = atomicAdd(&a.ctl[3 * a.bucket + 1], 1u) + 1;
-        s_last = (done == e * gridDim.x);
+        s_last = (done == gridDim.x);
+        if (s_last) a.ctl[3 * a.bucket + 1] = 0;                    // per-call count: calls may differ in grid size
     }
     __syncthreads();
     // the last CTA to finish announces this rank; every CTA waits for all ranks before the kernel ends
@@ -226,7 +228,10 @@ __global__ void __launch_bounds__(COMM_THREADS) allreduce_kernel(const ArArgs a)
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t fin = atomicAdd(&a.ctl[3 * a.bucket + 2], 1u) + 1;
-        if (fin == e * gridDim.x) a.ctl[3 * a.bucket] = e;          // epoch advances once per call
+        if (fin == gridDim.x) {                                     // epoch advances once per call
+            a.ctl[3 * a.bucket + 2] = 0;
+            a.ctl[3 * a.bucket] = e;
+        }
     }
 }
 
@@ -311,7 +316,8 @@ __global__ void __launch_bounds__(COMM_THREADS) fused_rs_adamw_ag_kernel(const F
     __shared__ int s_last;
     if (threadIdx.x == 0) {
         const uint32_t done = atomicAdd(&a.ctl[3 * a.bucket + 1], 1u) + 1;
-        s_last = (done == e * gridDim.x);
+        s_last = (done == gridDim.x);
+        if (s_last) a.ctl[3 * a.bucket + 1] = 0;                    // per-call count: calls may differ in grid size
     }
     __syncthreads();
     if (s_last) signal_peers(P, slot1, e);
@@ -320,7 +326,10 @@ __global__ void __launch_bounds__(COMM_THREADS) fused_rs_adamw_ag_kernel(const F
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t fin = atomicAdd(&a.ctl[3 * a.bucket + 2], 1u) + 1;
-        if (fin == e * gridDim.x) a.ctl[3 * a.bucket] = e;
+        if (fin == gridDim.x) {
+            a.ctl[3 * a.bucket + 2] = 0;
+            a.ctl[3 * a.bucket] = e;
+        }
     }
 }
 

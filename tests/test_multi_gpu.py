@@ -58,6 +58,24 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert status.item() == 0 and waited.item() < 0.1e9
 
 
+def test_allreduce_calls_on_one_bucket_may_change_their_grid_size():
+    """Consecutive calls on the same bucket with different CTA counts (a size sweep) must each complete their
+    barriers: the per-call CTA counters start from zero every time."""
+    from cme213_final_project_b200.parallel.fused_sync import PeerComm
+    from cme213_final_project_b200.parallel.symm import LocalPeers
+    dev = torch.device("cuda", 0)
+    comm = PeerComm(dev, max_buckets=2, budget_ms=200.0, single=True)
+    src = LocalPeers(torch.randn(1 << 16, device=dev).to(torch.bfloat16))
+    dst = LocalPeers(torch.zeros(1 << 16, device=dev, dtype=torch.bfloat16))
+    for ctas, n in ((1, 512), (1, 512), (4, 8192), (3, 8192), (16, 1 << 16), (1, 512)):
+        for algo in ("one_shot", "two_shot"):
+            dst.tensor.zero_()
+            comm.allreduce(src, dst, n, algo=algo, bucket=0, ctas=ctas)
+            torch.cuda.synchronize()
+            assert comm.check_status() == 0
+            assert torch.equal(dst.tensor[:n], src.tensor[:n])
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_peer_memory_collectives_and_fused_sync():
     n = min(torch.cuda.device_count(), 8)
