@@ -67,7 +67,18 @@ class NativeEngine:
             self.lr_dev = torch.full((1,), optim.lr, dtype=torch.float32, device=self.device)
             self.loss_dev = torch.zeros(1, dtype=torch.float32, device=self.device)
             self.normsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+            # early loss read-back: after the forward of every step the loss and a sequence number are copied to
+            # pinned host memory, so a caller can read the step's loss while backward is still running
+            self.seq_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+            self.seq_host = torch.zeros(1, dtype=torch.int32).pin_memory()
             self._norm_partial = torch.empty(1024, dtype=torch.float32, device=self.device)
+        self.seq_expected = 0          # steps handed to the device so far (the trainer counts graph replays too)
+        self._loss_host_dev, self._seq_host_dev = ctypes.c_void_p(), ctypes.c_void_p()
+        ops._check(self.lib.cme_host_device_ptr(ctypes.c_void_p(self.loss_host.data_ptr()),
+                                                ctypes.byref(self._loss_host_dev)))
+        ops._check(self.lib.cme_host_device_ptr(ctypes.c_void_p(self.seq_host.data_ptr()),
+                                                ctypes.byref(self._seq_host_dev)))
         nd = [(s.offset, s.offset + s.numel) for s in self.layout.specs if s.kind not in ("weight", "embed")]
         self.nodecay = torch.tensor(nd, dtype=torch.int64, device=self.device).reshape(-1, 2)
         self.step_count = 0
@@ -243,7 +254,31 @@ class NativeEngine:
         for i, (x, y) in enumerate(zip(tokens, targets)):
             self.forward(x, y, loss_weight=1.0 / accum, accumulate_loss=i > 0, grad_scale=gs)
             last = i == accum - 1
+            if last:
+                self._publish_loss()
             self.backward(bucket_callback if last else None, buckets if last else None, accumulate=i > 0)
+
+    def _publish_loss(self) -> None:
+        """Enqueue (capturable) one single-thread kernel that bumps the sequence number and writes the loss, then the
+        sequence number, into pinned host memory: the host sees the new number only after the loss has landed."""
+        with torch.cuda.device(self.device):
+            ops._check(self.lib.cme_publish_loss(ops._p(self.loss_dev), ops._p(self.seq_dev), self._loss_host_dev,
+                                                 self._seq_host_dev, ops._stream()))
 
     def read_loss(self) -> float:
         return float(self.loss_dev.item())
+
+    def wait_loss(self, timeout_s: float = 30.0) -> float:
+        """Loss of the most recently enqueued step, as soon as its forward pass has finished: polls the pinned
+        sequence number instead of synchronising the stream, so backward and the optimizer keep running and the
+        caller can already enqueue the next step.  Falls back to a full synchronisation after ``timeout_s``."""
+        import time
+        want = self.seq_expected
+        t0 = time.perf_counter()
+        spins = 0
+        while int(self.seq_host.item()) < want:
+            spins += 1
+            if (spins & 1023) == 0 and time.perf_counter() - t0 > timeout_s:
+                torch.cuda.synchronize(self.device)
+                return float(self.loss_dev.item())
+        return float(self.loss_host.item())

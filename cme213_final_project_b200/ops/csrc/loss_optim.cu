@@ -276,6 +276,29 @@ CME_API int cme_grad_normsq(int dtype, const void* g, long long n, float* partia
     return CME_OK;
 }
 
+// Early loss read-back: bump the sequence number, write the loss and then the sequence number straight into
+// pinned, device-mapped host memory.  A host thread that sees the new sequence number also sees the loss.
+__global__ void publish_loss_kernel(const float* loss, int* seq, volatile float* host_loss, volatile int* host_seq) {
+    const int s = *seq + 1;
+    *seq = s;
+    *host_loss = *loss;
+    __threadfence_system();
+    *host_seq = s;
+}
+
+// Device-side address of a pinned host allocation (once per buffer, outside stream capture).
+CME_API int cme_host_device_ptr(void* host, void** dev) {
+    CME_CUDA(cudaHostGetDevicePointer(dev, host, 0));
+    return CME_OK;
+}
+
+CME_API int cme_publish_loss(const float* loss, int* seq, void* host_loss_dev, void* host_seq_dev, void* stream) {
+    publish_loss_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(loss, seq, static_cast<volatile float*>(host_loss_dev),
+                                                           static_cast<volatile int*>(host_seq_dev));
+    CME_LAUNCH_CHECK();
+    return CME_OK;
+}
+
 CME_API int cme_step_inc(int* step, void* stream) {
     step_inc_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(step);
     CME_LAUNCH_CHECK();

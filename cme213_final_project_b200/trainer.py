@@ -56,11 +56,27 @@ class Trainer:
         """One optimizer step over ``len(tokens)`` micro-batches (``grad_accum`` of them)."""
         if isinstance(tokens, torch.Tensor):
             tokens, targets = [tokens], [targets]
+        if hasattr(self.model, "seq_expected"):
+            self.model.seq_expected += 1
+        mdev = getattr(self.model, "device", None)
+        if (self.graphed is None and len(tokens) and not tokens[0].is_cuda and mdev is not None
+                and torch.device(mdev).type == "cuda"):
+            tokens, targets = self._stage(tokens, targets)       # host (pinned) batches: one async copy each
         if self.graphed is not None:
             self.graphed(tokens, targets)
             self.steps += 1
         else:
             self._step(tokens, targets)
+
+    def _stage(self, tokens, targets):
+        dev = self.model.device
+        if getattr(self, "_stage_x", None) is None or self._stage_x.shape != (len(tokens), tokens[0].numel()):
+            self._stage_x = torch.empty(len(tokens), tokens[0].numel(), dtype=torch.int32, device=dev)
+            self._stage_y = torch.empty_like(self._stage_x)
+        for i, (x, y) in enumerate(zip(tokens, targets)):
+            self._stage_x[i].copy_(x.reshape(-1), non_blocking=True)
+            self._stage_y[i].copy_(y.reshape(-1), non_blocking=True)
+        return [self._stage_x[i] for i in range(len(tokens))], [self._stage_y[i] for i in range(len(tokens))]
 
     def _step(self, tokens: Sequence[torch.Tensor], targets: Sequence[torch.Tensor]) -> None:
         m, d = self.model, self.dist
