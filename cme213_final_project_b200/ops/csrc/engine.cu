@@ -128,7 +128,10 @@ size_t carve(Engine& e, char* base) {
     e.ln_scratch = (float*)take((size_t)cme_layernorm_bwd_blocks((int)BT) * 2 * D * 4);
     e.col_scratch = (float*)take((size_t)(cme_colsum_splits((int)BT, (int)D) + cme_colsum_splits((int)BT, (int)FF)) *
                                  widest * 4);
-    e.gemm_ws_bytes = 64ll << 20;
+    // split-K partials (fp32): room for four splits of the widest activation-gradient product, e.g. the LM-head
+    // input gradient whose 192 pair tiles fill 74 CTA pairs unevenly unless K is split three ways
+    const long long want_ws = 4ll * (long long)BT * (long long)widest * 4ll;
+    e.gemm_ws_bytes = want_ws > (64ll << 20) ? want_ws : (64ll << 20);
     e.gemm_ws = take((size_t)e.gemm_ws_bytes);
     return off;
 }

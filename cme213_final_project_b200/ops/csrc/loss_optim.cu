@@ -10,6 +10,7 @@
 // captured CUDA graph of the step stays correct on every replay (the reference bakes the host-computed
 // bias corrections into its captured launch).
 #include "common.h"
+#include <cuda_fp16.h>
 
 namespace {
 
@@ -102,6 +103,84 @@ cross_entropy_bf16_vec_kernel(const __nv_bfloat16* __restrict__ logits, const in
                 x[j] = p * grad_scale;
             }
             g[i] = pack8(x);
+        }
+    }
+}
+
+// Same contract, for rows of at most CEV_THREADS * CER_MAXV 16-byte vectors (53248 bf16: GPT-2's padded vocabulary
+// fits): the row lives in registers from its single read to its single write.  Pass 1 finds the maximum, pass 2
+// evaluates exp(x - max) once per element and keeps it as fp16 in the registers that held the logits (values in
+// (0, 1], 11 significant bits -- finer than the bf16 the gradient is stored in), pass 3 only scales.  One
+// exponential per element instead of two: the kernel is otherwise bound by the special-function unit as much as by
+// memory (100 K exponentials per row).
+constexpr int CER_MAXV = 13;
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_h2(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+__global__ void __launch_bounds__(CEV_THREADS)
+cross_entropy_bf16_reg_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                              __nv_bfloat16* dlogits, float* __restrict__ losses, int V, long long ld,
+                              float grad_scale, float prob_eps) {
+    __shared__ float scratch[32];
+    const long long off = (long long)blockIdx.x * ld;
+    const uint4* row = reinterpret_cast<const uint4*>(logits + off);
+    const int nv = V / 8;
+    uint4 r[CER_MAXV];
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < CER_MAXV; ++k) {
+        const int i = threadIdx.x + k * CEV_THREADS;
+        if (i < nv) {
+            r[k] = row[i];
+            float x[8];
+            unpack8(r[k], x);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, x[j]);
+        }
+    }
+    const float row_max = block_max(m, scratch);
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < CER_MAXV; ++k) {
+        if (threadIdx.x + k * CEV_THREADS < nv) {
+            float x[8];
+            unpack8(r[k], x);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { x[j] = __expf(x[j] - row_max); s += x[j]; }
+            r[k] = make_uint4(pack_h2(x[0], x[1]), pack_h2(x[2], x[3]), pack_h2(x[4], x[5]), pack_h2(x[6], x[7]));
+        }
+    }
+    const float denom = block_sum(s, scratch);
+    const float inv = 1.f / (denom + prob_eps);
+    int tgt = targets[blockIdx.x];
+    tgt = tgt < 0 ? 0 : (tgt >= V ? V - 1 : tgt);
+    if (threadIdx.x == 0) {
+        const float xt = __bfloat162float(logits[off + tgt]);
+        const float p = __expf(xt - row_max) * inv;
+        losses[blockIdx.x] = prob_eps > 0.f ? -logf(p + prob_eps) : -(xt - row_max - logf(denom));
+    }
+    __syncthreads();                 // the target's logit has been read before the row is overwritten in place
+    if (dlogits) {
+        uint4* g = reinterpret_cast<uint4*>(dlogits + off);
+        const float sc = inv * grad_scale;
+#pragma unroll
+        for (int k = 0; k < CER_MAXV; ++k) {
+            const int i = threadIdx.x + k * CEV_THREADS;
+            if (i < nv) {
+                const float2 a = unpack_h2(r[k].x), b = unpack_h2(r[k].y), c = unpack_h2(r[k].z), d = unpack_h2(r[k].w);
+                float x[8] = {a.x * sc, a.y * sc, b.x * sc, b.y * sc, c.x * sc, c.y * sc, d.x * sc, d.y * sc};
+                const int t = tgt - i * 8;
+                if (t >= 0 && t < 8) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (j == t) x[j] -= grad_scale;
+                }
+                g[i] = pack8(x);
+            }
         }
     }
 }
@@ -239,7 +318,11 @@ CME_API int cme_cross_entropy(int dtype, const void* logits, const int* targets,
     const bool vec = dtype == CME_BF16 && V % 8 == 0 && ld % 8 == 0 && V >= 2048 &&
                      (reinterpret_cast<uintptr_t>(logits) & 15) == 0 &&
                      (!dlogits || (reinterpret_cast<uintptr_t>(dlogits) & 15) == 0);
-    if (vec) {
+    if (vec && V / 8 <= CEV_THREADS * CER_MAXV) {
+        cross_entropy_bf16_reg_kernel<<<rows, CEV_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets,
+                                                                   (__nv_bfloat16*)dlogits, losses, V, ld, grad_scale,
+                                                                   prob_eps);
+    } else if (vec) {
         const size_t row_bytes = (size_t)V * 2;
         const int cache = row_bytes <= 110 * 1024;          // two blocks per SM still fit
         static bool attr = false;
@@ -284,6 +367,7 @@ __global__ void publish_loss_kernel(const float* loss, int* seq, volatile float*
     *host_loss = *loss;
     __threadfence_system();
     *host_seq = s;
+    __threadfence_system();      // push the number out now: inside a CUDA graph nothing else flushes it before the end
 }
 
 // Device-side address of a pinned host allocation (once per buffer, outside stream capture).

@@ -176,6 +176,33 @@ def test_training_reduces_loss_and_bucket_callbacks_fire_in_arena_order():
     assert eng.read_loss() < first - 0.5
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_early_loss_readback_and_host_batches(graph):
+    """``Trainer.step`` takes pinned host batches; ``wait_loss`` returns the step's loss from pinned memory as soon
+    as the forward pass has produced it and agrees with the synchronising read, in eager steps and graph replays."""
+    from cme213_final_project_b200.config import RunConfig, preset
+    from cme213_final_project_b200.data import synthetic_batches
+    from cme213_final_project_b200.parallel.dist import DistributedContext
+    from cme213_final_project_b200.trainer import Trainer
+    cfg, optim = preset("tiny-gpt")
+    eng, _ = _mk(cfg, optim, strict=False)
+    ctx = DistributedContext()
+    ctx.device = torch.device("cuda", 0)
+    tr = Trainer(eng, ctx, RunConfig(cuda_graph=graph), optim)
+    if graph:
+        assert tr.enable_cuda_graph(warmup_steps=2)
+    x, y = synthetic_batches(cfg.vocab_size, cfg.seq_len, cfg.batch_size, 6, seed=0)
+    x, y = x.pin_memory(), y.pin_memory()
+    seen = []
+    for i in range(6):
+        tr.step([x[i]], [y[i]])
+        early = eng.wait_loss()
+        torch.cuda.synchronize()
+        assert early == eng.read_loss()
+        seen.append(early)
+    assert len(set(seen)) > 1 and all(math.isfinite(v) for v in seen)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("layout,causal", [("flat", False), ("split", True), ("split", False)])
 @pytest.mark.parametrize("B,H,T,HD", [(2, 4, 64, 32), (1, 2, 100, 64), (2, 1, 37, 128)])
