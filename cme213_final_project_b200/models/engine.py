@@ -208,12 +208,14 @@ class NativeEngine:
 
     def logits(self) -> torch.Tensor:
         """A copy of the logits buffer (after ``forward`` with targets it holds d(logits))."""
-        n = self.cfg.tokens_per_step * self.cfg.vocab_size
+        self.lib.cme_engine_logits_ld.restype = ctypes.c_longlong
+        ld = int(self.lib.cme_engine_logits_ld(self._h))        # rows are padded to a multiple of 8 elements
+        n = self.cfg.tokens_per_step * ld
         ptr = self.lib.cme_engine_logits(self._h)
         out = torch.empty(n, dtype=self.dtype, device=self.device)
         ops._check(self.lib.cme_copy_d2d(ops._p(out), ctypes.c_void_p(ptr), ctypes.c_longlong(n * out.element_size()),
                                          ops._stream()))
-        return out.view(self.cfg.tokens_per_step, self.cfg.vocab_size)
+        return out.view(self.cfg.tokens_per_step, ld)[:, :self.cfg.vocab_size].contiguous()
 
     def update(self, grad_scale: float = 1.0, lr: Optional[float] = None) -> None:
         """Unfused optimizer path: global norm (if clipping) then Adam / AdamW over the whole arena.

@@ -72,6 +72,8 @@ struct Engine {
     std::vector<char*> x;          // L+1 residual-stream buffers
     std::vector<LayerAct> la;
     char *xf, *logits;
+    long long VL;                  // row pitch of the logits buffer: the vocabulary rounded up to 8 elements, so every
+                                   // row starts 16-byte aligned and the LM-head products run on the TMA-fed GEMM
     float *meanf, *rstdf, *losses;
     // backward temporaries
     char *dxa, *dxb, *dff, *dln, *dqkv, *dattn;
@@ -113,7 +115,8 @@ size_t carve(Engine& e, char* base) {
     }
     e.xf = d.final_ln ? take(BT * D * es) : nullptr;
     e.meanf = (float*)take(BT * 4); e.rstdf = (float*)take(BT * 4);
-    e.logits = take(BT * (size_t)d.V * es);
+    e.VL = ((long long)d.V + 7) / 8 * 8;
+    e.logits = take(BT * (size_t)e.VL * es);
     e.losses = (float*)take(BT * 4);
     e.dxa = take(BT * D * es); e.dxb = take(BT * D * es);
     e.dff = take(BT * FF * es);
@@ -212,6 +215,7 @@ CME_API int cme_engine_bind(void* h, void* params, void* grads, void* workspace,
 CME_API void cme_engine_destroy(void* h) { delete static_cast<Engine*>(h); }
 
 CME_API void* cme_engine_logits(void* h) { return static_cast<Engine*>(h)->logits; }
+CME_API long long cme_engine_logits_ld(void* h) { return static_cast<Engine*>(h)->VL; }
 CME_API void* cme_engine_activation(void* h, int layer, int which) {
     Engine* e = static_cast<Engine*>(h);
     if (which == 0) return e->x[layer];
@@ -265,10 +269,10 @@ CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, f
                               BT, D, d.ln_eps, st));
         xlast = e.xf;
     }
-    if (d.tied) TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.tok), D, 1, e.logits, V));
-    else        TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.Wout), V, 0, e.logits, V));
+    if (d.tied) TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.tok), D, 1, e.logits, e.VL));
+    else        TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.Wout), V, 0, e.logits, e.VL));
     if (targets)
-        TRY(cme_cross_entropy(dt, e.logits, targets, e.logits, e.losses, loss_out, BT, V, V, grad_scale, d.prob_eps,
+        TRY(cme_cross_entropy(dt, e.logits, targets, e.logits, e.losses, loss_out, BT, V, e.VL, grad_scale, d.prob_eps,
                               loss_weight, accumulate_loss, st));
     return CME_OK;
 }
@@ -289,11 +293,11 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
     char* dx_other = e.dxb;
     // ---- output head
     if (d.tied) {
-        TRY(gemm(e, st, BT, D, V, e.logits, V, 0, e.P(e.gs.tok), D, 0, dx, D));                 // dX = dL @ tok
-        TRY(gemm(e, st, V, D, BT, e.logits, V, 1, xlast, D, 0, e.G(e.gs.tok), D, accumulate));  // dtok = dL^T @ X
+        TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.P(e.gs.tok), D, 0, dx, D));                 // dX = dL @ tok
+        TRY(gemm(e, st, V, D, BT, e.logits, e.VL, 1, xlast, D, 0, e.G(e.gs.tok), D, accumulate));  // dtok = dL^T @ X
     } else {
-        TRY(gemm(e, st, BT, D, V, e.logits, V, 0, e.P(e.gs.Wout), V, 1, dx, D));                // dX = dL @ Wout^T
-        TRY(gemm(e, st, D, V, BT, xlast, D, 1, e.logits, V, 0, e.G(e.gs.Wout), V, accumulate)); // dWout = X^T @ dL
+        TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.P(e.gs.Wout), V, 1, dx, D));                // dX = dL @ Wout^T
+        TRY(gemm(e, st, D, V, BT, xlast, D, 1, e.logits, e.VL, 0, e.G(e.gs.Wout), V, accumulate)); // dWout = X^T @ dL
         emit();
     }
     if (d.final_ln) {

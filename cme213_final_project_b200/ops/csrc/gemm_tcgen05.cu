@@ -151,9 +151,10 @@ int gemm_tcgen05_supported(const CmeGemm* g) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (!al16(g->A) || !al16(g->B) || !al16(g->C)) return 0;
     if (g->lda % 8 || g->ldb % 8 || g->strideA % 8 || g->strideB % 8) return 0;
-    // inner extents must make a legal map (>= one 16-byte unit) -- tiny shapes go to the SIMT kernel
+    // Extents need not be multiples of the 16-byte unit: row pitches are (checked above), and a box that reaches
+    // past an extent reads zeros.  Degenerate extents go to the SIMT kernel.
     const long long innerA = g->a_trans ? g->M : g->K, innerB = g->b_trans ? g->K : g->N;
-    if (innerA % 8 || innerB % 8) return 0;
+    if (innerA < 8 || innerB < 8) return 0;
     if (g->c_dtype == CME_F32 && (g->act || g->dact || g->residual || g->aux_out)) return 0;
     return 1;
 }
