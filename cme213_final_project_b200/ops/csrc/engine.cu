@@ -72,6 +72,8 @@ struct Engine {
     std::vector<char*> x;          // L+1 residual-stream buffers
     std::vector<LayerAct> la;
     char *xf, *logits;
+    char* wout_pad = nullptr;      // untied output projection [D, V] re-pitched to [D, VL] when V is not a multiple of
+                                   // 8 (bf16): refreshed at the start of every forward, read by forward and dX
     long long VL;                  // row pitch of the logits buffer: the vocabulary rounded up to 8 elements, so every
                                    // row starts 16-byte aligned and the LM-head products run on the TMA-fed GEMM
     float *meanf, *rstdf, *losses;
@@ -118,6 +120,7 @@ size_t carve(Engine& e, char* base) {
     e.VL = ((long long)d.V + 7) / 8 * 8;
     e.logits = take(BT * (size_t)e.VL * es);
     e.losses = (float*)take(BT * 4);
+    e.wout_pad = (!d.tied && d.dtype == CME_BF16 && e.VL != d.V) ? take(D * (size_t)e.VL * es) : nullptr;
     e.dxa = take(BT * D * es); e.dxb = take(BT * D * es);
     e.dff = take(BT * FF * es);
     e.dln = take(BT * D * es);
@@ -269,8 +272,15 @@ CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, f
                               BT, D, d.ln_eps, st));
         xlast = e.xf;
     }
-    if (d.tied) TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.tok), D, 1, e.logits, e.VL));
-    else        TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.Wout), V, 0, e.logits, e.VL));
+    if (d.tied) {
+        TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.tok), D, 1, e.logits, e.VL));
+    } else if (e.wout_pad) {
+        CME_CUDA(cudaMemcpy2DAsync(e.wout_pad, (size_t)e.VL * e.es, e.P(e.gs.Wout), (size_t)V * e.es, (size_t)V * e.es, D,
+                                   cudaMemcpyDeviceToDevice, st));
+        TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.wout_pad, e.VL, 0, e.logits, e.VL));
+    } else {
+        TRY(gemm(e, st, BT, V, D, xlast, D, 0, e.P(e.gs.Wout), V, 0, e.logits, e.VL));
+    }
     if (targets)
         TRY(cme_cross_entropy(dt, e.logits, targets, e.logits, e.losses, loss_out, BT, V, e.VL, grad_scale, d.prob_eps,
                               loss_weight, accumulate_loss, st));
@@ -296,7 +306,8 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.P(e.gs.tok), D, 0, dx, D));                 // dX = dL @ tok
         TRY(gemm(e, st, V, D, BT, e.logits, e.VL, 1, xlast, D, 0, e.G(e.gs.tok), D, accumulate));  // dtok = dL^T @ X
     } else {
-        TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.P(e.gs.Wout), V, 1, dx, D));                // dX = dL @ Wout^T
+        if (e.wout_pad) TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.wout_pad, e.VL, 1, dx, D));   // dX = dL @ Wout^T
+        else TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.P(e.gs.Wout), V, 1, dx, D));
         TRY(gemm(e, st, D, V, BT, xlast, D, 1, e.logits, e.VL, 0, e.G(e.gs.Wout), V, accumulate)); // dWout = X^T @ dL
         emit();
     }
