@@ -21,7 +21,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from cme213_final_project_b200.parallel.comm_model import fit_alpha_beta          # noqa: E402
 from cme213_final_project_b200.parallel.dist import DistributedContext            # noqa: E402
 from cme213_final_project_b200.parallel.fused_sync import PeerComm                # noqa: E402
-from cme213_final_project_b200.parallel.symm import SymmetricBuffer               # noqa: E402
+from cme213_final_project_b200.parallel.symm import LocalPeers, SymmetricBuffer   # noqa: E402
 
 
 def timed(fn, iters, dev, sync):
@@ -29,15 +29,18 @@ def timed(fn, iters, dev, sync):
         fn()
     sync()
     ts = []
+    multi = dist.is_initialized() and dist.get_world_size() > 1
     for _ in range(iters):
-        dist.barrier(device_ids=[dev.index])
+        if multi:
+            dist.barrier(device_ids=[dev.index])
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         fn()
         e.record()
         e.synchronize()
         t = torch.tensor([s.elapsed_time(e)], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ts.append(t.item())
     return statistics.median(ts)
 
@@ -53,29 +56,58 @@ def main():
     a = ap.parse_args()
     ctx = DistributedContext().init(backend="nccl", device="cuda")
     dev, W, R = ctx.device, ctx.world_size, ctx.rank
-    comm = PeerComm(dev, max_buckets=4, budget_ms=10000.0)
-    sync = lambda: (torch.cuda.synchronize(), dist.barrier(device_ids=[dev.index]))
+    comm = PeerComm(dev, max_buckets=4, budget_ms=2000.0)
+    multi = dist.is_initialized() and W > 1
+    sync = lambda: (torch.cuda.synchronize(), dist.barrier(device_ids=[dev.index]) if multi else None)
+    # one rank (a single GPU): plain buffers stand in for the symmetric ones; the kernels run their world-of-one case
+    mkbuf = (lambda n, dt: SymmetricBuffer(n, dt, dev)) if multi else \
+            (lambda n, dt: LocalPeers(torch.zeros(n, dtype=dt, device=dev)))
     rows = []
     for dtype, es in ((torch.bfloat16, 2), (torch.float32, 4)):
         max_n = a.max_mb * (1 << 20) // es
-        src, dst = SymmetricBuffer(max_n, dtype, dev), SymmetricBuffer(max_n, dtype, dev)
+        src, dst = mkbuf(max_n, dtype), mkbuf(max_n, dtype)
         src.tensor.normal_(generator=torch.Generator(device=dev).manual_seed(1000 + R))
         nccl_buf = src.tensor.clone()
         algos = ["one_shot", "two_shot"] + (["nvls"] if src.multicast_ptr else [])
+        fused = None
+        if dtype == torch.bfloat16:
+            # the training path's kernel: reduce-scatter + scale + AdamW on this rank's fp32 shard + all-gather of the
+            # bf16 parameters (src = gradient arena, dst = parameter arena)
+            import ctypes
+            from cme213_final_project_b200 import ops
+            master = torch.zeros(max_n, dtype=torch.float32, device=dev)
+            am, av = torch.zeros_like(master), torch.zeros_like(master)
+            step = torch.ones(1, dtype=torch.int32, device=dev)
+            lr = torch.full((1,), 1e-4, dtype=torch.float32, device=dev)
+            use_nvls = int(bool(src.multicast_ptr and dst.multicast_ptr))
+
+            def fused(n, ctas):
+                ops._check(comm.lib.cme_comm_fused_adamw(
+                    W, R, src.c_ptrs, dst.c_ptrs, comm.flags.c_ptrs, ctypes.c_void_p(src.multicast_ptr),
+                    ctypes.c_void_p(dst.multicast_ptr), ctypes.c_longlong(0), ctypes.c_longlong(n), ops._p(master),
+                    ops._p(am), ops._p(av), ops._p(step), ops._p(lr), ctypes.c_float(0.9), ctypes.c_float(0.95),
+                    ctypes.c_float(1e-8), ctypes.c_float(0.1), ctypes.c_float(1.0 / W), None, 0, use_nvls, 3, ctas,
+                    ops._p(comm.ctl), ops._p(comm.status), ctypes.c_double(comm.budget_ms),
+                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
         nbytes = a.min_kb * 1024
         while nbytes <= a.max_mb * (1 << 20):
             n = max(nbytes // es, (16 // es) * W)
             n -= n % ((16 // es) * W)
             rec = {"dtype": str(dtype).split(".")[-1], "bytes": n * es, "world": W}
-            rec["nccl_ms"] = timed(lambda: dist.all_reduce(nccl_buf[:n]), a.iters, dev, sync)
+            rec["nccl_ms"] = timed(lambda: dist.all_reduce(nccl_buf[:n]) if multi else None, a.iters, dev, sync)
             for i, algo in enumerate(algos):
                 if algo == "one_shot" and n * es > (32 << 20):
                     continue
                 ctas = min(a.ctas, max(1, n * es // 4096))
                 rec[algo + "_ms"] = timed(lambda: comm.allreduce(src, dst, n, algo=algo, bucket=i, ctas=ctas), a.iters,
                                           dev, sync)
+            if fused is not None:
+                fc = min(4 * 148, max(1, n * es // 4096))
+                rec["fused_adamw_ms"] = timed(lambda: fused(n, fc), a.iters, dev, sync)
+                # bytes over NVLink per GPU and direction: (W-1)/W of the gradients in, the same of the parameters out
+                rec["fused_adamw_link_gbs"] = n * es * (W - 1) / W / (rec["fused_adamw_ms"] * 1e-3) / 1e9
             assert comm.check_status() == 0
-            best = min((rec[k], k) for k in rec if k.endswith("_ms") and k != "nccl_ms")
+            best = min((rec[k], k) for k in rec if k.endswith("_ms") and k not in ("nccl_ms", "fused_adamw_ms"))
             rec["best"] = best[1][:-3]
             bus = lambda ms: rec["bytes"] * 2 * (W - 1) / W / (ms * 1e-3) / 1e9
             rec["best_busbw_gbs"], rec["nccl_busbw_gbs"] = bus(best[0]), bus(rec["nccl_ms"])

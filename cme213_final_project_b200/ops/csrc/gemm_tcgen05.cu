@@ -177,9 +177,8 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     }
     int tiles_m = cme_cdiv(g->M, BM);
     const int num_kb = cme_cdiv(g->K, BK);
-    // Tile width and K splits: minimise  waves x k-blocks per unit x cost(bn)  (+ fixed per-tile and
-    // per-split overheads).  cost(bn) per 16-deep MMA is max(tensor time bn/2, shared-memory read time
-    // (128 + bn)/4) in clocks: 128 / 64 / 48 for bn = 256 / 128 / 64.
+    // Tile shape and K splits: minimise  waves x k-blocks per unit x cost(tile)  (+ fixed per-tile and per-split
+    // overheads), with measured clocks per 16-deep MMA step for each tile shape (table below).
     const bool plain_epi = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;
     // force_bn: 64 / 128 / 256 = tile width on one CTA; 512 = the 256 x 256 tile on a CTA pair
     int bn = g->force_bn, splits = g->force_splits;

@@ -143,3 +143,57 @@ def test_auto_dispatch_falls_back_for_vocab_65():
     a, b = _mk((256, 128), 21), _mk((128, 65), 22)          # the reference's output head shape
     out = ops.gemm(a, b)
     _check(out, a.float() @ b.float())
+
+
+@pytest.mark.parametrize("a_trans,b_trans", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (384, 320, 192), (1000, 520, 328), (2304, 256, 4096)])
+def test_cta_pair_tiles(M, N, K, a_trans, b_trans):
+    """force_bn=512: the 256 x 256 tile on a CTA pair (cta_group::2), including edges where the second CTA of a
+    pair has only padding rows or columns, and many tiles per pair."""
+    ops = _ops()
+    a = _mk((K, M) if a_trans else (M, K), 31)
+    b = _mk((N, K) if b_trans else (K, N), 32)
+    out = ops.gemm(a, b, a_trans=a_trans, b_trans=b_trans, backend="tcgen05", force_bn=512)
+    assert ops.gemm_check_status() == 0
+    _check(out, _ref(a, b, a_trans, b_trans))
+
+
+@pytest.mark.parametrize("bn", [64, 128, 512])
+def test_compile_time_epilogue_variants(bn):
+    """Each fused epilogue that has its own kernel instantiation (per tile width), against the same arithmetic in
+    fp32; two output tiles per CTA in every direction so the prefetch ring crosses tile boundaries."""
+    ops = _ops()
+    M, N, K = 1024, 1536 if bn == 512 else 512, 192
+    a, b = _mk((M, K), 41), _mk((K, N), 42)
+    bias, res, x = _mk((N,), 43), _mk((M, N), 44), _mk((M, N), 45)
+    ref = a.float() @ b.float()
+    refb = ref + bias.float()
+    gelu = lambda t: torch.nn.functional.gelu(t, approximate="tanh")
+    kw = dict(backend="tcgen05", force_bn=bn)
+    _check(ops.gemm(a, b, bias=bias, **kw), refb)
+    _check(ops.gemm(a, b, bias=bias, act="relu", **kw), torch.relu(refb))
+    _check(ops.gemm(a, b, residual=res, **kw), ref + res.float())
+    _check(ops.gemm(a, b, bias=bias, residual=res, **kw), refb + res.float())
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    _check(ops.gemm(a, b, bias=bias, act="gelu", aux_out=pre, **kw), gelu(refb))
+    _check(pre, refb)
+    xf = x.float().requires_grad_(True)
+    gelu(xf).sum().backward()
+    _check(ops.gemm(a, b, dact="gelu", aux_in=x, **kw), ref * xf.grad)
+    _check(ops.gemm(a, b, dact="relu", aux_in=x, **kw), ref * (x.float() > 0))
+    acc = res.clone()
+    ops.gemm(a, b, out=acc, accumulate=True, **kw)
+    _check(acc, ref + res.float())
+    _check(ops.gemm(a, b, out_dtype=torch.float32, force_splits=2, **kw).float(), ref, tol=1e-3)
+    assert ops.gemm_check_status() == 0
+
+
+def test_output_narrower_than_a_vector_unit_on_the_tensor_core_path():
+    """[M, 65] logits from a tied [65, D] embedding: K-major operands with legal pitches, an output whose rows are
+    not 16-byte addressable (direct-store epilogue, no TMA store)."""
+    ops = _ops()
+    M, V, D = 512, 65, 128
+    x, w = _mk((M, D), 53), _mk((V, D), 52)
+    logits = ops.gemm(x, w, b_trans=True, backend="tcgen05")
+    assert ops.gemm_check_status() == 0
+    _check(logits, x.float() @ w.float().t())
