@@ -340,7 +340,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint64_t* p_free = bars + 8;               // dV's MMAs of a block have read P
     uint64_t* dqs_full = bars + 9;             // dQ staging written (512 arrivals)
     uint64_t* dqs_free = bars + 10;            // dQ staging read by the reduce-store
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* s_free = bars + 11;              // S and dP of a query block are in registers (512 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,6 +361,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_init(p_free, 1);
         mbar_init(dqs_full, 512);
         mbar_init(dqs_free, 1);
+        mbar_init(s_free, 512);
         fence_barrier_init();
     }
     if (warp == BWD_MMA_WARP) { tmem_alloc(tmem_slot, BWD_TMEM_COLS); tmem_relinquish(); }
@@ -414,13 +416,17 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             for (int it = 0; it < n_it && ok; ++it) {
                 const int st = it & 1;
-                if (!mbar_wait(p_ready, it & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                if (it + 1 < n_it) {       // next block's scores first: the softmax warps can start on them at once
+                if (it + 1 < n_it) {
+                    // The next block's S and dP are issued as soon as this block's have been read out of TMEM (the
+                    // gradient warps signal that right after their loads), so they are computed while the warps
+                    // do this block's arithmetic instead of after it.
+                    if (!mbar_wait(s_free, it & 1, abort_flag)) { ok = false; break; }
                     if (!mbar_wait(&q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     issue_s(it + 1);
                 }
+                if (!mbar_wait(p_ready, it & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
                 const uint64_t pd = pMN0, sd = desc_add(sMN0, st * 2 * TILE_BYTES),
                                sk = desc_add(sK0, st * 2 * TILE_BYTES), qd = desc_add(qMN0, st * TILE_BYTES),
                                od = desc_add(oMN0, st * TILE_BYTES);
@@ -484,12 +490,20 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_arrive(dqs_full);
             return true;
         };
+        // row statistics of a query block are fetched one block ahead: their global-memory latency must not sit
+        // between the arrival of S and the first exponential
+        auto row_stats = [&](int it2, float& l2, float& d2) {
+            const int qc2 = min((i_begin + it2) * BQ + row, p.T - 1);
+            l2 = p.lse[(long long)bh * p.T + qc2] * LOG2E;
+            d2 = p.delta[(long long)bh * p.T + qc2];
+        };
+        float lse2_n = 0.f, dl_n = 0.f;
+        if (n_it > 0) row_stats(0, lse2_n, dl_n);
         for (int it = 0; it < n_it && ok; ++it) {
             const int qi0 = (i_begin + it) * BQ;
             const int q = qi0 + row;
-            const int qc = min(q, p.T - 1);
-            const float lse2 = p.lse[(long long)bh * p.T + qc] * LOG2E;
-            const float dl = p.delta[(long long)bh * p.T + qc];
+            const float lse2 = lse2_n, dl = dl_n;
+            if (it + 1 < n_it) row_stats(it + 1, lse2_n, dl_n);
             uint8_t* bufP = sP;
             uint8_t* bufS = sdS + (it & 1) * 2 * TILE_BYTES;
             if (!mbar_wait(s_full, it & 1, abort_flag)) { ok = false; break; }
@@ -499,6 +513,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tmem_ld32(tmem_S + lane_addr + cg * 32, rs);
             tmem_ld32(tmem_dP + lane_addr + cg * 32, rd);
             tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(s_free);                        // S and dP may be overwritten by the next block's products
             if (it > 0 && !mbar_wait(p_free, (it - 1) & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
