@@ -474,7 +474,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         bool ok = true;
         // dQ of a finished query block: this warp's 16 columns go to the fp32 staging tile (swizzled for TMA); the
         // store warp then adds the tile into the global accumulator with one bulk reduce per 32-column half
-        auto flush_dq = [&](int f) -> bool {
+        // `signal`: false leaves the proxy fence and the arrival on dqs_full to the caller, who then covers the P / dS
+        // stores of the current block and this staging write with one fence
+        auto flush_dq = [&](int f, bool signal) -> bool {
             if (!mbar_wait(dq_full, f & 1, abort_flag)) return false;
             tc_fence_after();
             uint32_t t[16];
@@ -486,8 +488,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int g = 0; g < 4; ++g)
                 *reinterpret_cast<uint4*>(atom + swz(row, (cg & 1) * 4 + g)) =
                     make_uint4(t[4 * g], t[4 * g + 1], t[4 * g + 2], t[4 * g + 3]);
-            fence_proxy_async();
-            mbar_arrive(dqs_full);
+            if (signal) {
+                fence_proxy_async();
+                mbar_arrive(dqs_full);
+            }
             return true;
         };
         // row statistics of a query block are fetched one block ahead: their global-memory latency must not sit
@@ -535,12 +539,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             // the previous block's dQ is read here, after this block's arithmetic, so that its MMAs had the whole
             // time of that arithmetic to finish
-            if (it > 0 && !flush_dq(it - 1)) { ok = false; break; }
+            if (it > 0 && !flush_dq(it - 1, false)) { ok = false; break; }
             tc_fence_before();
-            fence_proxy_async();
+            fence_proxy_async();                        // one fence for P, dS and the dQ staging tile
+            if (it > 0) mbar_arrive(dqs_full);
             mbar_arrive(p_ready);
         }
-        if (ok && n_it > 0) ok = flush_dq(n_it - 1);
+        if (ok && n_it > 0) ok = flush_dq(n_it - 1, true);
         // dK, dV of this key block (all MMAs are complete: the last dq_full wait covered them); this warp stores its
         // 16 columns (32 bytes = one full sector per row) straight from registers
         if (ok) {
