@@ -1,8 +1,10 @@
 #!/bin/bash
 # Builds the unmodified reference single-GPU trainer for sm_100, one binary per hidden size, under baseline/_ref.
 # Usage: baseline/build_reference.sh [/path/to/reference/FINAL_CLEAN_CODE_]
+#        (default: $CME213_REFERENCE_DIR/FINAL_CLEAN_CODE_, else the checkout next to this repository)
 set -e
-SRC=${1:-/root/reference/FINAL_CLEAN_CODE_}
+HERE="$(cd "$(dirname "$0")" && pwd)"
+SRC=${1:-${CME213_REFERENCE_DIR:-$HERE/../../reference}/FINAL_CLEAN_CODE_}
 DST="$(cd "$(dirname "$0")" && pwd)/_ref"
 mkdir -p "$DST"
 cp -r "$SRC/Makefile" "$SRC/include" "$SRC/src" "$SRC/inp.txt" "$DST/"

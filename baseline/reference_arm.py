@@ -1,7 +1,7 @@
 """Reference arm of bench.py: runs the UNMODIFIED reference trainer through its own command line.
 
 The reference (prince71753/CME213-Final-Project) is a Makefile project, not a Python package:
-``pip install --no-index --target baseline/_ref /root/reference`` fails with "Neither 'setup.py' nor
+``pip install --no-index --target baseline/_ref <reference checkout>`` fails with "Neither 'setup.py' nor
 'pyproject.toml' found".  Instead ``baseline/build_reference.sh`` copies its sources (``Makefile include/ src/
 inp.txt``, untouched) into ``baseline/_ref`` and runs its own ``make`` with ``CUDA_ARCH=-arch=sm_100`` once per
 hidden size (the model shape is a compile-time macro there).  Only the single-process binary can be built: the

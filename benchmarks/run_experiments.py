@@ -198,7 +198,8 @@ def main():
     ap.add_argument("--strong", action="store_true")
     ap.add_argument("--synthetic", action="store_true")
     ap.add_argument("--cuda-graph", action="store_true")
-    ap.add_argument("--data", default="/root/reference/FINAL_CLEAN_CODE_/inp.txt")
+    from cme213_final_project_b200.data import reference_corpus_path
+    ap.add_argument("--data", default=reference_corpus_path())
     ap.add_argument("--out", default="results")
     a, extra = ap.parse_known_args()          # anything not recognised here is passed to the trainer
     a.extra = [e for e in extra if e != "--"]

@@ -134,3 +134,13 @@ class ShardPlan:
 
     def batch_index(self, step: int, rank: int) -> int:
         return step * self.world_size + rank
+
+
+def reference_corpus_path() -> str:
+    """Where the reference's tiny-Shakespeare corpus (``FINAL_CLEAN_CODE_/inp.txt``) is expected:
+    ``$CME213_REFERENCE_DIR`` if set, else a ``reference`` checkout next to this repository.  The file may not
+    exist; callers fall back to synthetic tokens."""
+    import os
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    root = os.environ.get("CME213_REFERENCE_DIR") or os.path.join(os.path.dirname(here), "reference")
+    return os.path.join(root, "FINAL_CLEAN_CODE_", "inp.txt")

@@ -229,110 +229,45 @@ ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
     }
 }
 
-// dx = rstd * (dy*g - mean(dy*g) - xhat * mean(dy*g*xhat)) [+ dres];  per-block partial dgamma / dbeta.
-// Grid-stride over rows; each lane owns fixed columns so its partial sums stay in registers.
-template <typename T, bool VEC>
+// Fallback for row lengths the vector kernel does not take (not a multiple of the vector width, or too long):
+// same arithmetic with scalar accesses, per-warp partial d(gamma) / d(beta) rows in shared memory.
+template <typename T>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
               const float* __restrict__ mean, const float* __restrict__ rstd, const T* __restrict__ dres,
               T* __restrict__ dx, float* __restrict__ partial /*[gridDim.x][2][D]*/, int rows, int D) {
-    constexpr int W = VecOf<T>::N;
     extern __shared__ float sm[];     // [LN_WARPS][2][D]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if constexpr (VEC) {
-        // Each warp keeps its partial d(gamma) / d(beta) rows in shared memory (its own [2][D] slice), so only the
-        // row being processed lives in registers and several blocks fit on an SM.
-        const int nvec = D / W;
-        constexpr int SLOTS = LN_MAX_VEC * W * 32;          // per-warp accumulator slots (>= D), bank-conflict free
-        float* wdg = sm + (size_t)warp * 2 * SLOTS;
-        float* wdb = wdg + SLOTS;
-        for (int c = lane; c < 2 * SLOTS; c += 32) wdg[c] = 0.f;
-        __syncwarp();
-        for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
-            const long long off = (long long)row * D;
-            const float mu = mean[row], rs = rstd[row];
-            float xh[LN_MAX_VEC][W], dyg[LN_MAX_VEC][W];
-            float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-            for (int i = 0; i < LN_MAX_VEC; ++i) {
-                const int v = lane + 32 * i;
-                if (v < nvec) {
-                    float xv[W], dv[W], g[W];
-                    load_vec<T>(x + off + v * W, xv);
-                    load_vec<T>(dy + off + v * W, dv);
-                    load_vec<T>(gamma + v * W, g);
-#pragma unroll
-                    for (int j = 0; j < W; ++j) {
-                        xh[i][j] = (xv[j] - mu) * rs;
-                        dyg[i][j] = dv[j] * g[j];
-                        s1 += dyg[i][j];
-                        s2 += dyg[i][j] * xh[i][j];
-                        // slot (i*W + j)*32 + lane: consecutive lanes hit consecutive banks
-                        wdg[(i * W + j) * 32 + lane] += dv[j] * xh[i][j];
-                        wdb[(i * W + j) * 32 + lane] += dv[j];
-                    }
-                }
-            }
-            s1 = warp_sum(s1) / D;
-            s2 = warp_sum(s2) / D;
-#pragma unroll
-            for (int i = 0; i < LN_MAX_VEC; ++i) {
-                const int v = lane + 32 * i;
-                if (v < nvec) {
-                    float o[W];
-#pragma unroll
-                    for (int j = 0; j < W; ++j) o[j] = rs * (dyg[i][j] - s1 - xh[i][j] * s2);
-                    if (dres) {
-                        float t[W];
-                        load_vec<T>(dres + off + v * W, t);
-#pragma unroll
-                        for (int j = 0; j < W; ++j) o[j] += t[j];
-                    }
-                    store_vec<T>(dx + off + v * W, o);
-                }
-            }
+    for (int c = threadIdx.x; c < LN_WARPS * 2 * D; c += blockDim.x) sm[c] = 0.f;
+    __syncthreads();
+    for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
+        const long long off = (long long)row * D;
+        const float mu = mean[row], rs = rstd[row];
+        float s1 = 0.f, s2 = 0.f;
+        for (int c = lane; c < D; c += 32) {
+            const float xh = (to_f32<T>(x[off + c]) - mu) * rs;
+            const float dv = to_f32<T>(dy[off + c]);
+            const float d = dv * to_f32<T>(gamma[c]);
+            s1 += d;
+            s2 += d * xh;
+            sm[(warp * 2 + 0) * D + c] += dv * xh;
+            sm[(warp * 2 + 1) * D + c] += dv;
         }
-    } else {
-        for (int c = threadIdx.x; c < LN_WARPS * 2 * D; c += blockDim.x) sm[c] = 0.f;
-        __syncthreads();
-        for (int row = blockIdx.x * LN_WARPS + warp; row < rows; row += gridDim.x * LN_WARPS) {
-            const long long off = (long long)row * D;
-            const float mu = mean[row], rs = rstd[row];
-            float s1 = 0.f, s2 = 0.f;
-            for (int c = lane; c < D; c += 32) {
-                const float xh = (to_f32<T>(x[off + c]) - mu) * rs;
-                const float dv = to_f32<T>(dy[off + c]);
-                const float d = dv * to_f32<T>(gamma[c]);
-                s1 += d;
-                s2 += d * xh;
-                sm[(warp * 2 + 0) * D + c] += dv * xh;
-                sm[(warp * 2 + 1) * D + c] += dv;
-            }
-            s1 = warp_sum(s1) / D;
-            s2 = warp_sum(s2) / D;
-            for (int c = lane; c < D; c += 32) {
-                const float xh = (to_f32<T>(x[off + c]) - mu) * rs;
-                const float d = to_f32<T>(dy[off + c]) * to_f32<T>(gamma[c]);
-                float o = rs * (d - s1 - xh * s2);
-                if (dres) o += to_f32<T>(dres[off + c]);
-                dx[off + c] = from_f32<T>(o);
-            }
+        s1 = warp_sum(s1) / D;
+        s2 = warp_sum(s2) / D;
+        for (int c = lane; c < D; c += 32) {
+            const float xh = (to_f32<T>(x[off + c]) - mu) * rs;
+            const float d = to_f32<T>(dy[off + c]) * to_f32<T>(gamma[c]);
+            float o = rs * (d - s1 - xh * s2);
+            if (dres) o += to_f32<T>(dres[off + c]);
+            dx[off + c] = from_f32<T>(o);
         }
     }
     __syncthreads();
     for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) {
         float s = 0.f;
-        if constexpr (VEC) {
-            constexpr int SLOTS = LN_MAX_VEC * W * 32;
-            const int which = c >= D, col = c - which * D;
-            const int v = col / W, j = col % W;
-            const int slot = ((v >> 5) * W + j) * 32 + (v & 31);
 #pragma unroll
-            for (int w = 0; w < LN_WARPS; ++w) s += sm[(size_t)w * 2 * SLOTS + which * SLOTS + slot];
-        } else {
-#pragma unroll
-            for (int w = 0; w < LN_WARPS; ++w) s += sm[w * 2 * D + c];
-        }
+        for (int w = 0; w < LN_WARPS; ++w) s += sm[w * 2 * D + c];
         partial[(long long)blockIdx.x * 2 * D + c] = s;
     }
 }
@@ -429,7 +364,7 @@ int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, co
         if (rc) return rc;
     } else {
         const size_t smem = (size_t)LN_WARPS * 2 * D * sizeof(float);
-        auto k = ln_bwd_kernel<T, false>;
+        auto k = ln_bwd_kernel<T>;
         if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         k<<<nblocks, LN_WARPS * 32, smem, st>>>((const T*)dy, (const T*)x, (const T*)g, mean, rstd, (const T*)dres,
                                                 (T*)dx, scratch, rows, D);

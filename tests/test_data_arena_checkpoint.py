@@ -38,7 +38,8 @@ def test_batcher_chunks_and_cursor():
 
 def test_reference_corpus_counts():
     import os
-    path = "/root/reference/FINAL_CLEAN_CODE_/inp.txt"
+    from cme213_final_project_b200.data import reference_corpus_path
+    path = reference_corpus_path()
     if not os.path.exists(path):
         pytest.skip("corpus not present")
     from cme213_final_project_b200.data import read_file

@@ -84,7 +84,8 @@ def test_comm_worker_error_reaches_the_trainer():
 
 def test_cli_trains_on_cpu_and_writes_checkpoint(tmp_path):
     ck = str(tmp_path / "ck.bin")
-    corpus = "/root/reference/FINAL_CLEAN_CODE_/inp.txt"
+    from cme213_final_project_b200.data import reference_corpus_path
+    corpus = reference_corpus_path()
     args = [sys.executable, "-m", "cme213_final_project_b200.train", "--device", "cpu", "--epochs", "1", "--max-steps", "3",
             "--hidden", "32", "--batch-size", "4", "--trace-trajectory", "--save-checkpoint", ck, "--log-every", "1"]
     args += [corpus] if os.path.exists(corpus) else ["--synthetic"]
