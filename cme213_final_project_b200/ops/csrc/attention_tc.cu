@@ -131,6 +131,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+    pdl_wait();        // barrier set-up and TMEM allocation above may overlap the tail of the previous kernel
 
     if (warp == 4) {
         if (lane == 0) {
@@ -580,6 +581,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 __global__ void dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int T, int nh,
                                   long long sb, long long sh, long long st, float scale, long long rows, int nkb,
                                   int causal) {
+    pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per 8 elements
     if (i >= rows * (HD / 8)) return;
     const long long r = i / (HD / 8);
@@ -688,7 +690,7 @@ int attention_tc_fwd(const CmeAttn* a, cudaStream_t st) {
     }
     FwdParams p{a->T, a->nh, a->causal, a->scale * LOG2E, a->lse, g_attn_status};
     dim3 grid(cme_cdiv(a->T, BQ), a->nb * a->nh);
-    attn_fwd_tc_kernel<<<grid, FWD_THREADS, FWD_SMEM, st>>>(mq, mk, mv, mo, p);
+    CME_CUDA(cme_launch_dependent(attn_fwd_tc_kernel, grid, dim3(FWD_THREADS), (size_t)FWD_SMEM, st, mq, mk, mv, mo, p));
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
@@ -727,8 +729,9 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
     attn_bwd_tc_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, mdo, mdq, p);
     CME_LAUNCH_CHECK();
     const long long nthreads = rows * (HD / 8);
-    dq_convert_kernel<<<cme_cdiv(nthreads, 256), 256, 0, st>>>(a->dq_accum, (__nv_bfloat16*)a->dq, a->T, a->nh, a->sb,
-                                                              a->sh, a->st, a->scale, rows, 1, 0);
+    CME_CUDA(cme_launch_dependent(dq_convert_kernel, dim3(cme_cdiv(nthreads, 256)), dim3(256), 0, st,
+                                  (const float*)a->dq_accum, (__nv_bfloat16*)a->dq, a->T, a->nh, a->sb, a->sh, a->st,
+                                  a->scale, rows, 1, 0));
     CME_LAUNCH_CHECK();
     return CME_OK;
 }

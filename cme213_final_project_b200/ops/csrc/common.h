@@ -4,6 +4,7 @@
 // process; here every exported function returns a status code (0 = ok) and records a message that the
 // Python side turns into an exception, so a failed launch never takes the interpreter down.
 #pragma once
+#include <utility>
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -55,6 +56,29 @@ extern long long g_cme_launches;
 static inline int cme_cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 #ifdef __CUDACC__
+
+// Programmatic dependent launch for the many short kernels of a step.  A kernel launched through
+// cme_launch_dependent may be scheduled while the previous kernel of the stream is still draining; it must call
+// pdl_wait() before it touches anything that kernel wrote (first statement of every such kernel).  The wait
+// returns once the previous kernel has completed and its writes are visible, so results are unchanged; what is
+// saved is the launch gap between consecutive kernels.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t cme_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                        Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 __host__ __device__ __forceinline__ int cme_cdiv_dev(int a, int b) { return (a + b - 1) / b; }
 

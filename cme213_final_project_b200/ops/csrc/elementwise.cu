@@ -90,6 +90,7 @@ dact_colsum_kernel(const T* __restrict__ dout, const T* __restrict__ pre, T* __r
                    int rows, int cols, int act) {
     constexpr int W = Vw<T>::N;
     __shared__ float sm[32][8 * W + 1];
+    pdl_wait();
     const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
     const int c0 = (blockIdx.x * 8 + cl) * W;
     float s[W];
@@ -144,6 +145,7 @@ __global__ void dact_colsum_scalar_kernel(const T* dout, const T* pre, T* g, flo
 }
 template <typename T>
 __global__ void colsum_finalize_kernel(const float* partial, int splits, int cols, T* out, int accumulate) {
+    pdl_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= cols) return;
     float s = 0.f;
@@ -317,7 +319,8 @@ int dact_colsum_t(const void* dout, const void* pre, void* g, void* dbias, float
                      (!g || aligned16((const T*)g));
     if (vec) {
         dim3 grid(cme_cdiv(cols, 8 * W), splits);
-        dact_colsum_kernel<T><<<grid, 256, 0, st>>>((const T*)dout, (const T*)pre, (T*)g, scratch, rows, cols, act);
+        CME_CUDA(cme_launch_dependent(dact_colsum_kernel<T>, grid, dim3(256), 0, st, (const T*)dout, (const T*)pre, (T*)g,
+                                      scratch, rows, cols, act));
     } else {
         dim3 grid(cme_cdiv(cols, 128), splits);
         dact_colsum_scalar_kernel<T><<<grid, 128, 0, st>>>((const T*)dout, (const T*)pre, (T*)g, scratch, rows, cols,
@@ -325,7 +328,8 @@ int dact_colsum_t(const void* dout, const void* pre, void* g, void* dbias, float
     }
     CME_LAUNCH_CHECK();
     if (dbias) {
-        colsum_finalize_kernel<T><<<cme_cdiv(cols, 256), 256, 0, st>>>(scratch, splits, cols, (T*)dbias, accumulate);
+        CME_CUDA(cme_launch_dependent(colsum_finalize_kernel<T>, dim3(cme_cdiv(cols, 256)), dim3(256), 0, st,
+                                      (const float*)scratch, splits, cols, (T*)dbias, accumulate));
         CME_LAUNCH_CHECK();
     }
     return CME_OK;

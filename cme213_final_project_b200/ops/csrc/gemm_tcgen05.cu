@@ -43,6 +43,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ P, int splits, lo
 __global__ void splitk_reduce_vec4_kernel(const float4* __restrict__ P, int splits, long long per_split4, void* Cout,
                                           int c_f32, int accumulate, int M, int N4, long long ldc, long long strideC,
                                           int batch) {
+    pdl_wait();
     const long long total = (long long)batch * M * N4;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -327,9 +328,9 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         if (vec) {
             const long long per4 = per / 4;
             const int blocks = (int)((per4 + 255) / 256 < 8 * g_num_sms ? (per4 + 255) / 256 : 8 * g_num_sms);
-            splitk_reduce_vec4_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(g->workspace), splits,
-                                                                  per4, g->C, f32, g->accumulate, g->M, g->N / 4,
-                                                                  g->ldc, g->strideC, g->batch);
+            CME_CUDA(cme_launch_dependent(splitk_reduce_vec4_kernel, dim3(blocks), dim3(256), 0, stream,
+                                          reinterpret_cast<const float4*>(g->workspace), splits, per4, g->C, (int)f32,
+                                          g->accumulate, g->M, g->N / 4, g->ldc, g->strideC, g->batch));
         } else {
             const int blocks = (int)((per + 255) / 256 < 4096 ? (per + 255) / 256 : 4096);
             splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(g->workspace), splits, per,

@@ -42,6 +42,7 @@ ln_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ 
               const T* __restrict__ beta, T* __restrict__ y, float* __restrict__ mean_out,
               float* __restrict__ rstd_out, int rows, int D, float eps) {
     constexpr int W = VecOf<T>::N;
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -141,6 +142,7 @@ ln_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
     constexpr int W = VecOf<T>::N;
     constexpr int SLOTS = NV * W * 32;
     extern __shared__ float sm[];     // [LN_WARPS][2][SLOTS]
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvec = D / W;
     float* wdg = sm + (size_t)warp * 2 * SLOTS;
@@ -237,6 +239,7 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
               const float* __restrict__ mean, const float* __restrict__ rstd, const T* __restrict__ dres,
               T* __restrict__ dx, float* __restrict__ partial /*[gridDim.x][2][D]*/, int rows, int D) {
     extern __shared__ float sm[];     // [LN_WARPS][2][D]
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int c = threadIdx.x; c < LN_WARPS * 2 * D; c += blockDim.x) sm[c] = 0.f;
     __syncthreads();
@@ -279,6 +282,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int D, T* dgamma, T* dbeta, int accumulate) {
     __shared__ float sm[16][17];
+    pdl_wait();
     const int cx = threadIdx.x & 15, ry = threadIdx.x >> 4;
     const int c = blockIdx.x * 16 + cx;
     float s = 0.f;
@@ -312,11 +316,11 @@ int ln_fwd_t(const void* a, const void* b, void* r, const void* g, const void* b
     const bool vec = (D % W == 0) && (D / W <= 32 * LN_MAX_VEC);
     const int grid = cme_cdiv(rows, LN_WARPS);
     if (vec)
-        ln_fwd_kernel<T, true><<<grid, LN_WARPS * 32, 0, st>>>((const T*)a, (const T*)b, (T*)r, (const T*)g,
-                                                               (const T*)be, (T*)y, mean, rstd, rows, D, eps);
+        CME_CUDA(cme_launch_dependent(ln_fwd_kernel<T, true>, dim3(grid), dim3(LN_WARPS * 32), 0, st, (const T*)a,
+                                      (const T*)b, (T*)r, (const T*)g, (const T*)be, (T*)y, mean, rstd, rows, D, eps));
     else
-        ln_fwd_kernel<T, false><<<grid, LN_WARPS * 32, 0, st>>>((const T*)a, (const T*)b, (T*)r, (const T*)g,
-                                                                (const T*)be, (T*)y, mean, rstd, rows, D, eps);
+        CME_CUDA(cme_launch_dependent(ln_fwd_kernel<T, false>, dim3(grid), dim3(LN_WARPS * 32), 0, st, (const T*)a,
+                                      (const T*)b, (T*)r, (const T*)g, (const T*)be, (T*)y, mean, rstd, rows, D, eps));
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
@@ -343,7 +347,8 @@ int ln_bwd_vec_launch(const T* dy, const T* x, const T* g, const float* mean, co
         nb = cme_cdiv(nb, rounds);
     }
     if (nb > max_blocks) nb = max_blocks;
-    k<<<nb, LN_WARPS * 32, smem, st>>>(dy, x, g, mean, rstd, dres, dx, scratch, rows, D);
+    CME_CUDA(cme_launch_dependent(k, dim3(nb), dim3(LN_WARPS * 32), smem, st, dy, x, g, mean, rstd, dres, dx, scratch, rows,
+                                  D));
     *used_blocks = nb;
     return CME_OK;
 }
@@ -366,12 +371,12 @@ int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, co
         const size_t smem = (size_t)LN_WARPS * 2 * D * sizeof(float);
         auto k = ln_bwd_kernel<T>;
         if (smem > 48 * 1024) CME_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<nblocks, LN_WARPS * 32, smem, st>>>((const T*)dy, (const T*)x, (const T*)g, mean, rstd, (const T*)dres,
-                                                (T*)dx, scratch, rows, D);
+        CME_CUDA(cme_launch_dependent(k, dim3(nblocks), dim3(LN_WARPS * 32), smem, st, (const T*)dy, (const T*)x,
+                                      (const T*)g, mean, rstd, (const T*)dres, (T*)dx, scratch, rows, D));
     }
     CME_LAUNCH_CHECK();
-    ln_bwd_finalize_kernel<T><<<cme_cdiv(2 * D, 16), 256, 0, st>>>(scratch, nblocks, D, (T*)dgamma, (T*)dbeta,
-                                                                  accumulate);
+    CME_CUDA(cme_launch_dependent(ln_bwd_finalize_kernel<T>, dim3(cme_cdiv(2 * D, 16)), dim3(256), 0, st,
+                                  (const float*)scratch, nblocks, D, (T*)dgamma, (T*)dbeta, accumulate));
     CME_LAUNCH_CHECK();
     return CME_OK;
 }
