@@ -146,6 +146,64 @@ CME_API int cme_gemm_status_word(int** out) {
     return CME_OK;
 }
 
+// Tile shape and K splits for a product: minimise  waves x k-blocks per unit x cost(tile)  (+ fixed per-tile and
+// per-split overheads), with measured clocks per 16-deep MMA step for each tile shape.  Pure host arithmetic.
+//   force_bn: 0 = choose; 64 / 128 / 256 = tile width on one CTA; 512 = the 256 x 256 tile on a CTA pair
+//   force_splits: 0 = choose.  Split-K needs the plain epilogue, a workspace for the fp32 partials and at least
+//   four 64-deep k-blocks per split.
+static void plan_tiles(int M, int N, int K, int batch, bool plain_epi, long long workspace_bytes, int num_sms,
+                       int max_pairs, int force_bn, int force_splits, int* bn_out, bool* pair_out, int* splits_out) {
+    const int num_kb = cme_cdiv(K, BK);
+    int bn = force_bn, splits = force_splits;
+    bool pair = false;
+    if (bn == 512) { bn = 256; pair = true; }
+    if (!bn || !splits) {
+        double best = 1e30;
+        int best_bn = 128, best_s = 1;
+        bool best_pair = false;
+        const int bns[4] = {256, 256, 128, 64};
+        // clocks per 16-deep MMA step and SM: the 128-row tiles are limited by how fast shared memory can be
+        // refilled from L2 ((128 + bn) x 32 bytes per step), the pair tile (128 + 128 per SM) by the tensor pipe
+        const double cost[4] = {136.0, 168.0, 100.0, 72.0};
+        for (int i = 0; i < 4; ++i) {
+            const bool pr = i == 0;
+            if (pr && (max_pairs <= 0 || M <= BM)) continue;
+            if (force_bn && (force_bn == 512 ? !pr : (pr || bns[i] != force_bn))) continue;
+            if (bns[i] > 64 && N <= bns[i] / 2) continue;            // tile mostly padding
+            const long long t = (long long)cme_cdiv(M, pr ? 2 * BM : BM) * cme_cdiv(N, bns[i]) * batch;
+            const int slots = pr ? max_pairs : num_sms;
+            for (int s = 1; s <= 16; ++s) {
+                if (force_splits && s != force_splits) continue;
+                if (s > 1 && (!plain_epi || num_kb / s < 4 || (long long)s * batch * M * N * 4 > workspace_bytes)) break;
+                const long long units = t * s;
+                const double waves = (double)((units + slots - 1) / slots);
+                const double kb = (double)cme_cdiv(num_kb, s);
+                // 4 MMAs per k-block; epilogue / pipeline fill ~ 6 k-blocks of the widest tile per unit;
+                // a split adds one fp32 write + read of the output per split
+                double est = waves * ((kb + 2.0) * 4.0 * cost[i] + 6.0 * 4.0 * bns[i] / 2.0);
+                if (s > 1) est += 6000.0 + (double)s * M * N * batch / num_sms / 16.0;   // + one more launch
+                if (est < best) { best = est; best_bn = bns[i]; best_s = s; best_pair = pr; }
+            }
+        }
+        if (!bn) { bn = best_bn; pair = best_pair; }
+        if (!splits) splits = best_s;
+    }
+    *bn_out = bn; *pair_out = pair; *splits_out = splits;
+}
+
+// The plan the launcher would choose, without a device: `num_sms` SMs, `max_pairs` co-resident CTA pairs (0 = no
+// cluster launches).  out = {tile width, pair (0/1), splits}.
+CME_API int cme_gemm_plan(int M, int N, int K, int batch, int plain_epilogue, long long workspace_bytes, int num_sms,
+                          int max_pairs, int force_bn, int force_splits, int* out) {
+    CME_REQUIRE(M > 0 && N > 0 && K > 0 && batch > 0 && num_sms > 0, CME_ERR_SHAPE, "gemm plan: empty problem");
+    int bn = 0, splits = 0;
+    bool pair = false;
+    plan_tiles(M, N, K, batch, plain_epilogue != 0, workspace_bytes, num_sms, max_pairs, force_bn, force_splits, &bn,
+               &pair, &splits);
+    out[0] = bn; out[1] = pair ? 1 : 0; out[2] = splits;
+    return CME_OK;
+}
+
 int gemm_tcgen05_supported(const CmeGemm* g) {
     if (g->ab_dtype != CME_BF16) return 0;
     if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->batch <= 0) return 0;
@@ -178,45 +236,11 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     }
     int tiles_m = cme_cdiv(g->M, BM);
     const int num_kb = cme_cdiv(g->K, BK);
-    // Tile shape and K splits: minimise  waves x k-blocks per unit x cost(tile)  (+ fixed per-tile and per-split
-    // overheads), with measured clocks per 16-deep MMA step for each tile shape (table below).
     const bool plain_epi = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;
-    // force_bn: 64 / 128 / 256 = tile width on one CTA; 512 = the 256 x 256 tile on a CTA pair
-    int bn = g->force_bn, splits = g->force_splits;
+    int bn = 0, splits = 0;
     bool pair = false;
-    if (bn == 512) { bn = 256; pair = true; }
-    if (!bn || !splits) {
-        double best = 1e30;
-        int best_bn = 128, best_s = 1;
-        bool best_pair = false;
-        const int bns[4] = {256, 256, 128, 64};
-        // clocks per 16-deep MMA step and SM: the 128-row tiles are limited by how fast shared memory can be
-        // refilled from L2 ((128 + bn) x 32 bytes per step), the pair tile (128 + 128 per SM) by the tensor pipe
-        const double cost[4] = {136.0, 168.0, 100.0, 72.0};
-        for (int i = 0; i < 4; ++i) {
-            const bool pr = i == 0;
-            if (pr && (g_max_pairs <= 0 || g->M <= BM)) continue;
-            if (g->force_bn && (g->force_bn == 512 ? !pr : (pr || bns[i] != g->force_bn))) continue;
-            if (bns[i] > 64 && g->N <= bns[i] / 2) continue;            // tile mostly padding
-            const long long t = (long long)cme_cdiv(g->M, pr ? 2 * BM : BM) * cme_cdiv(g->N, bns[i]) * g->batch;
-            const int slots = pr ? g_max_pairs : g_num_sms;
-            for (int s = 1; s <= 16; ++s) {
-                if (g->force_splits && s != g->force_splits) continue;
-                if (s > 1 && (!plain_epi || !g->workspace || num_kb / s < 4 ||
-                              (long long)s * g->batch * g->M * g->N * 4 > g->workspace_bytes)) break;
-                const long long units = t * s;
-                const double waves = (double)((units + slots - 1) / slots);
-                const double kb = (double)cme_cdiv(num_kb, s);
-                // 4 MMAs per k-block; epilogue / pipeline fill ~ 6 k-blocks of the widest tile per unit;
-                // a split adds one fp32 write + read of the output per split
-                double est = waves * ((kb + 2.0) * 4.0 * cost[i] + 6.0 * 4.0 * bns[i] / 2.0);
-                if (s > 1) est += 6000.0 + (double)s * g->M * g->N * g->batch / g_num_sms / 16.0;   // + one more launch
-                if (est < best) { best = est; best_bn = bns[i]; best_s = s; best_pair = pr; }
-            }
-        }
-        if (!bn) { bn = best_bn; pair = best_pair; }
-        if (!splits) splits = best_s;
-    }
+    plan_tiles(g->M, g->N, g->K, g->batch, plain_epi, g->workspace ? g->workspace_bytes : 0, g_num_sms, g_max_pairs,
+               g->force_bn, g->force_splits, &bn, &pair, &splits);
     CME_REQUIRE(bn == 64 || bn == 128 || bn == 256, CME_ERR_SHAPE, "tile width must be 64, 128, 256 or 512 (pair)");
     CME_REQUIRE(!pair || g_max_pairs > 0, CME_ERR_SHAPE, "CTA-pair tiles are not available on this device");
     if (pair) tiles_m = cme_cdiv(g->M, 2 * BM);
