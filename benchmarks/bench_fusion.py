@@ -87,6 +87,39 @@ def main():
     rec("layernorm-bwd+residual", fused, time_kernel(unf5, 3, a.iters, fl), 4 * h.numel() * 2)
     fused = time_kernel(lambda: ops.layernorm_fwd(h, g, b, 1e-5), 3, a.iters, fl)
     rec("layernorm fwd", fused, fused, 2 * h.numel() * 2)
+    # Softmax-cross-entropy forward + backward in one kernel against PyTorch (forward, then autograd backward), and the
+    # fused AdamW step (bf16 gradients in, fp32 master / moments, bf16 parameters out) against torch's fused AdamW.
+    ce_rows = min(rows, 4096) if not a.reference_shapes else rows
+    V = 65 if a.reference_shapes else 50304
+    lg = torch.randn(ce_rows, V, device="cuda").to(bf)
+    tg = torch.randint(0, V, (ce_rows,), device="cuda", dtype=torch.int32)
+    fused = time_kernel(lambda: ops.cross_entropy(lg, tg), 3, a.iters, fl)
+    lg32 = lg.clone().requires_grad_(True)
+    tg64 = tg.long()
+
+    def unf6():
+        lg32.grad = None
+        torch.nn.functional.cross_entropy(lg32.float(), tg64).backward()
+    rec("softmax-cross-entropy fwd+bwd (vs torch)", fused, time_kernel(unf6, 3, a.iters, fl), 2 * lg.numel() * 2)
+
+    n = 2048 * 512 if a.reference_shapes else 124 * 1000 * 1000
+    master = torch.randn(n, device="cuda") * 0.02
+    grads = (torch.randn(n, device="cuda") * 1e-3).to(bf)
+    m1, v1 = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    comp = master.to(bf)
+    step = torch.ones(1, dtype=torch.int32, device="cuda")
+    lr = torch.full((1,), 3e-4, device="cuda")
+    fused = time_kernel(lambda: ops.adam_step(master, grads, m1, v1, step, lr, compute=comp, beta2=0.95,
+                                              weight_decay=0.1), 3, a.iters, fl)
+    pt = torch.nn.Parameter(master.clone())
+    pt.grad = grads.float()
+    opt = torch.optim.AdamW([pt], lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+
+    def unf7():
+        pt.grad = grads.float()            # torch's optimizer wants the gradient in the parameter's dtype
+        opt.step()
+        comp.copy_(pt.detach())            # and the bf16 copy of the parameters is one more pass
+    rec("adamw step (vs torch fused AdamW + casts)", fused, time_kernel(unf7, 3, a.iters, fl), n * 30)
     if a.json:
         json.dump(out, open(a.json, "w"), indent=1)
 
