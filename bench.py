@@ -144,6 +144,20 @@ def main() -> int:
 
     ms_e2e, clocks_e2e, _ = timed(step_e2e)
 
+    # ---- exposed gradient-synchronisation time: a few eager steps with the wait of the compute stream on the
+    # last bucket kernels bracketed by events (median, max over ranks) -----------------------------------------
+    exposed_ms = None
+    if world > 1 and getattr(model, "fused", None) is not None:
+        fs = model.fused
+        fs.measure_exposed = True
+        for s in range(6):
+            trainer._step([dx[s * accum + i] for i in range(accum)], [dy[s * accum + i] for i in range(accum)])
+        vals = sorted(fs.exposed_ms()[2:])
+        fs.measure_exposed = False
+        t = torch.tensor([vals[len(vals) // 2] if vals else 0.0], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        exposed_ms = t.item()
+
     tokens_per_step = BT * accum * world
     value = tokens_per_step / (ms_step / 1e3)
     e2e = tokens_per_step / (ms_e2e / 1e3)
@@ -168,6 +182,7 @@ def main() -> int:
                     "h2d_bytes_per_step": 2 * accum * BT * 4, "d2h_bytes_per_step": 4,
                     "clocks": {"sm_mhz": clocks_e2e["sm_mhz"], "reasons": clocks_e2e["reasons"]}},
             "gpu_launches": int(launches),
+            "exposed_comm_ms_per_step": exposed_ms,
             "loss": last_loss[0], "loss_resident": loss_resident, "device_status": status,
             "rejected": bool(bad),
         }

@@ -112,6 +112,8 @@ class FusedSync:
         self.grad_scale = 1.0 / self.world
         self.lib = ops.lib()
         self.launched = 0
+        self.measure_exposed = False
+        self._exposed = []
 
     def launch_bucket(self, b: Bucket) -> None:
         """Called on the host as soon as backward has enqueued the last kernel of bucket ``b``."""
@@ -133,10 +135,27 @@ class FusedSync:
         self.launched += 1
 
     def join(self) -> None:
-        """Make the compute stream wait for every bucket kernel (parameters are then final on this rank)."""
+        """Make the compute stream wait for every bucket kernel (parameters are then final on this rank).  With
+        ``measure_exposed`` set (eager steps only) the wait is bracketed by timing events: the time the compute
+        stream sits idle behind the last bucket kernels is the step's exposed synchronisation time."""
         ev = torch.cuda.Event()
         ev.record(self.stream)
-        torch.cuda.current_stream().wait_event(ev)
+        cur = torch.cuda.current_stream()
+        if self.measure_exposed and not torch.cuda.is_current_stream_capturing():
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(cur)
+            cur.wait_event(ev)
+            e1.record(cur)
+            self._exposed.append((e0, e1))
+        else:
+            cur.wait_event(ev)
+
+    def exposed_ms(self) -> List[float]:
+        """Exposed synchronisation time of every step since ``measure_exposed`` was set (synchronises)."""
+        torch.cuda.synchronize(self.model.device)
+        out = [a.elapsed_time(b) for a, b in self._exposed]
+        self._exposed = []
+        return out
 
     def owned_mask(self) -> torch.Tensor:
         """1.0 where this rank owns the optimizer state (slice ``rank`` of every bucket), else 0.0."""
