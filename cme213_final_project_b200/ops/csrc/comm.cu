@@ -253,7 +253,7 @@ struct FusedArgs {
 // One bucket of the data-parallel step: barrier -> reduce-scatter (this rank's 1/world slice of the bucket, fp32
 // accumulation in rank order) -> x grad_scale -> AdamW on the fp32 master slice -> bf16 parameters into every
 // rank's parameter arena -> barrier.  After the kernel every rank holds identical bf16 parameters for the bucket.
-__global__ void __launch_bounds__(COMM_THREADS) fused_rs_adamw_ag_kernel(const FusedArgs a) {
+__global__ void __launch_bounds__(COMM_THREADS, 5) fused_rs_adamw_ag_kernel(const FusedArgs a) {
     const Peers& P = a.P;
     const uint32_t e = a.ctl[3 * a.bucket] + 1;
     const int slot0 = 2 * a.bucket, slot1 = slot0 + 1;
@@ -266,12 +266,28 @@ __global__ void __launch_bounds__(COMM_THREADS) fused_rs_adamw_ag_kernel(const F
         const long long per = a.count / P.world;                  // elements in this rank's slice
         const long long e0 = a.start + per * P.rank;
         const long long nvec = per / 8;
-        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
-             i += (long long)gridDim.x * blockDim.x) {
+        // Four vectors per thread and trip: the in-switch reductions of all four are requested before the first is
+        // consumed, so a thread keeps 64 bytes of NVLink reads in flight instead of 16 (one request per thread was
+        // not enough outstanding data to fill the links at their latency).
+        constexpr int U = 4;
+        const long long stride = (long long)gridDim.x * blockDim.x;
+        for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+          uint4 raw[U];
+          if (a.use_nvls) {
+#pragma unroll
+              for (int k = 0; k < U; ++k) {
+                  const long long ik = i0 + k * stride;
+                  if (ik < nvec) raw[k] = mc_ld_reduce_bf16(reinterpret_cast<const __nv_bfloat16*>(P.mc_buf) + e0 + ik * 8);
+              }
+          }
+#pragma unroll
+          for (int k = 0; k < U; ++k) {
+            const long long i = i0 + k * stride;
+            if (i >= nvec) break;
             const long long el = e0 + i * 8;
             float g[8];
             if (a.use_nvls) {
-                unpack8(mc_ld_reduce_bf16(reinterpret_cast<const __nv_bfloat16*>(P.mc_buf) + el), g);
+                unpack8(raw[k], g);
             } else {
                 reduce_peers<__nv_bfloat16>(P, el / 8, g);
             }
@@ -309,6 +325,7 @@ __global__ void __launch_bounds__(COMM_THREADS) fused_rs_adamw_ag_kernel(const F
             } else {
                 for (int r = 0; r < P.world; ++r) st_peer(reinterpret_cast<__nv_bfloat16*>(P.buf2[r]) + el, out);
             }
+          }
         }
     }
     __threadfence_system();
