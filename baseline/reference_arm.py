@@ -15,6 +15,10 @@ configuration this arm reports ``unavailable``.
 Metric of the reference arm: the reference's own epoch line (``Epoch N: ... <ms>ms <tok/s> tok/s``), i.e. host
 wall clock between barriers around K steps (``FINAL_CLEAN_CODE_/src/main.cu:322-323,429-450``); epoch 1 (K steps,
 at least W) is warm-up, epoch 2 is reported.
+
+``--ref-graph`` sets the reference's own ``CME213_USE_CUDA_GRAPH=1`` (its fastest single-GPU mode: three eager
+steps, then the whole step replayed as one CUDA graph, ``FINAL_CLEAN_CODE_/src/main.cu:299-355``); every other
+``CME213_*`` variable of the caller's environment is dropped so the reference runs its stock defaults.
 """
 from __future__ import annotations
 
@@ -52,6 +56,9 @@ def run_reference(a) -> int:
                             f"(run baseline/build_reference.sh)", a)
     steps = max(a.steps, a.warmup)
     env = {k: v for k, v in os.environ.items() if not k.startswith("CME213_")}
+    ref_graph = bool(getattr(a, "ref_graph", False))
+    if ref_graph:
+        env["CME213_USE_CUDA_GRAPH"] = "1"
     cmd = [exe, os.path.join(REF, "inp.txt"), "--epochs", "2", "--max-steps", str(steps), "--lr", LR[H]]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=1800, env=env, cwd=REF)
     if r.returncode != 0:
@@ -73,7 +80,7 @@ def run_reference(a) -> int:
            "vs_baseline": toks / table[H], "dtype": "fp32 storage, cuBLAS fp16 tensor-core math (its auto backend)",
            "data": "tiny-Shakespeare inp.txt (the reference takes no synthetic input)",
            "config": {"model": a.config, "global_batch": 32, "seq_len": 64, "parallelism": "dp1",
-                      "tokens_per_epoch": tokens},
+                      "tokens_per_epoch": tokens, "cuda_graph": ref_graph},
            "e2e": {"value": toks, "unit": "tokens/s",
                    "note": "the reference preloads every batch to the device before the loop; its number has no per-step copies"},
            "loss": loss}

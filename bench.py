@@ -17,7 +17,15 @@ by a barrier and a device synchronize on both sides, timed with CUDA events, max
                     the step's loss back to the host.
 
 ``--impl reference`` runs the unmodified reference trainer built into ``baseline/_ref`` when the configuration
-is one it can express (single-block ``parity-*`` presets on one GPU); otherwise it reports why it cannot.
+is one it can express (single-block ``parity-*`` presets on one GPU; ``--ref-graph`` turns on the reference's own
+CUDA-graph mode); otherwise it reports why it cannot.  ``--impl torch`` runs the same model, configuration and
+timing protocol in plain PyTorch (SDPA, ``torch.matmul``, fused AdamW, DDP over NCCL for N > 1) as an independent
+same-box anchor; it is not the reference.
+
+After the timed regions the line also carries what tells a valid run from a silently broken one: the status words
+of the GEMM, attention and gradient-synchronisation kernels (max over ranks; non-zero sets ``rejected``), the
+cross-rank span of a parameter checksum (must be 0: every rank holds the same bf16 parameters), and the exposed
+synchronisation time of the last replayed step from device timestamps.
 """
 from __future__ import annotations
 
@@ -36,7 +44,8 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
+    ap.add_argument("--ref-graph", action="store_true", help="reference arm: its own CUDA-graph mode")
     ap.add_argument("--config", default="gpt2-small")
     ap.add_argument("--grad-accum", type=int, default=None)
     ap.add_argument("--bucket-mb", type=float, default=25.0)
@@ -58,6 +67,9 @@ def main() -> int:
     if a.impl == "reference":
         from baseline.reference_arm import run_reference
         return run_reference(a)
+    if a.impl == "torch":
+        from baseline.torch_arm import run_torch
+        return run_torch(a)
 
     import torch
     import torch.distributed as dist
@@ -73,7 +85,7 @@ def main() -> int:
         print(f"bench.py: --gpus {a.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N > 1",
               file=sys.stderr)
         return 2
-    ctx = DistributedContext().init(backend="nccl" if world > 1 else "auto", device="cuda")
+    ctx = DistributedContext().init(backend=a.comm if world > 1 else "auto", device="cuda")
     dev = ctx.device
     cfg, optim = preset(a.config)
     accum = a.grad_accum or (4 if a.config == "gpt2-medium" else 1)
@@ -81,10 +93,8 @@ def main() -> int:
                     grad_accum=accum, comm_backend=a.comm, cuda_graph=not a.no_graph, synthetic=True)
 
     from cme213_final_project_b200.train import build_model
-    model = build_model(cfg, optim, run, ctx, seed=42)
-    if world > 1 and a.comm == "fused":
-        from cme213_final_project_b200.parallel.fused_sync import attach_fused_sync
-        attach_fused_sync(model, ctx, run)
+    model = build_model(cfg, optim, run, ctx, seed=42)          # attaches the fused path when world > 1 and --comm fused
+    fused = getattr(model, "fused", None)
     trainer = Trainer(model, ctx, run, optim)
     graphed = (not a.no_graph) and trainer.enable_cuda_graph(warmup_steps=min(3, max(a.warmup - 1, 1)))
 
@@ -144,24 +154,31 @@ def main() -> int:
 
     ms_e2e, clocks_e2e, _ = timed(step_e2e)
 
-    # ---- exposed gradient-synchronisation time: a few eager steps with the wait of the compute stream on the
-    # last bucket kernels bracketed by events (median, max over ranks) -----------------------------------------
-    exposed_ms = None
-    if world > 1 and getattr(model, "fused", None) is not None:
-        fs = model.fused
-        fs.measure_exposed = True
-        for s in range(6):
-            trainer._step([dx[s * accum + i] for i in range(accum)], [dy[s * accum + i] for i in range(accum)])
-        vals = sorted(fs.exposed_ms()[2:])
-        fs.measure_exposed = False
-        t = torch.tensor([vals[len(vals) // 2] if vals else 0.0], dtype=torch.float64, device=dev)
+    # ---- exposed gradient-synchronisation time of the last timed step, from device timestamps written inside the
+    # (replayed) step: end of the last synchronisation kernel minus end of backward, max over ranks ---------------
+    exposed_ms, timeline = None, None
+    if world > 1 and fused is not None:
+        timeline = fused.timeline()
+        t = torch.tensor([timeline["exposed_ms"]], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         exposed_ms = t.item()
+
+    # ---- validity: status words (max over ranks) and the cross-rank parameter checksum span -------------------
+    st = torch.tensor([ops.gemm_check_status(), ops.attention_check_status(),
+                       fused.check_status() if fused is not None else 0], dtype=torch.int32, device=dev)
+    checksum = torch.tensor([float(model.params.double().sum().item())], dtype=torch.float64, device=dev)
+    span = 0.0
+    if world > 1:
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        lo, hi = checksum.clone(), checksum.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        span = float((hi - lo).item())
+    gemm_status, attn_status, comm_status = (int(v) for v in st.tolist())
 
     tokens_per_step = BT * accum * world
     value = tokens_per_step / (ms_step / 1e3)
     e2e = tokens_per_step / (ms_e2e / 1e3)
-    status = ops.gemm_check_status()
     bad = [r for r in clocks["reasons"] if r in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown")]
     if ctx.is_root():
         base = baseline_number(a.config, world)
@@ -174,7 +191,9 @@ def main() -> int:
             "impl": "ours",
             "config": {"model": a.config, "global_batch": cfg.batch_size * accum * world, "seq_len": cfg.seq_len,
                        "micro_batch_per_gpu": cfg.batch_size, "grad_accum": accum,
-                       "parallelism": f"dp{world}", "sync": f"{a.comm}/{run.sync_mode}/bucket_mb={a.bucket_mb}",
+                       "parallelism": f"dp{world}", "sync": (f"{ctx.backend}/{run.sync_mode}/bucket_mb={a.bucket_mb}" if world > 1
+                                else "none (single rank: separate AdamW kernel)"),
+                       "sync_detail": ctx.backend_note or None,
                        "cuda_graph": bool(graphed), "optimizer": "adamw" if optim.weight_decay > 0 else "adam+clip",
                        "l2": "per-step working set (activations + weights, several GB) is far larger than the 126 MB L2"},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
@@ -183,8 +202,12 @@ def main() -> int:
                     "clocks": {"sm_mhz": clocks_e2e["sm_mhz"], "reasons": clocks_e2e["reasons"]}},
             "gpu_launches": int(launches),
             "exposed_comm_ms_per_step": exposed_ms,
-            "loss": last_loss[0], "loss_resident": loss_resident, "device_status": status,
-            "rejected": bool(bad),
+            "comm_timeline_ms": timeline,
+            "loss": last_loss[0], "loss_resident": loss_resident,
+            "device_status": gemm_status, "attn_status": attn_status, "comm_status": comm_status,
+            "checksum_span": span,
+            "sm_mhz_x_ms": clocks["sm_mhz"] * ms_step if clocks.get("sm_mhz") else None,
+            "rejected": bool(bad) or bool(gemm_status or attn_status or comm_status) or span != 0.0,
         }
         print(json.dumps(out), flush=True)
     ctx.finalize()

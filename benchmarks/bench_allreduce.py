@@ -79,16 +79,17 @@ def main():
             am, av = torch.zeros_like(master), torch.zeros_like(master)
             step = torch.ones(1, dtype=torch.int32, device=dev)
             lr = torch.full((1,), 1e-4, dtype=torch.float32, device=dev)
-            use_nvls = int(bool(src.multicast_ptr and dst.multicast_ptr))
+            has_mc = bool(src.multicast_ptr and dst.multicast_ptr)
+            fused_algo = [1]                       # 1 two-shot over peer loads, 2 NVLS; set per measurement below
 
             def fused(n, ctas):
                 ops._check(comm.lib.cme_comm_fused_adamw(
                     W, R, src.c_ptrs, dst.c_ptrs, comm.flags.c_ptrs, ctypes.c_void_p(src.multicast_ptr),
                     ctypes.c_void_p(dst.multicast_ptr), ctypes.c_longlong(0), ctypes.c_longlong(n), ops._p(master),
                     ops._p(am), ops._p(av), ops._p(step), ops._p(lr), ctypes.c_float(0.9), ctypes.c_float(0.95),
-                    ctypes.c_float(1e-8), ctypes.c_float(0.1), ctypes.c_float(1.0 / W), None, 0, use_nvls, 3, ctas,
-                    ops._p(comm.ctl), ops._p(comm.status), ctypes.c_double(comm.budget_ms),
-                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+                    ctypes.c_float(1e-8), ctypes.c_float(0.1), ctypes.c_float(1.0 / W), None, 0, fused_algo[0], 3,
+                    comm.max_buckets, ctas, ops._p(comm.ctl), ops._p(comm.status), ctypes.c_double(comm.budget_ms),
+                    None, None, None, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
         nbytes = a.min_kb * 1024
         while nbytes <= a.max_mb * (1 << 20):
             n = max(nbytes // es, (16 // es) * W)
@@ -103,11 +104,16 @@ def main():
                                           dev, sync)
             if fused is not None:
                 fc = min(4 * 148, max(1, n * es // 4096))
-                rec["fused_adamw_ms"] = timed(lambda: fused(n, fc), a.iters, dev, sync)
+                for name, code in (("two_shot", 1), ("nvls", 2)):
+                    if code == 2 and not has_mc:
+                        continue
+                    fused_algo[0] = code
+                    rec[f"fused_{name}_ms"] = timed(lambda: fused(n, fc), a.iters, dev, sync)
+                rec["fused_adamw_ms"] = min(rec[k] for k in ("fused_two_shot_ms", "fused_nvls_ms") if k in rec)
                 # bytes over NVLink per GPU and direction: (W-1)/W of the gradients in, the same of the parameters out
                 rec["fused_adamw_link_gbs"] = n * es * (W - 1) / W / (rec["fused_adamw_ms"] * 1e-3) / 1e9
             assert comm.check_status() == 0
-            best = min((rec[k], k) for k in rec if k.endswith("_ms") and k not in ("nccl_ms", "fused_adamw_ms"))
+            best = min((rec[k], k) for k in rec if k.endswith("_ms") and k != "nccl_ms" and not k.startswith("fused_"))
             rec["best"] = best[1][:-3]
             bus = lambda ms: rec["bytes"] * 2 * (W - 1) / W / (ms * 1e-3) / 1e9
             rec["best_busbw_gbs"], rec["nccl_busbw_gbs"] = bus(best[0]), bus(rec["nccl_ms"])
@@ -123,8 +129,19 @@ def main():
         if len(pts) >= 3:
             al, be = fit_alpha_beta(pts)
             fits[algo] = {"alpha_ms": al, "beta_ms_per_mb": be * (1 << 20)}
-    cross = [r["bytes"] for r in rows if r["dtype"] == "bfloat16" and r.get("best") == "one_shot"]
-    table = {"one_shot_max_bytes": max(cross) if cross else 0, "use_nvls": any(r.get("best") == "nvls" for r in rows)}
+    # The table the training path consumes (parallel/fused_sync.py::choose_algo), from the fused kernel's own timings
+    # where it has both variants: one-shot up to the largest size it won; NVLS from the smallest size after which it
+    # stays ahead of peer loads.
+    bf = [r for r in rows if r["dtype"] == "bfloat16"]
+    cross = [r["bytes"] for r in bf if r.get("best") == "one_shot"]
+    nvls_min, use_nvls = 0, False
+    for r in sorted(bf, key=lambda r: -r["bytes"]):
+        two, nv = r.get("fused_two_shot_ms", r.get("two_shot_ms")), r.get("fused_nvls_ms", r.get("nvls_ms"))
+        if nv is None or two is None or nv > two:
+            break
+        nvls_min, use_nvls = r["bytes"], True
+    table = {str(W): {"one_shot_max_bytes": max(cross) if cross else 0, "use_nvls": use_nvls,
+                      "nvls_min_bytes": nvls_min, "measured": True}}
     if R == 0:
         print("FIT " + json.dumps(fits))
         print("TABLE " + json.dumps(table))

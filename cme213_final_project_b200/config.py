@@ -97,11 +97,13 @@ class RunConfig:
     trace_trajectory: bool = False
     # additions
     comm_backend: str = "auto"     # auto | fused | nccl | gloo | host
+    comm_algo: str = "auto"        # fused path, per bucket: auto (measured table) | one_shot | two_shot | nvls
+    comm_table: Optional[str] = None   # JSON written by benchmarks/bench_allreduce.py --table (default: the shipped one)
     defer_grad_avg: bool = False
     comm_thread: bool = False
     cuda_graph: bool = False
     grad_accum: int = 1
-    gemm_backend: str = "auto"     # auto | tcgen05 | simt | torch
+    gemm_backend: str = "auto"     # auto | tcgen05 | simt
     compute_dtype: str = "bf16"    # bf16 | fp32
     synthetic: bool = False
     seed: int = 42
@@ -160,6 +162,14 @@ ENV_TOGGLES = (
 )
 
 
+# The reference selects among its own kernels and two library paths (``gemm.cu:16-106``).  This framework has two
+# GEMM implementations, both its own: the tcgen05 tensor-core kernel and the SIMT kernel.  The reference's names
+# are accepted and mapped onto them: its hand-written kernels to the SIMT kernel, its library paths (which exist
+# to reach the tensor cores) to the tensor-core kernel.
+GEMM_BACKEND_MAP = {"auto": "tcgen05", "custom": "simt", "cublas": "tcgen05", "cublas_tc": "tcgen05",
+                    "tcgen05": "tcgen05", "simt": "simt"}
+
+
 def env_enabled(name: str, env: Optional[Dict[str, str]] = None) -> bool:
     """A toggle is on when set to anything but the empty string or "0" (``main.cu:69-72``)."""
     v = (os.environ if env is None else env).get(name)
@@ -172,7 +182,8 @@ def environment_report(env: Optional[Dict[str, str]] = None, gemm_requested: str
     lines = ["CME213 environment:"]
     found = [f"  {k}={v}" for k, v in env.items() if k.startswith("CME213_")]
     lines += found if found else ["  (none set)"]
-    lines.append(f"  GEMM requested={gemm_requested} auto_policy=tcgen05")
+    lines.append(f"  GEMM requested={gemm_requested} effective={GEMM_BACKEND_MAP.get(gemm_requested, gemm_requested)} "
+                 f"auto_policy=tcgen05")
     return lines
 
 
@@ -203,7 +214,7 @@ def validate_environment(world_size: int, env: Optional[Dict[str, str]] = None) 
         warns.append("Warning: CME213_USE_NCCL=1 requested without CME213_ALLOW_UNVALIDATED_NCCL=1; "
                      "the fused peer-memory path stays the default")
     backend = (os.environ if env is None else env).get("CME213_GEMM_BACKEND")
-    if backend not in (None, "", "auto", "custom", "cublas", "cublas_tc", "tcgen05", "simt", "torch"):
+    if backend not in (None, "") and backend not in GEMM_BACKEND_MAP:
         errs.append(f"unknown CME213_GEMM_BACKEND '{backend}'")
     return errs, warns
 
@@ -220,8 +231,10 @@ def validate_run(model: ModelConfig, run: RunConfig, world_size: int) -> List[st
         errs.append("--bucket-kb must be >= 0")
     if run.compute_dtype not in ("bf16", "fp32"):
         errs.append(f"unknown compute dtype '{run.compute_dtype}'")
-    if run.gemm_backend not in ("auto", "tcgen05", "simt", "torch"):
+    if run.gemm_backend not in ("auto", "tcgen05", "simt"):
         errs.append(f"unknown gemm backend '{run.gemm_backend}'")
+    if run.comm_algo not in ("auto", "one_shot", "two_shot", "nvls"):
+        errs.append(f"unknown comm algorithm '{run.comm_algo}'")
     if run.comm_thread and run.comm_backend == "fused":
         errs.append("--comm-thread drives host-issued collectives; it is not combined with the fused device path")
     return errs
@@ -243,7 +256,7 @@ def apply_environment(run: RunConfig, env: Optional[Dict[str, str]] = None) -> R
         run.compute_dtype = "fp32"
     b = e.get("CME213_GEMM_BACKEND")
     if b:
-        run.gemm_backend = {"custom": "simt", "cublas": "torch", "cublas_tc": "torch"}.get(b, b)
+        run.gemm_backend = GEMM_BACKEND_MAP.get(b, b) if b != "auto" else "auto"
     return run
 
 
@@ -275,6 +288,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--vocab-size", type=int)
     # run options
     p.add_argument("--comm-backend", default="auto")
+    p.add_argument("--comm-algo", default="auto", help="fused path: auto (measured table) | one_shot | two_shot | nvls")
+    p.add_argument("--comm-table", default=None, help="algorithm table written by benchmarks/bench_allreduce.py")
     p.add_argument("--defer-grad-avg", action="store_true")
     p.add_argument("--comm-thread", action="store_true")
     p.add_argument("--cuda-graph", action="store_true")
@@ -308,7 +323,8 @@ def parse_args(argv: Optional[Sequence[str]] = None) -> Tuple[ModelConfig, Optim
     run = RunConfig(data_path=a.data, epochs=a.epochs, max_steps=a.max_steps, sync_mode=sync,
                     bucket_kb=a.bucket_kb, auto_overlap_max_mb=a.auto_overlap_max_mb,
                     validate_config=a.validate_config, trace_trajectory=a.trace_trajectory,
-                    comm_backend=a.comm_backend, defer_grad_avg=a.defer_grad_avg, comm_thread=a.comm_thread,
+                    comm_backend=a.comm_backend, comm_algo=a.comm_algo, comm_table=a.comm_table,
+                    defer_grad_avg=a.defer_grad_avg, comm_thread=a.comm_thread,
                     cuda_graph=a.cuda_graph, grad_accum=a.grad_accum, gemm_backend=a.gemm_backend,
                     compute_dtype=a.compute_dtype, synthetic=a.synthetic, seed=a.seed,
                     save_checkpoint=a.save_checkpoint, load_checkpoint=a.load_checkpoint, profile=a.profile,

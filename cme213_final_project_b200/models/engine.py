@@ -44,7 +44,7 @@ class NativeEngine:
     handles_sync = False
 
     def __init__(self, cfg: ModelConfig, optim: OptimConfig, run: Optional[RunConfig] = None, dist_ctx=None,
-                 seed: int = 42, device=None, shard_multiple: int = 1) -> None:
+                 seed: int = 42, device=None, shard_multiple: int = 1, align: int = 64) -> None:
         run = run or RunConfig()
         self.cfg, self.optim, self.run = cfg, optim, run
         self.device = torch.device(device) if device is not None else (
@@ -52,9 +52,13 @@ class NativeEngine:
         if self.device.type != "cuda":
             raise ops.NativeError("the native engine needs a CUDA device")
         self.lib = ops.lib()
+        with torch.cuda.device(self.device):
+            ops._check(self.lib.cme_init_device())               # status words exist before any stream capture
         self.strict = run.compute_dtype == "fp32"
         self.dtype = torch.float32 if self.strict else torch.bfloat16
-        self.layout = ArenaLayout(cfg, align=64, shard_multiple=shard_multiple)
+        # `align` (elements) is 64 unless the arena has to split into per-rank slices for a world size whose
+        # 8 * world does not divide 64 (parallel.fused_sync.shard_align)
+        self.layout = ArenaLayout(cfg, align=align, shard_multiple=shard_multiple)
         n = self.layout.total
         with torch.cuda.device(self.device):
             flat = init_flat(self.layout, seed).to(self.device)
@@ -83,7 +87,7 @@ class NativeEngine:
         self.nodecay = torch.tensor(nd, dtype=torch.int64, device=self.device).reshape(-1, 2)
         self.step_count = 0
 
-        gemm_backend = {"auto": 0, "tcgen05": 0, "simt": 2, "torch": 0}[run.gemm_backend]
+        gemm_backend = {"auto": 0, "tcgen05": 0, "simt": 2}[run.gemm_backend]
         d = _EngineDesc(V=cfg.vocab_size, T=cfg.seq_len, D=cfg.hidden, H=cfg.heads, FF=cfg.ff, L=cfg.layers,
                         B=cfg.batch_size, act=ops.ACT[cfg.activation], causal=int(cfg.causal),
                         head_flat=int(cfg.head_layout == "flat"), tied=int(cfg.tied_embeddings),

@@ -655,11 +655,13 @@ int make_map_dq(CUtensorMap* out, const void* base, int T, int nbh) {
     return CME_OK;
 }
 
-int* g_attn_status = nullptr;
-
 }  // namespace
 
-int* cme_attn_status_ptr() { return g_attn_status; }
+// Status word of the attention kernels on the current device (null if the device state cannot be set up).
+int* cme_attn_status_ptr() {
+    CmeDeviceState* ds;
+    return cme_device_state(&ds) ? nullptr : ds->status + CME_STATUS_ATTENTION;
+}
 
 int attention_tc_supported(const CmeAttn* a) {
     if (a->dtype != CME_BF16 || a->HD != HD) return 0;
@@ -673,20 +675,20 @@ int attention_tc_supported(const CmeAttn* a) {
 int attention_tc_fwd(const CmeAttn* a, cudaStream_t st) {
     CME_REQUIRE(attention_tc_supported(a), CME_ERR_SHAPE, "attention: shape not supported by the tensor-core kernel");
     CME_REQUIRE(a->lse != nullptr, CME_ERR_SHAPE, "attention: lse buffer is required");
-    if (!g_attn_status) {
-        CME_CUDA(cudaMalloc(&g_attn_status, sizeof(int)));
-        CME_CUDA(cudaMemset(g_attn_status, 0, sizeof(int)));
-    }
+    int* const g_attn_status = cme_attn_status_ptr();
+    CME_REQUIRE(g_attn_status != nullptr, CME_ERR_CUDA, "attention: device state unavailable");
     CUtensorMap mq, mk, mv, mo;
     int rc;
     if ((rc = make_map4(&mq, a->q, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mk, a->k, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mv, a->v, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mo, a->o, a->T, a->nh, a->nb, a->ost, a->osh, a->osb, 32))) return rc;
-    static bool attr = false;
-    if (!attr) {
+    static bool attr[CME_MAX_DEVICES] = {};               // function attributes are per device
+    int dev = 0;
+    CME_CUDA(cudaGetDevice(&dev));
+    if (!attr[dev % CME_MAX_DEVICES]) {
         CME_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
-        attr = true;
+        attr[dev % CME_MAX_DEVICES] = true;
     }
     FwdParams p{a->T, a->nh, a->causal, a->scale * LOG2E, a->lse, g_attn_status};
     dim3 grid(cme_cdiv(a->T, BQ), a->nb * a->nh);
@@ -704,10 +706,8 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     CME_REQUIRE(al16(a->d_o) && al16(a->dq) && al16(a->dk) && al16(a->dv), CME_ERR_SHAPE,
                 "attention backward: gradient buffers must be 16-byte aligned");
-    if (!g_attn_status) {
-        CME_CUDA(cudaMalloc(&g_attn_status, sizeof(int)));
-        CME_CUDA(cudaMemset(g_attn_status, 0, sizeof(int)));
-    }
+    int* const g_attn_status = cme_attn_status_ptr();
+    CME_REQUIRE(g_attn_status != nullptr, CME_ERR_CUDA, "attention: device state unavailable");
     int rc;
     if ((rc = attention_delta_launch(a, st))) return rc;
     const long long rows = (long long)a->nb * a->nh * a->T;
@@ -718,10 +718,12 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
     if ((rc = make_map4(&mdo, a->d_o, a->T, a->nh, a->nb, a->ost, a->osh, a->osb, 128))) return rc;
     if ((rc = make_map_dq(&mdq, a->dq_accum, a->T, a->nb * a->nh))) return rc;
     CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
-    static bool attr = false;
-    if (!attr) {
+    static bool attr[CME_MAX_DEVICES] = {};               // function attributes are per device
+    int dev = 0;
+    CME_CUDA(cudaGetDevice(&dev));
+    if (!attr[dev % CME_MAX_DEVICES]) {
         CME_CUDA(cudaFuncSetAttribute(attn_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
-        attr = true;
+        attr[dev % CME_MAX_DEVICES] = true;
     }
     BwdParams p{a->T, a->nh, a->causal, a->scale, a->scale * LOG2E, a->lse, a->delta, a->dq_accum,
                 (__nv_bfloat16*)a->dk, (__nv_bfloat16*)a->dv, a->sb, a->sh, a->st, g_attn_status};
@@ -738,9 +740,5 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
 
 // Reads and clears the attention status word (non-zero: a bounded wait ran out).
 CME_API int cme_attention_check_status(int* host_out) {
-    *host_out = 0;
-    if (!g_attn_status) return CME_OK;
-    CME_CUDA(cudaMemcpy(host_out, g_attn_status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (*host_out) CME_CUDA(cudaMemset(g_attn_status, 0, sizeof(int)));
-    return CME_OK;
+    return cme_check_status_word(CME_STATUS_ATTENTION, host_out);
 }

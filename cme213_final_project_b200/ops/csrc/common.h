@@ -55,6 +55,19 @@ extern long long g_cme_launches;
 
 static inline int cme_cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
 
+// Per-device facts and status words, created once per device by cme_init_device() -- or by the first launch on
+// the device, which must then happen outside stream capture (it allocates).  A process may drive several GPUs:
+// everything here is indexed by the current device.
+constexpr int CME_MAX_DEVICES = 64;
+enum CmeStatusWord : int { CME_STATUS_GEMM = 0, CME_STATUS_ATTENTION = 1, CME_STATUS_WORDS = 4 };
+struct CmeDeviceState {
+    int num_sms;
+    int* status;           // CME_STATUS_WORDS ints in device memory; a kernel whose bounded wait ran out sets its word
+    int max_pairs;         // co-resident CTA pairs of the pair GEMM kernel (-1: not queried yet, 0: unusable)
+};
+int cme_device_state(CmeDeviceState** out);
+int cme_check_status_word(int which, int* host_out);
+
 #ifdef __CUDACC__
 
 // Programmatic dependent launch for the many short kernels of a step.  A kernel launched through

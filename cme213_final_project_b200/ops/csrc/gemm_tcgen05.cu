@@ -111,19 +111,14 @@ int make_tmap(CUtensorMap* out, const void* base, long long inner, long long row
     return CME_OK;
 }
 
-int g_num_sms = 0;
-int* g_status = nullptr;     // device status word shared by all launches on this device
-
-int g_max_pairs = -1;        // co-resident CTA pairs of the pair kernels on this device (0: cluster launch unusable)
-
 // How many CTA pairs of the pair kernel can be resident at once (the persistent grid must not exceed it: a pair
 // that is not resident would only start when another has finished all of its tiles).
-int query_max_pairs() {
+int query_max_pairs(int num_sms) {
     auto kern = gemm_tc_kernel<256, false, false, true, true, -1>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256, true, true>::SMEM_BYTES) !=
         cudaSuccess) { cudaGetLastError(); return 0; }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(2 * g_num_sms);
+    cfg.gridDim = dim3(2 * num_sms);
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = Cfg<256, true, true>::SMEM_BYTES;
     cudaLaunchAttribute attr[1];
@@ -138,11 +133,10 @@ int query_max_pairs() {
 }  // namespace
 
 CME_API int cme_gemm_status_word(int** out) {
-    if (!g_status) {
-        CME_CUDA(cudaMalloc(&g_status, sizeof(int)));
-        CME_CUDA(cudaMemset(g_status, 0, sizeof(int)));
-    }
-    *out = g_status;
+    CmeDeviceState* ds;
+    int rc = cme_device_state(&ds);
+    if (rc) return rc;
+    *out = ds->status + CME_STATUS_GEMM;
     return CME_OK;
 }
 
@@ -220,20 +214,17 @@ int gemm_tcgen05_supported(const CmeGemm* g) {
 
 int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     CME_REQUIRE(gemm_tcgen05_supported(g), CME_ERR_SHAPE, "gemm shape/alignment not supported by the tcgen05 kernel");
-    if (!g_num_sms) {
-        int dev = 0;
-        CME_CUDA(cudaGetDevice(&dev));
-        CME_CUDA(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+    CmeDeviceState* ds;
+    {
+        int rc0 = cme_device_state(&ds);
+        if (rc0) return rc0;
     }
-    if (!g_status) {
-        int* dummy;
-        int rc = cme_gemm_status_word(&dummy);
-        if (rc) return rc;
-    }
-    if (g_max_pairs < 0) {
+    if (ds->max_pairs < 0) {
         const char* e = getenv("CME213_GEMM_PAIR");
-        g_max_pairs = (e && e[0] == '0') ? 0 : query_max_pairs();
+        ds->max_pairs = (e && e[0] == '0') ? 0 : query_max_pairs(ds->num_sms);
     }
+    const int g_num_sms = ds->num_sms, g_max_pairs = ds->max_pairs;
+    int* const g_status = ds->status + CME_STATUS_GEMM;
     int tiles_m = cme_cdiv(g->M, BM);
     const int num_kb = cme_cdiv(g->K, BK);
     const bool plain_epi = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;
@@ -367,10 +358,4 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
 }
 
 // Reads and clears the device status word (0 = every bounded wait completed).
-CME_API int cme_gemm_check_status(int* host_out) {
-    *host_out = 0;
-    if (!g_status) return CME_OK;
-    CME_CUDA(cudaMemcpy(host_out, g_status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (*host_out) CME_CUDA(cudaMemset(g_status, 0, sizeof(int)));
-    return CME_OK;
-}
+CME_API int cme_gemm_check_status(int* host_out) { return cme_check_status_word(CME_STATUS_GEMM, host_out); }

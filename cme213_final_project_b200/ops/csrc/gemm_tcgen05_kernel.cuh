@@ -743,10 +743,12 @@ template <int BN, bool A_MN, bool B_MN, bool SIMPLE, bool PAIR, int SPEC>
 int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
                const CUtensorMap& ti, const EpiParams& ep, int grid, cudaStream_t st) {
     auto kern = gemm_tc_kernel<BN, A_MN, B_MN, SIMPLE, PAIR, SPEC>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[CME_MAX_DEVICES] = {};          // function attributes are per device
+    int dev = 0;
+    CME_CUDA(cudaGetDevice(&dev));
+    if (!attr_set[dev % CME_MAX_DEVICES]) {
         CME_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, PAIR, SIMPLE, SPEC>::SMEM_BYTES));
-        attr_set = true;
+        attr_set[dev % CME_MAX_DEVICES] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);

@@ -4,6 +4,7 @@
 
 #include <cstdarg>
 #include <cstring>
+#include <mutex>
 
 static thread_local char g_err[1024] = "";
 long long g_cme_launches = 0;
@@ -48,3 +49,49 @@ CME_API int cme_copy_d2d(void* dst, const void* src, long long bytes, void* stre
 
 // Number of kernels this library has launched (or captured into a graph) in this process.
 CME_API long long cme_launch_count() { return g_cme_launches; }
+
+static CmeDeviceState g_dev[CME_MAX_DEVICES];
+static bool g_dev_ready[CME_MAX_DEVICES];
+static std::mutex g_dev_mu;
+
+// State of the current device; the first call on a device queries it and allocates its status words.
+int cme_device_state(CmeDeviceState** out) {
+    int dev = 0;
+    CME_CUDA(cudaGetDevice(&dev));
+    CME_REQUIRE(dev >= 0 && dev < CME_MAX_DEVICES, CME_ERR_LIMIT, "device index %d beyond %d", dev, CME_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_dev_mu);
+    if (!g_dev_ready[dev]) {
+        CmeDeviceState st{};
+        CME_CUDA(cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev));
+        CME_CUDA(cudaMalloc(&st.status, CME_STATUS_WORDS * sizeof(int)));
+        CME_CUDA(cudaMemset(st.status, 0, CME_STATUS_WORDS * sizeof(int)));
+        st.max_pairs = -1;
+        g_dev[dev] = st;
+        g_dev_ready[dev] = true;
+    }
+    *out = &g_dev[dev];
+    return CME_OK;
+}
+
+// Sets up the current device (SM count, status words).  Call once per device before the first stream capture;
+// every launcher calls it too, so eager use needs no explicit call.
+CME_API int cme_init_device() {
+    CmeDeviceState* st;
+    return cme_device_state(&st);
+}
+
+// Reads and clears one status word of the current device (0 = every bounded wait completed).
+int cme_check_status_word(int which, int* host_out) {
+    *host_out = 0;
+    int dev = 0;
+    CME_CUDA(cudaGetDevice(&dev));
+    int* word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mu);
+        if (dev >= 0 && dev < CME_MAX_DEVICES && g_dev_ready[dev]) word = g_dev[dev].status + which;
+    }
+    if (!word) return CME_OK;
+    CME_CUDA(cudaMemcpy(host_out, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*host_out) CME_CUDA(cudaMemset(word, 0, sizeof(int)));
+    return CME_OK;
+}

@@ -55,7 +55,8 @@ class DistributedContext:
         self.rank = 0
         self.local_rank = 0
         self.device = torch.device("cpu")
-        self.backend = "none"               # gradient backend: none | nccl | gloo | host
+        self.backend = "none"               # gradient backend: none | fused | nccl | gloo | host
+        self.backend_note = ""              # why the effective backend differs from the requested one
         self.use_comm_thread = False
         self.defer_gradient_average = False
         self.last_allreduce_ms = 0.0
@@ -97,10 +98,14 @@ class DistributedContext:
                                         timeout=datetime.timedelta(seconds=timeout_s), **kw)
                 self._owns_pg = True
             self.group = dist.group.WORLD
+        # "auto" on GPUs is the fused device path (parallel/fused_sync.py: peer-memory kernels, no library
+        # collective on the gradient path); torch.distributed stays the control plane (rendezvous, handle exchange,
+        # scalar reductions).  The training driver attaches the fused path to the model and calls
+        # `fall_back` with the reason when the model or the options cannot use it.
         if backend == "auto":
-            backend = "none" if world == 1 else ("nccl" if use_cuda else "gloo")
-        if backend == "fused":                 # the device path does its own transfers; NCCL is its fallback
-            backend = "nccl" if use_cuda else "gloo"
+            backend = "none" if world == 1 else ("fused" if use_cuda else "gloo")
+        if backend == "fused" and not use_cuda:
+            backend, self.backend_note = "gloo", "the fused device path needs GPUs"
         self.backend = backend if world > 1 else "none"
         self.defer_gradient_average = defer_grad_avg and world > 1
         self.use_comm_thread = comm_thread and world > 1
@@ -111,10 +116,15 @@ class DistributedContext:
             self._worker.start()
         return self
 
+    def fall_back(self, reason: str) -> None:
+        """The fused device path cannot serve this run: host-issued NCCL all-reduces take over."""
+        if self.backend == "fused":
+            self.backend, self.backend_note = "nccl", reason
+
     def banner(self) -> List[str]:
         """Rank-0 description of the effective mode (``distributed.cpp:128-145``)."""
         return [f"DP: world_size={self.world_size} rank={self.rank} device={self.device}",
-                f"DP gradient backend: {self.backend}",
+                f"DP gradient backend: {self.backend}" + (f" ({self.backend_note})" if self.backend_note else ""),
                 f"DP gradient averaging: {'deferred_to_adam' if self.defer_gradient_average else 'post_allreduce'}",
                 f"DP comm thread: {'enabled' if self.use_comm_thread else 'disabled'}"]
 

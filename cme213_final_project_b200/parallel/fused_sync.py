@@ -7,11 +7,20 @@ backward continues, a scale kernel per bucket and a separate Adam pass
 here one kernel per bucket on a communication stream, launched as soon as backward has produced the bucket,
 with the next step's forward joined on it.  No host thread, no library collective, and the whole step
 (including these kernels) can be captured in one CUDA graph.
+
+With global-norm clipping (the reference's optimizer, ``FINAL_CLEAN_CODE_/src/model/transformer.cu:618-636``) the
+update cannot start before the last gradient is reduced, so the step runs in two phases: the per-bucket kernels
+only reduce (keeping fp32 sums of this rank's slices and their sums of squares), and one kernel after the last
+bucket exchanges the partial norms, clips, applies the optimizer and distributes the parameters.
 """
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional, Sequence
+import json
+import math
+import os
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -22,6 +31,47 @@ from ..config import RunConfig, min_bucket_elems
 from .symm import LocalPeers, SymmetricBuffer
 
 ALGOS = {"one_shot": 0, "two_shot": 1, "nvls": 2}
+MAX_CTAS = 740
+TABLE_PATH = Path(__file__).with_name("comm_table.json")
+
+
+def shard_align(world: int, base: int = 64) -> int:
+    """Arena alignment (elements) under which every bucket splits into ``world`` slices of whole 16-byte bf16
+    vectors: a common multiple of the tensor alignment and ``8 * world``.  Worlds of 3, 5, 6 or 7 ranks need more
+    than the default 64 (the reference validates a 3-rank run, ``scripts/run_edge_case_validation.sh:90-97``)."""
+    return base * (8 * world) // math.gcd(base, 8 * world)
+
+
+def load_table(path: Optional[str] = None) -> Dict[str, dict]:
+    """Measured algorithm table: ``{"<world>": {"one_shot_max_bytes": .., "nvls_min_bytes": ..}, ..}`` as written
+    by ``benchmarks/bench_allreduce.py --table``.  ``path`` (or ``CME213_COMM_TABLE``) overrides the table shipped
+    with the package, which holds the sweeps measured on 2 and 8 B200s."""
+    p = path or os.environ.get("CME213_COMM_TABLE") or TABLE_PATH
+    try:
+        with open(p) as f:
+            return json.load(f)
+    except OSError:
+        return {}
+
+
+def table_for_world(table: Dict[str, dict], world: int) -> dict:
+    """The entry measured at ``world`` ranks, else the one of the nearest measured world size."""
+    sizes = sorted(int(k) for k in table if str(k).isdigit())
+    if not sizes:
+        return {}
+    return table[str(min(sizes, key=lambda s: (abs(s - world), -s)))]
+
+
+def choose_algo(nbytes: int, world: int, has_multicast: bool, table: Optional[dict] = None) -> str:
+    """Collective variant for one message: one-shot up to the measured latency crossover, NVLS from the size at
+    which the in-switch reduction was measured faster than peer loads (when the fabric offers multicast), else
+    two-shot.  ``table`` is one world size's entry of :func:`load_table`."""
+    t = table or {}
+    if world > 1 and nbytes <= t.get("one_shot_max_bytes", 0):
+        return "one_shot"
+    if has_multicast and t.get("use_nvls", True) and nbytes >= t.get("nvls_min_bytes", 0):
+        return "nvls"
+    return "two_shot"
 
 
 class PeerComm:
@@ -50,8 +100,9 @@ class PeerComm:
         ops._check(self.lib.cme_comm_allreduce(
             ops._dt(src.tensor), self.world, self.rank, src.c_ptrs, dst.c_ptrs, self.flags.c_ptrs,
             ctypes.c_void_p(src.multicast_ptr), ctypes.c_void_p(dst.multicast_ptr), ctypes.c_longlong(offset),
-            ctypes.c_longlong(n), ALGOS[algo], ctypes.c_float(scale), bucket, ctas, ops._p(self.ctl),
-            ops._p(self.status), ctypes.c_double(self.budget_ms), ctypes.c_void_p(st.cuda_stream)))
+            ctypes.c_longlong(n), ALGOS[algo], ctypes.c_float(scale), bucket, self.max_buckets, ctas,
+            ops._p(self.ctl), ops._p(self.status), ctypes.c_double(self.budget_ms),
+            ctypes.c_void_p(st.cuda_stream)))
 
     def check_status(self) -> int:
         """Read and clear the status word (non-zero: a bounded wait on a peer ran out)."""
@@ -61,33 +112,25 @@ class PeerComm:
         return v
 
 
-def choose_algo(nbytes: int, world: int, has_multicast: bool, table: Optional[dict] = None) -> str:
-    """Collective variant for a message size: one-shot below the latency crossover, NVLS above it when the
-    fabric offers multicast, else two-shot.  ``table`` (``{"one_shot_max_bytes": ..}``) comes from a measured
-    sweep (``benchmarks/bench_allreduce.py``); the defaults are that sweep's crossover on 8 x B200."""
-    t = table or {}
-    if nbytes <= t.get("one_shot_max_bytes", 256 * 1024):
-        return "one_shot"
-    if has_multicast and t.get("use_nvls", True):
-        return "nvls"
-    return "two_shot"
-
-
 class FusedSync:
     """Owns the symmetric gradient / parameter arenas of an engine and launches the fused kernel per bucket."""
 
     def __init__(self, model, ctx, run: RunConfig, ctas: int = 296, use_nvls: Optional[bool] = None,
-                 budget_ms: float = 5000.0) -> None:
+                 budget_ms: float = 5000.0, algo: Optional[str] = None, table: Optional[dict] = None) -> None:
         if model.strict:
             raise ops.NativeError("the fused synchronisation path needs bf16 gradients (--compute-dtype bf16)")
-        if model.optim.clip_norm > 0:
-            raise ops.NativeError("global-norm clipping needs the whole gradient before any update; "
-                                  "use the all-reduce path (comm backend nccl) for that optimizer setting")
         self.model, self.ctx = model, ctx
         dev = model.device
         n = model.layout.total
         self.world = ctx.world_size
         single = self.world == 1
+        elem = 2
+        self.buckets: List[Bucket] = model.layout.coalesced_buckets(min_bucket_elems(run.bucket_kb, elem))
+        bad = [b for b in self.buckets if b.numel % (8 * self.world) or b.start % 8]
+        if bad:
+            raise ops.NativeError(
+                f"bucket {bad[0].index} ({bad[0].numel} elements) does not split into {self.world} slices of whole "
+                f"16-byte vectors; build the engine with align=shard_align({self.world}) = {shard_align(self.world)}")
         if single:
             self.grads = LocalPeers(torch.zeros(n, dtype=torch.bfloat16, device=dev))
             self.params = LocalPeers(model.params.clone())
@@ -96,51 +139,106 @@ class FusedSync:
             self.params = SymmetricBuffer(n, torch.bfloat16, dev)
             self.params.tensor.copy_(model.params)
         model.rebind(self.params.tensor, self.grads.tensor)
-        elem = 2
-        self.buckets: List[Bucket] = model.layout.coalesced_buckets(min_bucket_elems(run.bucket_kb, elem))
-        self.comm = PeerComm(dev, max_buckets=max(len(self.buckets), 1), budget_ms=budget_ms, single=single)
-        import os
+        # two flag / control indices past the gradient buckets serve the clip kernel (barrier, norm exchange)
+        self.comm = PeerComm(dev, max_buckets=len(self.buckets) + 2, budget_ms=budget_ms, single=single)
         # SM budget: one small CTA per SM while backward is still running (they share SMs with the compute
         # kernels); the last bucket has the GPU to itself and gets four per SM
-        self.ctas = int(os.environ.get("CME213_COMM_CTAS", ctas))
-        self.tail_ctas = int(os.environ.get("CME213_COMM_TAIL_CTAS", 4 * 148))
+        self.ctas = min(int(os.environ.get("CME213_COMM_CTAS", ctas)), MAX_CTAS)
+        self.tail_ctas = min(int(os.environ.get("CME213_COMM_TAIL_CTAS", 4 * 148)), MAX_CTAS)
         mc = self.grads.multicast_ptr != 0 and self.params.multicast_ptr != 0
-        self.use_nvls = mc if use_nvls is None else (use_nvls and mc)
         if os.environ.get("CME213_COMM_NVLS") is not None:
-            self.use_nvls = mc and os.environ["CME213_COMM_NVLS"] != "0"
+            use_nvls = os.environ["CME213_COMM_NVLS"] != "0"
+        self.has_multicast = mc and use_nvls is not False
+        self.use_nvls = self.has_multicast            # kept for callers that print the mode
+        self.clip = model.optim.clip_norm > 0
+        forced = algo or getattr(run, "comm_algo", "auto")
+        if forced == "nvls" and not self.has_multicast:
+            raise ops.NativeError("comm algorithm 'nvls' requested but the buffers have no multicast mapping")
+        tab = table if table is not None else table_for_world(load_table(getattr(run, "comm_table", None)), self.world)
+        self.algos: List[str] = []
+        for b in self.buckets:
+            a = forced if forced != "auto" else choose_algo(b.numel * elem, self.world, self.has_multicast, tab)
+            if a == "one_shot" and (self.clip or single):
+                a = "two_shot"                       # the reduce-only form keeps slices; a world of one has one slice
+            self.algos.append(a)
         self.stream = torch.cuda.Stream(device=dev)
         self.grad_scale = 1.0 / self.world
         self.lib = ops.lib()
         self.launched = 0
         self.measure_exposed = False
         self._exposed = []
+        # device-side time log (ns, %globaltimer): [2b] / [2b + 1] = start / end of bucket b's kernel (index
+        # len(buckets): the clip kernel); the last two words = end of backward on the compute stream, end of the
+        # last synchronisation kernel.  Written by every step, eager or replayed; read with `timeline()`.
+        self.tlog = torch.zeros(2 * (len(self.buckets) + 2), dtype=torch.int64, device=dev)
+        if self.clip:
+            self.gred = torch.zeros(n, dtype=torch.float32, device=dev)
+            self.norm_part = torch.zeros(MAX_CTAS, dtype=torch.float32, device=dev)
+            self.norm_bucket = torch.zeros(len(self.buckets), dtype=torch.float32, device=dev)
+            self.ranges = torch.tensor([[b.start, b.numel] for b in self.buckets], dtype=torch.int64, device=dev)
+        else:
+            self.gred = self.norm_part = self.norm_bucket = self.ranges = None
+
+    def describe(self) -> str:
+        """One line for the training banner: which kernels synchronise which buckets."""
+        kinds = sorted(set(self.algos))
+        per = ", ".join(f"{k} x{self.algos.count(k)}" for k in kinds)
+        form = "reduce per bucket + one clip/AdamW/all-gather kernel" if self.clip else \
+               "reduce-scatter + AdamW + all-gather per bucket"
+        return f"fused device kernels ({form}); {len(self.buckets)} buckets: {per}"
+
+    def _opt_args(self):
+        m, o = self.model, self.model.optim
+        nd = m.nodecay if o.weight_decay > 0 else None
+        return (ops._p(m.master), ops._p(m.adam_m), ops._p(m.adam_v), ops._p(m.step_dev), ops._p(m.lr_dev),
+                ctypes.c_float(o.beta1), ctypes.c_float(o.beta2), ctypes.c_float(o.eps), ctypes.c_float(o.weight_decay)), \
+               (ops._p(nd), 0 if nd is None else nd.shape[0])
 
     def launch_bucket(self, b: Bucket) -> None:
         """Called on the host as soon as backward has enqueued the last kernel of bucket ``b``."""
-        m, o = self.model, self.model.optim
         cur = torch.cuda.current_stream()
         ev = torch.cuda.Event()
         ev.record(cur)
         self.stream.wait_event(ev)
-        nd = m.nodecay if o.weight_decay > 0 else None
+        opt, nd = self._opt_args()
+        last = b.index == len(self.buckets) - 1
         ops._check(self.lib.cme_comm_fused_adamw(
             self.world, self.comm.rank, self.grads.c_ptrs, self.params.c_ptrs, self.comm.flags.c_ptrs,
             ctypes.c_void_p(self.grads.multicast_ptr), ctypes.c_void_p(self.params.multicast_ptr),
-            ctypes.c_longlong(b.start), ctypes.c_longlong(b.numel), ops._p(m.master), ops._p(m.adam_m),
-            ops._p(m.adam_v), ops._p(m.step_dev), ops._p(m.lr_dev), ctypes.c_float(o.beta1), ctypes.c_float(o.beta2),
-            ctypes.c_float(o.eps), ctypes.c_float(o.weight_decay), ctypes.c_float(self.grad_scale), ops._p(nd),
-            0 if nd is None else nd.shape[0], int(self.use_nvls), b.index,
-            self.tail_ctas if b.index == len(self.buckets) - 1 else self.ctas, ops._p(self.comm.ctl),
-            ops._p(self.comm.status), ctypes.c_double(self.comm.budget_ms), ctypes.c_void_p(self.stream.cuda_stream)))
+            ctypes.c_longlong(b.start), ctypes.c_longlong(b.numel), *opt, ctypes.c_float(self.grad_scale), *nd,
+            ALGOS[self.algos[b.index]], b.index, self.comm.max_buckets, self.tail_ctas if last else self.ctas,
+            ops._p(self.comm.ctl), ops._p(self.comm.status), ctypes.c_double(self.comm.budget_ms),
+            ops._p(self.gred), ops._p(self.norm_part), ops._p(self.norm_bucket), ops._p(self.tlog),
+            ctypes.c_void_p(self.stream.cuda_stream)))
+        self.launched += 1
+        if last and self.clip:
+            self._launch_clip()
+
+    def _launch_clip(self) -> None:
+        """Second phase under clipping: global norm across ranks, clip, AdamW on the owned slices, all-gather."""
+        opt, nd = self._opt_args()
+        nb = len(self.buckets)
+        ops._check(self.lib.cme_comm_clip_adamw(
+            self.world, self.comm.rank, self.params.c_ptrs, self.comm.flags.c_ptrs,
+            ctypes.c_void_p(self.params.multicast_ptr), ops._p(self.ranges), nb, ops._p(self.gred),
+            ops._p(self.norm_bucket), *opt[:5], *opt[5:], ctypes.c_float(self.model.optim.clip_norm), *nd,
+            int(self.has_multicast), nb, 2 * (nb + 1), self.comm.max_buckets, self.tail_ctas,
+            ops._p(self.comm.ctl), ops._p(self.comm.status), ctypes.c_double(self.comm.budget_ms), ops._p(self.tlog),
+            ctypes.c_void_p(self.stream.cuda_stream)))
         self.launched += 1
 
     def join(self) -> None:
         """Make the compute stream wait for every bucket kernel (parameters are then final on this rank).  With
         ``measure_exposed`` set (eager steps only) the wait is bracketed by timing events: the time the compute
         stream sits idle behind the last bucket kernels is the step's exposed synchronisation time."""
+        cur = torch.cuda.current_stream()
+        nlog = self.tlog.numel()
+        tl = self.tlog.data_ptr()
+        ops._check(self.lib.cme_record_time(ctypes.c_void_p(tl + 8 * (nlog - 2)), ctypes.c_void_p(cur.cuda_stream)))
+        ops._check(self.lib.cme_record_time(ctypes.c_void_p(tl + 8 * (nlog - 1)),
+                                            ctypes.c_void_p(self.stream.cuda_stream)))
         ev = torch.cuda.Event()
         ev.record(self.stream)
-        cur = torch.cuda.current_stream()
         if self.measure_exposed and not torch.cuda.is_current_stream_capturing():
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(cur)
@@ -157,8 +255,28 @@ class FusedSync:
         self._exposed = []
         return out
 
+    def timeline(self) -> dict:
+        """Device timestamps of the most recent step (synchronises): per bucket the start and end of its kernel
+        relative to the end of backward on the compute stream, in ms, and the exposed synchronisation time -- how
+        long after the last backward kernel the last synchronisation kernel ended (0 if it ended earlier).  Works
+        for replayed CUDA graphs, where host-side events cannot bracket the wait."""
+        torch.cuda.synchronize(self.model.device)
+        t = self.tlog.tolist()
+        bwd_end, comm_end = t[-2], t[-1]
+        nb = len(self.buckets) + (1 if self.clip else 0)
+        rel = lambda x: (x - bwd_end) / 1e6
+        return {"exposed_ms": max(0.0, rel(comm_end)),
+                "buckets": [[round(rel(t[2 * b]), 4), round(rel(t[2 * b + 1]), 4)] for b in range(nb)],
+                "bucket_mb": [round(b.numel * 2 / 2 ** 20, 2) for b in self.buckets]}
+
+    def check_status(self) -> int:
+        """Non-zero when a bounded wait of a synchronisation kernel ran out since the last check: some rank did not
+        arrive, the step's parameters are not trustworthy."""
+        return self.comm.check_status()
+
     def owned_mask(self) -> torch.Tensor:
-        """1.0 where this rank owns the optimizer state (slice ``rank`` of every bucket), else 0.0."""
+        """1.0 where this rank owns the optimizer state (slice ``rank`` of every bucket), else 0.0.  Buckets
+        synchronised one-shot are updated on every rank with identical results; the same slice is taken there."""
         mask = torch.zeros(self.model.layout.total, dtype=torch.float32, device=self.model.device)
         for b in self.buckets:
             per = b.numel // self.world
@@ -167,13 +285,15 @@ class FusedSync:
         return mask
 
     def gather_state(self):
-        """Full fp32 master / moment arenas on every rank (checkpointing): owned slices summed over ranks."""
+        """Full fp32 master / moment arenas on every rank (checkpointing): owned slices summed over ranks.
+        Collective: every rank must call it."""
         m = self.model
         mask = self.owned_mask()
         out = []
         for t in (m.master, m.adam_m, m.adam_v):
             full = t * mask
-            dist.all_reduce(full)
+            if self.world > 1:
+                dist.all_reduce(full)
             out.append(full)
         return out[0], out[1], out[2], int(m.step_dev.item())
 

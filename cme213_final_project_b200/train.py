@@ -23,12 +23,43 @@ from .trainer import Trainer
 from .utils import logfmt
 
 
+def fused_sync_obstacle(model_cfg, optim_cfg, run: RunConfig, dist_ctx: DistributedContext) -> Optional[str]:
+    """Why this run cannot use the fused device synchronisation path, or ``None`` if it can."""
+    if dist_ctx.world_size <= 1:
+        return "a single rank has nothing to synchronise"
+    if dist_ctx.device.type != "cuda":
+        return "the fused device path needs GPUs"
+    if run.comm_backend not in ("auto", "fused"):
+        return f"comm backend '{run.comm_backend}' was requested"
+    if run.engine not in ("auto", "native"):
+        return "the fused path is part of the native engine"
+    if run.compute_dtype != "bf16":
+        return "the fused kernels reduce bf16 gradients (--compute-dtype bf16)"
+    if run.comm_thread:
+        return "--comm-thread drives host-issued collectives"
+    return None
+
+
 def build_model(model_cfg, optim_cfg, run: RunConfig, dist_ctx: DistributedContext, seed: int):
-    """Native sm_100a engine on a GPU, PyTorch oracle model otherwise (or on request)."""
+    """Native sm_100a engine on a GPU, PyTorch oracle model otherwise (or on request).  With several GPU ranks the
+    engine gets the fused synchronisation path (peer-memory reduce-scatter + optimizer + all-gather kernels, the
+    multi-GPU step capturable as one CUDA graph) unless an option rules it out; the reason is then recorded in
+    ``dist_ctx.backend_note`` and host-issued NCCL all-reduces are used."""
     use_native = run.engine == "native" or (run.engine == "auto" and dist_ctx.device.type == "cuda")
     if use_native:
         from .models.engine import NativeEngine
+        why = fused_sync_obstacle(model_cfg, optim_cfg, run, dist_ctx)
+        if why is None:
+            from .parallel.fused_sync import attach_fused_sync, shard_align
+            model = NativeEngine(model_cfg, optim_cfg, run, dist_ctx, seed=seed, align=shard_align(dist_ctx.world_size))
+            attach_fused_sync(model, dist_ctx, run)
+            dist_ctx.backend, dist_ctx.backend_note = "fused", model.fused.describe()
+            return model
+        if dist_ctx.world_size > 1:
+            dist_ctx.fall_back(why)
         return NativeEngine(model_cfg, optim_cfg, run, dist_ctx, seed=seed)
+    if dist_ctx.world_size > 1:
+        dist_ctx.fall_back("the fused path is part of the native engine")
     from .models.reference import ReferenceModel
     return ReferenceModel(model_cfg, optim_cfg, device=dist_ctx.device, dtype=torch.float32, seed=seed)
 
@@ -44,8 +75,6 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         return 1
     root = d.is_root()
     say = (lambda *a: print(*a, flush=True)) if root else (lambda *a: None)
-    for line in d.banner() if d.world_size > 1 else []:
-        say(line)
     for line in environment_report(gemm_requested=run.gemm_backend):
         say(line)
     errs, warns = validate_environment(d.world_size)
@@ -87,6 +116,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         all_x, all_y = ds.all_batches()
 
     model = build_model(model_cfg, optim_cfg, run, d, run.seed)
+    for line in d.banner() if d.world_size > 1 else []:
+        say(line)
     start_step = 0
     if run.load_checkpoint:
         _, p, m, v, start_step, _ = ckpt.load_checkpoint(run.load_checkpoint, model.layout)
@@ -121,8 +152,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         if trainer.enable_cuda_graph(warmup_steps=3):
             say("CUDA Graph: enabled, capture after 3 warmup steps")
         elif root:
-            print("Warning: --cuda-graph needs the native engine and, with several ranks, the fused sync path; "
-                  "running eagerly", file=sys.stderr)
+            print("Warning: --cuda-graph needs the native engine and, with several ranks, the fused sync path"
+                  + (f" ({d.backend_note})" if d.backend_note else "") + "; running eagerly", file=sys.stderr)
 
     BT = model_cfg.tokens_per_step
     step_loss = 0.0
@@ -144,6 +175,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                 if root:
                     step_loss = model.read_loss()
                     print(ckpt.trajectory_line(epoch + 1, step + 1, step_loss, st, spans), flush=True)
+            if (step + 1) % run.log_every == 0 or step + 1 == steps_per_epoch:
+                trainer.check_device_status()                   # raises if a bounded device-side wait ran out
             if root and ((step + 1) % run.log_every == 0 or step + 1 == steps_per_epoch):
                 step_loss = model.read_loss()
                 logged_sum += step_loss
@@ -163,11 +196,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                               max_ms, tokens / (max_ms / 1e3), d.world_size, trainer.use_overlap,
                               start_ms, sync_ms, span))
 
-    if run.save_checkpoint and root:
+    if run.save_checkpoint:
+        # every rank takes part: under the fused path the optimizer state is sharded and `state` gathers it
         p, m, v, t = model.state() if hasattr(model, "state") else (model.params, model.adam_m, model.adam_v,
                                                                      model.step_count)
-        st = ckpt.save_checkpoint(run.save_checkpoint, model.layout, p, m, v, t)
-        say(f"Checkpoint: wrote {run.save_checkpoint} step={t} param_hash={st.hex_hash()}")
+        if root:
+            st = ckpt.save_checkpoint(run.save_checkpoint, model.layout, p, m, v, t)
+            say(f"Checkpoint: wrote {run.save_checkpoint} step={t} param_hash={st.hex_hash()}")
     d.finalize()
     return 0
 

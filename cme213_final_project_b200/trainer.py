@@ -124,6 +124,23 @@ class Trainer:
             m.update(grad_scale=grad_scale)
         self.steps += 1
 
+    def check_device_status(self) -> None:
+        """Read the status words of the GEMM, attention and synchronisation kernels (each synchronises the device)
+        and raise if a bounded device-side wait ran out since the last check: the step that contained it did not
+        compute, or did not distribute, what it should have.  The training driver calls this at every logging
+        point and at the end of an epoch."""
+        m = self.model
+        if getattr(m, "device", None) is None or torch.device(m.device).type != "cuda" or not hasattr(m, "lib"):
+            return
+        from . import ops
+        with torch.cuda.device(m.device):
+            bad = {"gemm": ops.gemm_check_status(), "attention": ops.attention_check_status(),
+                   "gradient sync": m.fused.check_status() if getattr(m, "fused", None) is not None else 0}
+        bad = {k: v for k, v in bad.items() if v}
+        if bad:
+            raise RuntimeError("device-side wait ran out (status " + ", ".join(f"{k}={v}" for k, v in bad.items())
+                               + f") on rank {self.dist.rank} by step {self.steps}; parameters are not trustworthy")
+
     def reset_timers(self) -> None:
         self.comm_ms_sum = 0.0
         self.async_start_ms_sum = 0.0

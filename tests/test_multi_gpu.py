@@ -37,6 +37,41 @@ def test_fused_kernel_world_of_one_equals_unfused_update():
     assert torch.allclose(a.params.float(), b.params.float(), rtol=8e-3, atol=1e-6)
 
 
+def test_two_phase_clip_kernels_world_of_one_equal_norm_plus_adam():
+    """The clip-compatible fused form (reduce-only kernels that keep fp32 gradients and their sum of squares, then
+    one clip + Adam kernel) against the separate norm and Adam kernels, on the reference's model and optimizer
+    (Adam, global-norm clip), with a threshold low enough that the clip is active."""
+    import dataclasses
+    from cme213_final_project_b200.config import RunConfig, preset
+    from cme213_final_project_b200.models.engine import NativeEngine
+    from cme213_final_project_b200.parallel.dist import DistributedContext
+    from cme213_final_project_b200.parallel.fused_sync import attach_fused_sync
+    cfg, optim = preset("parity-h128")
+    optim = dataclasses.replace(optim, clip_norm=0.05)
+    ctx = DistributedContext()
+    ctx.device = torch.device("cuda", 0)
+    a = NativeEngine(cfg, optim, RunConfig(), device="cuda", seed=3)
+    b = NativeEngine(cfg, optim, RunConfig(bucket_kb=64), device="cuda", seed=3)
+    fs = attach_fused_sync(b, ctx, RunConfig(bucket_kb=64))
+    assert fs.clip and len(fs.buckets) > 1
+    g = torch.Generator().manual_seed(1)
+    n = cfg.tokens_per_step
+    p0 = a.master.clone()
+    for _ in range(3):
+        x = torch.randint(0, cfg.vocab_size, (n,), generator=g, dtype=torch.int32).cuda()
+        y = torch.randint(0, cfg.vocab_size, (n,), generator=g, dtype=torch.int32).cuda()
+        a.train_step([x], [y]); a.update()
+        b.train_step([x], [y]); b.update()
+    torch.cuda.synchronize()
+    assert fs.check_status() == 0 and fs.launched == 3 * (len(fs.buckets) + 1)
+    upd = (a.master - p0).abs().max().item()
+    # the norm is accumulated in a different order (per bucket and CTA instead of over the whole arena)
+    assert (a.master - b.master).abs().max().item() < 1e-3 * upd + 1e-7
+    assert torch.allclose(a.params.float(), b.params.float(), rtol=8e-3, atol=1e-6)
+    tl = fs.timeline()
+    assert len(tl["buckets"]) == len(fs.buckets) + 1 and all(e >= s for s, e in tl["buckets"])
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """A device-side wait on a flag that nothing sets gives up after its budget and reports through the status word."""
     import ctypes
@@ -85,3 +120,23 @@ def test_peer_memory_collectives_and_fused_sync():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "MP_RESULT" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_training_driver_runs_the_fused_path_in_one_graph(tmp_path):
+    """The command-line driver on several GPUs: `--comm-backend fused --cuda-graph` attaches the fused kernels,
+    captures the multi-GPU step, keeps the ranks' parameters identical and writes a checkpoint (gathered from the
+    sharded optimizer state).  Clipping stays on (the reference's optimizer), so the two-phase form runs."""
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    ck = str(tmp_path / "fused.ckpt")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29643", "-m", "cme213_final_project_b200.train",
+           "--preset", "parity-h128", "--synthetic", "--epochs", "1", "--max-steps", "12", "--sync-mode", "overlap",
+           "--bucket-kb", "64", "--comm-backend", "fused", "--cuda-graph", "--log-every", "4",
+           "--save-checkpoint", ck]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "DP gradient backend: fused" in r.stdout and "CUDA Graph: enabled" in r.stdout, r.stdout[-2000:]
+    assert "checksum_span=0.000e+00" in r.stdout, r.stdout[-2000:]
+    assert os.path.exists(ck)
