@@ -89,7 +89,7 @@ def main() -> int:
     dev = ctx.device
     cfg, optim = preset(a.config)
     accum = a.grad_accum or (4 if a.config == "gpt2-medium" else 1)
-    run = RunConfig(sync_mode=a.sync_mode if world > 1 else "blocking", bucket_kb=int(a.bucket_mb * 1024),
+    run = RunConfig(sync_mode=a.sync_mode, bucket_kb=int(a.bucket_mb * 1024),
                     grad_accum=accum, comm_backend=a.comm, cuda_graph=not a.no_graph, synthetic=True)
 
     from cme213_final_project_b200.train import build_model
@@ -157,10 +157,11 @@ def main() -> int:
     # ---- exposed gradient-synchronisation time of the last timed step, from device timestamps written inside the
     # (replayed) step: end of the last synchronisation kernel minus end of backward, max over ranks ---------------
     exposed_ms, timeline = None, None
-    if world > 1 and fused is not None:
+    if fused is not None:
         timeline = fused.timeline()
         t = torch.tensor([timeline["exposed_ms"]], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
         exposed_ms = t.item()
 
     # ---- validity: status words (max over ranks) and the cross-rank parameter checksum span -------------------
@@ -191,8 +192,9 @@ def main() -> int:
             "impl": "ours",
             "config": {"model": a.config, "global_batch": cfg.batch_size * accum * world, "seq_len": cfg.seq_len,
                        "micro_batch_per_gpu": cfg.batch_size, "grad_accum": accum,
-                       "parallelism": f"dp{world}", "sync": (f"{ctx.backend}/{run.sync_mode}/bucket_mb={a.bucket_mb}" if world > 1
-                                else "none (single rank: separate AdamW kernel)"),
+                       "parallelism": f"dp{world}", "sync": (f"{ctx.backend}/{run.sync_mode}/bucket_mb={a.bucket_mb}" if world > 1 else
+                                "single rank: " + ("AdamW per bucket on a second stream under backward"
+                                                   if fused is not None else "separate AdamW kernel")),
                        "sync_detail": ctx.backend_note or None,
                        "cuda_graph": bool(graphed), "optimizer": "adamw" if optim.weight_decay > 0 else "adam+clip",
                        "l2": "per-step working set (activations + weights, several GB) is far larger than the 126 MB L2"},

@@ -14,7 +14,18 @@ runs under a timeout, results land in one JSON file per experiment under --out.
     python benchmarks/run_experiments.py trajectory --preset parity-h128 --gpus 2 --steps 12
     python benchmarks/run_experiments.py edge      --gpus 3            # non-power-of-two ranks, odd batch
     python benchmarks/run_experiments.py matrix                        # pytest groups -> markdown table
+    python benchmarks/run_experiments.py fusion    --preset gpt2-small --steps 30      # fusion ablation of the step
+    python benchmarks/run_experiments.py graph     --preset parity-h256 --steps 200    # CUDA graph vs eager
+    python benchmarks/run_experiments.py null      --preset parity-h256 --repeats 6    # run-to-run noise floor
+    python benchmarks/run_experiments.py lr        --preset parity-h512 --lrs 2e-5 5e-5 1e-4 3e-4
+    python benchmarks/run_experiments.py ucurve    --preset gpt2-small --gpus 8 --bucket-kb 1024 8192 25600 102400 \
+                                                   --fits allreduce_8gpu.json      # bucket U-curve + alpha-beta prediction
+    python benchmarks/run_experiments.py precision                                 # GEMM error per backend / precision
     python benchmarks/run_experiments.py check --out results           # artifact audit
+
+Further reference scripts covered here: run_fusion_ablation.sh, cuda_graph_bench.sh, run_null_variance_bench.sh,
+run_h512_lr_sweep.sh, summarize_bucket_ucurve.py + predict_comm_model.py, run_gemm_precision_validation.sh.
+Every experiment leaves one JSON file and one markdown table under --out.
 """
 import argparse
 import json
@@ -45,10 +56,12 @@ def train_cmd(gpus, args):
             "cme213_final_project_b200.train"] + args
 
 
-def run(gpus, args, timeout=1800):
+def run(gpus, args, timeout=1800, env_extra=None):
     t0 = time.time()
+    env = clean_env()
+    env.update(env_extra or {})
     try:
-        r = subprocess.run(train_cmd(gpus, args), capture_output=True, text=True, timeout=timeout, env=clean_env(),
+        r = subprocess.run(train_cmd(gpus, args), capture_output=True, text=True, timeout=timeout, env=env,
                            cwd=ROOT)
         out, rc = r.stdout + "\n" + r.stderr[-2000:], r.returncode
     except subprocess.TimeoutExpired as e:
@@ -64,11 +77,31 @@ def base_args(a):
     return args
 
 
-def save(a, name, obj):
+def save(a, name, obj, table=None):
+    """One JSON file per experiment and, when `table` = (header, rows) is given, the same numbers as markdown."""
     os.makedirs(a.out, exist_ok=True)
     path = os.path.join(a.out, name + ".json")
     json.dump(obj, open(path, "w"), indent=1)
     print(f"[harness] wrote {path}")
+    if table:
+        head, rows = table
+        with open(os.path.join(a.out, name + ".md"), "w") as f:
+            f.write("| " + " | ".join(head) + " |\n|" + "---|" * len(head) + "\n")
+            for r in rows:
+                f.write("| " + " | ".join("" if v is None else (f"{v:.4g}" if isinstance(v, float) else str(v))
+                                          for v in r) + " |\n")
+
+
+def sync_timeline(text):
+    """The `SYNC_TIMELINE {json}` line the trainer prints after an epoch on the fused path (device timestamps of the
+    last step's bucket kernels), or None."""
+    for line in reversed(text.splitlines()):
+        if line.startswith("SYNC_TIMELINE "):
+            try:
+                return json.loads(line[len("SYNC_TIMELINE "):])
+            except ValueError:
+                return None
+    return None
 
 
 def cmd_repeated(a):
@@ -120,29 +153,158 @@ def cmd_scaling(a):
 
 
 def cmd_trajectory(a):
-    modes = {"blocking": ["--sync-mode", "blocking"], "overlap": ["--sync-mode", "overlap", "--bucket-kb", "256"],
-             "comm_thread": ["--sync-mode", "overlap", "--comm-thread", "--bucket-kb", "256"],
-             "deferred": ["--sync-mode", "blocking", "--defer-grad-avg"]}
+    # the host-issued NCCL modes (blocking is the yardstick, as in the reference) and the fused device path, eager
+    # and as one CUDA graph per step
+    nccl = ["--comm-backend", "nccl"]
+    modes = {"blocking": ["--sync-mode", "blocking"] + nccl,
+             "overlap": ["--sync-mode", "overlap", "--bucket-kb", "256"] + nccl,
+             "comm_thread": ["--sync-mode", "overlap", "--comm-thread", "--bucket-kb", "256"] + nccl,
+             "deferred": ["--sync-mode", "blocking", "--defer-grad-avg"] + nccl,
+             "fused": ["--sync-mode", "overlap", "--bucket-kb", "256", "--comm-backend", "fused"],
+             "fused_graph": ["--sync-mode", "overlap", "--bucket-kb", "256", "--comm-backend", "fused", "--cuda-graph"]}
     traj = {}
     for name, flags in modes.items():
         out, rc, _ = run(a.gpus[0], base_args(a) + ["--trace-trajectory"] + flags + a.extra)
         traj[name] = parse_trajectory(out)
         print(f"[trajectory] {name}: {len(traj[name])} steps rc={rc}")
     res = {name: compare_trajectories(traj["blocking"], t) for name, t in traj.items() if name != "blocking"}
-    save(a, f"trajectory_{a.preset}_g{a.gpus[0]}", {"comparisons": res, "all_ok": all(r["ok"] for r in res.values())})
+    spans = {name: max([max(s.sum_span, s.sumsq_span, s.maxabs_span) for s in t] or [float("nan")])
+             for name, t in traj.items()}
+    rows = [[name, len(traj[name]), res[name]["ok"] if name in res else True, spans[name]] for name in modes]
+    save(a, f"trajectory_{a.preset}_g{a.gpus[0]}",
+         {"comparisons": res, "cross_rank_span": spans, "all_ok": all(r["ok"] for r in res.values())},
+         (["mode", "steps", "within tolerance of blocking", "largest cross-rank span"], rows))
 
 
 def cmd_edge(a):
     cases = [("ranks", a.gpus[0], []), ("batch31", a.gpus[0], ["--batch-size", "31"])]
     res = []
     for name, g, flags in cases:
-        for mode in ("blocking", "overlap"):
-            out, rc, _ = run(g, base_args(a) + ["--sync-mode", mode] + flags + a.extra)
+        for mode, backend in (("blocking", "nccl"), ("overlap", "nccl"), ("overlap", "fused")):
+            out, rc, _ = run(g, base_args(a) + ["--sync-mode", mode, "--comm-backend", backend] + flags + a.extra)
             s = parse_run(out)
-            res.append({"case": name, "gpus": g, "sync_mode": mode, "valid": s.valid and rc == 0, "reason": s.reason,
-                        "tok_s": s.last.tok_s if s.last else None})
-            print(f"[edge] {name} {mode}: valid={res[-1]['valid']}")
-    save(a, "edge_cases", res)
+            res.append({"case": name, "gpus": g, "sync_mode": mode, "backend": backend,
+                        "valid": s.valid and rc == 0, "reason": s.reason,
+                        "tok_s": s.last.tok_s if s.last else None,
+                        "checksum_span": s.last.checksum_span if s.last else None})
+            print(f"[edge] {name} {mode}/{backend}: valid={res[-1]['valid']}")
+    save(a, "edge_cases", res, (["case", "gpus", "sync", "backend", "valid", "tok/s", "checksum span"],
+                                [[r["case"], r["gpus"], r["sync_mode"], r["backend"], r["valid"], r["tok_s"],
+                                  r["checksum_span"]] for r in res]))
+
+
+def _one(a, label, flags=(), env=None, gpus=None):
+    out, rc, wall = run(gpus or a.gpus[0], base_args(a) + list(flags) + a.extra, env_extra=env)
+    s = parse_run(out)
+    row = {"variant": label, "rc": rc, "valid": s.valid and rc == 0, "reason": s.reason,
+           "tok_s": s.last.tok_s if s.last else None, "loss": s.last.loss if s.last else None,
+           "ms_per_step": (s.last.ms / max(s.last.steps, 1)) if s.last else None, "wall_s": round(wall, 1)}
+    print(f"[{a.experiment}] {label}: tok/s={row['tok_s']} valid={row['valid']}")
+    return row, out
+
+
+def cmd_fusion(a):
+    """Fusion ablation of the training step (the reference's run_fusion_ablation.sh: the same run with and without
+    its epilogue fusion).  Variants: everything on; bias / activation / residual / activation-derivative as separate
+    kernels after plain products; the GELU derivative re-evaluated in backward with the bias gradient as its own
+    kernel; weight-gradient products on the main stream instead of the second one."""
+    variants = [("all fusions", [], {}),
+                ("no epilogue fusion", ["--no-epilogue-fusion"], {}),
+                ("derivative recomputed, separate bias gradient", [], {"CME213_FFN_DERIV": "0"}),
+                ("weight gradients on the main stream", [], {"CME213_WGRAD_STREAM": "0"})]
+    graph = ["--cuda-graph"] if a.cuda_graph else []
+    rows = [_one(a, label, graph + flags, env)[0] for label, flags, env in variants]
+    base = rows[0]["tok_s"]
+    for r in rows:
+        r["relative_to_all"] = (r["tok_s"] / base) if (r["tok_s"] and base) else None
+    save(a, f"fusion_ablation_{a.preset}_g{a.gpus[0]}", rows,
+         (["variant", "valid", "tok/s", "ms/step", "vs all fusions"],
+          [[r["variant"], r["valid"], r["tok_s"], r["ms_per_step"], r["relative_to_all"]] for r in rows]))
+
+
+def cmd_graph(a):
+    """Whole-step CUDA graph against eager launches (the reference's cuda_graph_bench.sh / CME213_USE_CUDA_GRAPH)."""
+    rows = []
+    for label, flags in (("eager", []), ("cuda graph", ["--cuda-graph"])):
+        toks = []
+        for _ in range(a.repeats):
+            r, _ = _one(a, label, flags)
+            toks.append(r["tok_s"] if r["valid"] else float("nan"))
+        rows.append({"mode": label, **summarize_repeats(toks, [t == t for t in toks], a.min_repeat)})
+    e, g = rows[0].get("mean"), rows[1].get("mean")
+    speed = (g / e) if (e and g) else None
+    save(a, f"graph_vs_eager_{a.preset}_g{a.gpus[0]}", {"rows": rows, "graph_speedup": speed},
+         (["mode", "runs", "mean tok/s", "cv"], [[r["mode"], r.get("runs"), r.get("mean"), r.get("cv")] for r in rows]))
+
+
+def cmd_null(a):
+    """Null-variance run: the same configuration repeated; what differs between identical runs is the noise floor any
+    claimed speed-up has to clear (the reference's run_null_variance_bench.sh)."""
+    toks, valid = [], []
+    for rep in range(a.repeats):
+        r, _ = _one(a, f"repeat {rep + 1}", ["--cuda-graph"] if a.cuda_graph else [])
+        toks.append(r["tok_s"] if r["tok_s"] else float("nan"))
+        valid.append(bool(r["valid"]))
+    summ = summarize_repeats(toks, valid, a.min_repeat)
+    warm = [t for t, v in list(zip(toks, valid))[a.min_repeat - 1:] if v]
+    spread = (max(warm) - min(warm)) / (sum(warm) / len(warm)) if len(warm) > 1 else None
+    save(a, f"null_variance_{a.preset}_g{a.gpus[0]}", {"tok_s": toks, "valid": valid, "summary": summ,
+                                                        "max_minus_min_over_mean": spread},
+         (["repeat", "tok/s", "valid"], [[i + 1, t, v] for i, (t, v) in enumerate(zip(toks, valid))]))
+
+
+def cmd_lr(a):
+    """Learning-rate sweep: final logged loss per rate (the reference's run_h512_lr_sweep.sh)."""
+    rows = []
+    for lr in a.lrs:
+        r, _ = _one(a, f"lr={lr:g}", ["--lr", str(lr)])
+        rows.append({"lr": lr, **r})
+    ok = [r for r in rows if r["valid"] and r["loss"] is not None]
+    best = min(ok, key=lambda r: r["loss"])["lr"] if ok else None
+    save(a, f"lr_sweep_{a.preset}_g{a.gpus[0]}", {"rows": rows, "best_lr": best},
+         (["lr", "valid", "final loss", "tok/s"], [[r["lr"], r["valid"], r["loss"], r["tok_s"]] for r in rows]))
+
+
+def cmd_ucurve(a):
+    """Bucket-size U-curve on the fused path with the alpha-beta prediction beside the measurement (the reference's
+    summarize_bucket_ucurve.py and predict_comm_model.py:109-139).  Measured: throughput, exposed synchronisation time
+    and summed device time of the bucket kernels of the last step (from the trainer's SYNC_TIMELINE line).
+    Predicted: sum over buckets of alpha + beta * bytes with the fit of --fits (bench_allreduce.py --json)."""
+    from cme213_final_project_b200.parallel.comm_model import predict_bucketed
+    fits = None
+    if a.fits and os.path.exists(a.fits):
+        f = json.load(open(a.fits)).get("fits", {})
+        fits = f.get("nvls") or f.get("two_shot")
+    rows = []
+    for kb in a.bucket_kb:
+        r, out = _one(a, f"bucket_kb={kb}", ["--sync-mode", "overlap", "--bucket-kb", str(kb), "--comm-backend", "fused"]
+                      + (["--cuda-graph"] if a.cuda_graph else []))
+        tl = sync_timeline(out)
+        row = {"bucket_kb": kb, **r, "buckets": len(tl["buckets"]) if tl else None,
+               "exposed_ms": tl["exposed_ms"] if tl else None,
+               "kernel_ms_sum": sum(e - s for s, e in tl["buckets"]) if tl else None, "predicted_ms": None}
+        if tl and fits:
+            row["predicted_ms"] = predict_bucketed(fits["alpha_ms"], fits["beta_ms_per_mb"] / (1 << 20),
+                                                   [mb * (1 << 20) for mb in tl["bucket_mb"]])
+        rows.append(row)
+    save(a, f"bucket_ucurve_{a.preset}_g{a.gpus[0]}", rows,
+         (["bucket KB", "buckets", "tok/s", "exposed ms", "bucket kernels ms (sum)", "alpha-beta prediction ms"],
+          [[r["bucket_kb"], r["buckets"], r["tok_s"], r["exposed_ms"], r["kernel_ms_sum"], r["predicted_ms"]]
+           for r in rows]))
+
+
+def cmd_precision(a):
+    """GEMM error per backend and precision at the reference's test sizes (64^3 ... 512^3), against an fp64 product
+    (run_gemm_precision_validation.sh reruns test_gemm under its three precision settings; tolerances there:
+    custom 1e-5, cuBLAS strict 1e-3, tensor cores 5e-3, FINAL_CLEAN_CODE_/tests/test_gemm.cu:28-105)."""
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", "gemm_precision.py")], capture_output=True,
+                       text=True, cwd=ROOT, timeout=1800, env=clean_env())
+    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    print(r.stdout[-2000:] + r.stderr[-1000:])
+    save(a, "gemm_precision", {"rc": r.returncode, "rows": rows, "all_pass": bool(rows) and all(x["pass"] for x in rows)},
+         (["backend", "storage", "size", "max rel err", "tolerance", "pass"],
+          [[x["backend"], x["storage"], x["size"], x["max_rel_err"], x["tol"], x["pass"]] for x in rows]))
+    return 0 if r.returncode == 0 and rows and all(x["pass"] for x in rows) else 1
 
 
 def cmd_matrix(a):
@@ -167,26 +329,82 @@ def cmd_matrix(a):
     save(a, "correctness_matrix", rows)
 
 
+def _numbers(obj):
+    if isinstance(obj, bool) or obj is None:
+        return
+    if isinstance(obj, (int, float)):
+        yield obj
+    elif isinstance(obj, dict):
+        for v in obj.values():
+            yield from _numbers(v)
+    elif isinstance(obj, (list, tuple)):
+        for v in obj:
+            yield from _numbers(v)
+
+
+# what each kind of result file must contain: (key that every row has, name of its validity flag or None)
+_RESULT_RULES = {"repeated_": ("runs", "valid"), "buckets_": (None, "valid"), "weak_scaling_": (None, "valid"),
+                 "strong_scaling_": (None, "valid"), "trajectory_": ("comparisons", None), "edge_cases": (None, "valid"),
+                 "fusion_ablation_": (None, "valid"), "graph_vs_eager_": ("rows", None), "null_variance_": ("tok_s", None),
+                 "lr_sweep_": ("rows", "valid"), "bucket_ucurve_": (None, "valid"), "gemm_precision": ("rows", "pass"),
+                 "correctness_matrix": (None, None)}
+
+
 def cmd_check(a):
-    """Artifact audit: every result file parses, is non-empty and has no non-finite number."""
-    bad = []
+    """Artifact audit (the reference's check_artifacts.py): every result file parses, is non-empty, holds only finite
+    numbers, has the rows its experiment produces, every row's validity flag is true, and its markdown twin exists
+    where the experiment writes one.  Prints one line per file and a summary; exit status 1 if anything is wrong."""
+    import math
+    problems, seen = [], 0
     for fn in sorted(os.listdir(a.out)) if os.path.isdir(a.out) else []:
         if not fn.endswith(".json"):
             continue
+        seen += 1
+        why = []
         try:
             txt = open(os.path.join(a.out, fn)).read()
             obj = json.loads(txt)
-            if not obj or "NaN" in txt or "Infinity" in txt:
-                bad.append(fn)
-        except Exception:
-            bad.append(fn)
-    print(f"[check] {'OK' if not bad else 'BAD: ' + ', '.join(bad)}")
-    return 1 if bad else 0
+        except Exception as e:
+            problems.append((fn, [f"unreadable: {e}"]))
+            continue
+        if not obj:
+            why.append("empty")
+        if any(isinstance(x, float) and not math.isfinite(x) for x in _numbers(obj)):
+            why.append("non-finite number")
+        rule = next((r for k, r in _RESULT_RULES.items() if fn.startswith(k)), None)
+        if rule is None:
+            why.append("unknown experiment")
+        else:
+            key, flag = rule
+            rows = obj.get(key) if (key and isinstance(obj, dict)) else obj
+            if key and isinstance(obj, dict) and key not in obj:
+                why.append(f"missing '{key}'")
+            if isinstance(rows, dict) and isinstance(rows.get("rows"), list):
+                rows = rows["rows"]
+            if flag and isinstance(rows, list):
+                bad = [i for i, r in enumerate(rows) if isinstance(r, dict) and not r.get(flag, False)]
+                if not rows:
+                    why.append("no rows")
+                if bad:
+                    why.append(f"rows not {flag}: {bad}")
+            if isinstance(obj, dict) and obj.get("all_ok") is False:
+                why.append("a comparison is outside its tolerance")
+        if fn.startswith(("trajectory_", "edge_cases", "fusion_", "graph_", "null_", "lr_", "bucket_ucurve", "gemm_prec")) \
+                and not os.path.exists(os.path.join(a.out, fn[:-5] + ".md")):
+            why.append("markdown table missing")
+        print(f"[check] {fn}: {'OK' if not why else '; '.join(why)}")
+        if why:
+            problems.append((fn, why))
+    print(f"[check] {seen} result files, {len(problems)} with problems")
+    return 1 if problems or not seen else 0
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("experiment", choices=["repeated", "buckets", "scaling", "trajectory", "edge", "matrix", "check"])
+    ap.add_argument("experiment", choices=["repeated", "buckets", "scaling", "trajectory", "edge", "matrix", "check",
+                                           "fusion", "graph", "null", "lr", "ucurve", "precision"])
+    ap.add_argument("--lrs", type=float, nargs="+", default=[2e-5, 5e-5, 1e-4, 3e-4])
+    ap.add_argument("--fits", default=None, help="bench_allreduce.py --json output holding the alpha-beta fits")
     ap.add_argument("--preset", default="parity-h256")
     ap.add_argument("--gpus", type=int, nargs="+", default=[1])
     ap.add_argument("--steps", type=int, default=100)
@@ -206,7 +424,8 @@ def main():
     if not a.synthetic and not os.path.exists(a.data):
         a.synthetic = True
     fn = {"repeated": cmd_repeated, "buckets": cmd_buckets, "scaling": cmd_scaling, "trajectory": cmd_trajectory,
-          "edge": cmd_edge, "matrix": cmd_matrix, "check": cmd_check}[a.experiment]
+          "edge": cmd_edge, "matrix": cmd_matrix, "check": cmd_check, "fusion": cmd_fusion, "graph": cmd_graph,
+          "null": cmd_null, "lr": cmd_lr, "ucurve": cmd_ucurve, "precision": cmd_precision}[a.experiment]
     sys.exit(fn(a) or 0)
 
 

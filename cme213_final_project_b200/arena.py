@@ -154,16 +154,26 @@ class ArenaLayout:
         assert flat.numel() >= self.total, (flat.numel(), self.total)
         return {s.name: flat[s.offset:s.offset + s.numel].view(*s.shape) for s in self.specs}
 
-    def coalesced_buckets(self, min_elems: int) -> List[Bucket]:
+    def coalesced_buckets(self, min_elems: int, merge_tail: bool = False) -> List[Bucket]:
         """Merge adjacent natural buckets, in emission order, until each has at least ``min_elems``
         elements (the reference's ``--bucket-kb`` rule, ``transformer.cu:428-457``).  A trailing
-        remainder smaller than the floor is still emitted (flush at the end of backward)."""
+        remainder smaller than the floor is still emitted (flush at the end of backward).
+
+        ``merge_tail`` (models with several blocks): the gradients that only become final in the last stretch of
+        backward -- block 0 and the embeddings -- form one bucket, and the buckets before it are cut so that the
+        last of them completes when block 1 does (a remainder below the floor joins its predecessor).  A bucket
+        that ends inside block 0 would be launched at the very end of backward and delay the embedding bucket
+        behind it; this way one kernel handles everything that cannot overlap, and nothing else is left."""
         if min_elems <= 0:
             return list(self.natural_buckets)
+        nat = self.natural_buckets
+        tail_at = len(nat)
+        if merge_tail and self.cfg.layers > 1 and "h0.W2" in self.by_name:
+            tail_at = self.by_name["h0.W2"].bucket
         out: List[Bucket] = []
         start: Optional[int] = None
         names: List[str] = []
-        for b in self.natural_buckets:
+        for b in nat[:tail_at]:
             if start is None:
                 start = b.start
             names += list(b.names)
@@ -171,7 +181,15 @@ class ArenaLayout:
                 out.append(Bucket(len(out), start, b.end, tuple(names)))
                 start, names = None, []
         if start is not None:
-            out.append(Bucket(len(out), start, self.natural_buckets[-1].end, tuple(names)))
+            end = nat[tail_at - 1].end
+            if tail_at < len(nat) and out:      # remainder before the tail group: joins the bucket before it
+                prev = out.pop()
+                out.append(Bucket(len(out), prev.start, end, prev.names + tuple(names)))
+            else:
+                out.append(Bucket(len(out), start, end, tuple(names)))
+        if tail_at < len(nat):
+            tnames = tuple(n for b in nat[tail_at:] for n in b.names)
+            out.append(Bucket(len(out), nat[tail_at].start, nat[-1].end, tnames))
         return out
 
     def bucket_ready_after(self, buckets: Sequence[Bucket]) -> Dict[int, int]:

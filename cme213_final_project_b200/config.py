@@ -113,6 +113,7 @@ class RunConfig:
     device: str = "auto"           # auto | cuda | cpu
     engine: str = "auto"           # auto | native | torch
     log_every: int = 100
+    epilogue_fusion: bool = True   # False: bias / activation / residual as separate kernels (ablation)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -252,6 +253,8 @@ def apply_environment(run: RunConfig, env: Optional[Dict[str, str]] = None) -> R
         run.comm_thread = True
     if env_enabled("CME213_USE_NCCL", e) and env_enabled("CME213_ALLOW_UNVALIDATED_NCCL", e):
         run.comm_backend = "nccl"
+    if e.get("CME213_LT_FUSION") == "0":          # the reference's epilogue-fusion switch, here on by default
+        run.epilogue_fusion = False
     if env_enabled("CME213_STRICT_FP32", e):
         run.compute_dtype = "fp32"
     b = e.get("CME213_GEMM_BACKEND")
@@ -304,6 +307,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--device", default="auto")
     p.add_argument("--engine", default="auto")
     p.add_argument("--log-every", type=int, default=100)
+    p.add_argument("--no-epilogue-fusion", action="store_true",
+                   help="run bias / activation / residual / activation-derivative as separate kernels (ablation)")
     return p
 
 
@@ -328,7 +333,8 @@ def parse_args(argv: Optional[Sequence[str]] = None) -> Tuple[ModelConfig, Optim
                     cuda_graph=a.cuda_graph, grad_accum=a.grad_accum, gemm_backend=a.gemm_backend,
                     compute_dtype=a.compute_dtype, synthetic=a.synthetic, seed=a.seed,
                     save_checkpoint=a.save_checkpoint, load_checkpoint=a.load_checkpoint, profile=a.profile,
-                    device=a.device, engine=a.engine, log_every=a.log_every)
+                    device=a.device, engine=a.engine, log_every=a.log_every,
+                    epilogue_fusion=not a.no_epilogue_fusion)
     return model, optim, apply_environment(run)
 
 

@@ -23,7 +23,7 @@ from ..config import ModelConfig, OptimConfig, RunConfig
 
 class _EngineDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("V", "T", "D", "H", "FF", "L", "B", "act", "causal", "head_flat", "tied",
-                                             "final_ln", "fused_qkv")] + \
+                                             "final_ln", "fused_qkv", "fuse_epilogues")] + \
                [("ln_eps", ctypes.c_float), ("prob_eps", ctypes.c_float)] + \
                [(n, ctypes.c_int) for n in ("dtype", "gemm_backend", "attn_backend")]
 
@@ -91,7 +91,8 @@ class NativeEngine:
         d = _EngineDesc(V=cfg.vocab_size, T=cfg.seq_len, D=cfg.hidden, H=cfg.heads, FF=cfg.ff, L=cfg.layers,
                         B=cfg.batch_size, act=ops.ACT[cfg.activation], causal=int(cfg.causal),
                         head_flat=int(cfg.head_layout == "flat"), tied=int(cfg.tied_embeddings),
-                        final_ln=int(cfg.final_layernorm), fused_qkv=int(cfg.mode == "gpt"), ln_eps=cfg.ln_eps,
+                        final_ln=int(cfg.final_layernorm), fused_qkv=int(cfg.mode == "gpt"),
+                        fuse_epilogues=int(run.epilogue_fusion), ln_eps=cfg.ln_eps,
                         prob_eps=1e-9 if cfg.mode == "parity" else 0.0, dtype=ops.F32 if self.strict else ops.BF16,
                         gemm_backend=2 if self.strict else gemm_backend, attn_backend=2 if self.strict else 0)
         off = lambda name: self.layout.by_name[name].offset if name in self.layout.by_name else -1
@@ -113,10 +114,25 @@ class NativeEngine:
                                             ctypes.c_void_p(self.grads.data_ptr()), ctypes.c_void_p(base),
                                             ctypes.c_longlong(nbytes)))
         self._ws_base, self._ws_bytes = base, nbytes
+        # weight-gradient products on a second stream beside the input-gradient chain (CME213_WGRAD_STREAM=0: off)
+        import os
+        self.overlap_wgrad = False
+        self.set_overlap(os.environ.get("CME213_WGRAD_STREAM", "1") != "0")
         self._tokens: Optional[torch.Tensor] = None
         self._cb_keepalive = None
         self.fused = None                 # set by parallel.fused_sync.attach_fused_sync
         self.handles_sync = False
+
+    def set_overlap(self, on: bool) -> None:
+        """Run the weight-gradient products of backward on the engine's second stream (outside stream capture)."""
+        with torch.cuda.device(self.device):
+            ops._check(self.lib.cme_engine_set_overlap(self._h, int(bool(on))))
+        self.overlap_wgrad = bool(on)
+
+    def fence(self, target: "torch.cuda.Stream") -> None:
+        """Make ``target`` wait for everything backward has enqueued so far, on the current stream and on the
+        engine's second stream: call it from a bucket callback before reading the bucket on ``target``."""
+        ops._check(self.lib.cme_engine_fence(self._h, ops._stream(), ctypes.c_void_p(target.cuda_stream)))
 
     def rebind(self, params: torch.Tensor, grads: torch.Tensor) -> None:
         """Point the executor at other parameter / gradient arenas (e.g. symmetric, peer-mapped buffers)."""

@@ -42,6 +42,8 @@ class CmeGemm(ctypes.Structure):
         ("act", ctypes.c_int), ("dact", ctypes.c_int), ("accumulate", ctypes.c_int),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_longlong),
         ("force_bn", ctypes.c_int), ("force_splits", ctypes.c_int),
+        ("aux_deriv", ctypes.c_int),
+        ("colsum", ctypes.c_void_p), ("colsum_slabs", ctypes.POINTER(ctypes.c_int)),
     ]
 
 
@@ -126,13 +128,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_trans: bool = False, b_trans: bo
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
          bias: Optional[torch.Tensor] = None, act: Optional[str] = None, aux_out: Optional[torch.Tensor] = None,
          dact: Optional[str] = None, aux_in: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-         accumulate: bool = False, backend: str = "auto", force_bn: int = 0, force_splits: int = 0) -> torch.Tensor:
+         accumulate: bool = False, backend: str = "auto", force_bn: int = 0, force_splits: int = 0,
+         aux_deriv: bool = False, dbias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out (+)= epilogue(op(a) @ op(b))`` for 2-D or batched 3-D row-major operands.
 
     ``a``: ``[M, K]`` (or ``[K, M]`` with ``a_trans``); ``b``: ``[K, N]`` (or ``[N, K]`` with ``b_trans``);
     a leading batch dimension on either operand makes the product batched (a 2-D operand is shared).
     Epilogue order: ``+bias`` -> store pre-activation to ``aux_out`` -> ``act`` -> ``* act'(aux_in)`` (``dact``)
     -> ``+residual`` -> ``+out`` (``accumulate``).  ``backend``: ``auto`` | ``tcgen05`` | ``simt``.
+    ``aux_deriv``: the auxiliary tensor holds ``act'(pre-activation)`` instead of the pre-activation (forward
+    stores it, backward multiplies by it).  ``dbias`` (a ``[N]`` tensor): receives the column sums of ``out`` --
+    from the GEMM's own epilogue when the kernel that runs can produce them, else from a separate pass.
     """
     _cuda(a, b, out, bias, aux_out, aux_in, residual)
     batch = 1
@@ -164,7 +170,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_trans: bool = False, b_trans: bo
     g.act, g.dact, g.accumulate = ACT[act], ACT[dact], int(accumulate)
     g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel() * 4
     g.force_bn, g.force_splits = force_bn, force_splits
+    g.aux_deriv = int(aux_deriv)
+    slabs = ctypes.c_int(0)
+    if dbias is not None:
+        part = torch.empty((M + 31) // 32 * N, dtype=torch.float32, device=a.device)
+        g.colsum, g.colsum_slabs = part.data_ptr(), ctypes.pointer(slabs)
     _check(lib().cme_gemm(ctypes.byref(g), {"auto": 0, "tcgen05": 1, "simt": 2}[backend], _stream()))
+    if dbias is not None:
+        gemm.last_colsum_slabs = slabs.value          # 0: the epilogue did not sum (tests look at this)
+        if slabs.value:
+            _check(lib().cme_colsum_slabs_finalize(_dt(dbias), _p(part), slabs.value, N, _p(dbias), 0, _stream()))
+        else:
+            dact_colsum(out.reshape(-1, N), want_g=False, dbias=dbias)
     return out
 
 

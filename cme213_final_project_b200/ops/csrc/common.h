@@ -166,6 +166,15 @@ __device__ __forceinline__ float dgelu_fast(float x) {
     return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
 }
 
+// GELU and its derivative from one hardware tanh (the forward epilogue that also leaves the derivative for backward).
+__device__ __forceinline__ void gelu_and_grad_fast(float x, float& g, float& d) {
+    const float x2 = x * x;
+    const float t = tanh_fast(x * fmaf(0.0356774081f, x2, 0.7978845608f));
+    const float hx = 0.5f * x;
+    g = fmaf(hx, t, hx);
+    d = fmaf(hx * fmaf(-t, t, 1.f), fmaf(0.1070322243f, x2, 0.7978845608f), fmaf(0.5f, t, 0.5f));
+}
+
 // 8 x bf16 <-> 8 x f32 through one 128-bit word (a uint4, so loads and stores stay single 128-bit accesses).
 typedef uint4 Bf16x8;
 __device__ __forceinline__ float2 bf2_to_f2(uint32_t w) {

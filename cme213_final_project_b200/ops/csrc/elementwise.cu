@@ -311,6 +311,39 @@ int bias_act_res_t(const void* x, const void* bias, const void* res, void* pre, 
     return CME_OK;
 }
 
+// dbias[c] (+)= sum over the `slabs` rows of partial[slabs][cols], added in a fixed order: a block covers 32 columns
+// with 8 row groups; each thread sums every 8th row (four independent chains), then the 8 groups are added in
+// shared memory.  The rows come from a GEMM epilogue that sums its stored output per 32-row slab.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_slabs_finalize_kernel(const float* __restrict__ partial, int slabs, int cols, T* dbias, int accumulate) {
+    __shared__ float sm[8][33];
+    pdl_wait();
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
+    float s = 0.f;
+    if (c < cols) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        int r = ry;
+        for (; r + 24 < slabs; r += 32) {
+            s0 += partial[(long long)r * cols + c];
+            s1 += partial[(long long)(r + 8) * cols + c];
+            s2 += partial[(long long)(r + 16) * cols + c];
+            s3 += partial[(long long)(r + 24) * cols + c];
+        }
+        for (; r < slabs; r += 8) s0 += partial[(long long)r * cols + c];
+        s = (s0 + s1) + (s2 + s3);
+    }
+    sm[ry][cx] = s;
+    __syncthreads();
+    if (ry == 0 && c < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) t += sm[g][cx];
+        dbias[c] = from_f32<T>(accumulate ? to_f32<T>(dbias[c]) + t : t);
+    }
+}
+
 template <typename T>
 int dact_colsum_t(const void* dout, const void* pre, void* g, void* dbias, float* scratch, int splits, int rows,
                   int cols, int act, int accumulate, cudaStream_t st) {
@@ -366,6 +399,21 @@ CME_API int cme_dact_colsum(int dtype, const void* dout, const void* pre, void* 
     return DISPATCH_T(dtype,
                       dact_colsum_t<__nv_bfloat16>(dout, pre, g, dbias, scratch, splits, rows, cols, act, accumulate, st),
                       dact_colsum_t<float>(dout, pre, g, dbias, scratch, splits, rows, cols, act, accumulate, st));
+}
+
+// dbias (+)= column sums of partial[slabs][cols] (the per-slab sums a GEMM epilogue left, gemm.h: colsum).
+CME_API int cme_colsum_slabs_finalize(int dtype, const float* partial, int slabs, int cols, void* dbias, int accumulate,
+                                      void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    CME_REQUIRE(slabs > 0 && cols > 0, CME_ERR_SHAPE, "colsum finalize: empty input");
+    if (dtype == CME_BF16)
+        CME_CUDA(cme_launch_dependent(colsum_slabs_finalize_kernel<__nv_bfloat16>, dim3(cme_cdiv(cols, 32)), dim3(256), 0,
+                                      st, partial, slabs, cols, (__nv_bfloat16*)dbias, accumulate));
+    else
+        CME_CUDA(cme_launch_dependent(colsum_slabs_finalize_kernel<float>, dim3(cme_cdiv(cols, 32)), dim3(256), 0, st,
+                                      partial, slabs, cols, (float*)dbias, accumulate));
+    CME_LAUNCH_CHECK();
+    return CME_OK;
 }
 
 CME_API int cme_scale(int dtype, void* x, long long n, float s, void* stream) {

@@ -11,10 +11,15 @@
 //   * weight gradients overwrite (or accumulate, for micro-batches after the first), so there is no
 //     gradient memset per step (the reference zeroes all gradients because split-K uses atomics);
 //   * `bucket_ready(index)` is called on the host right after the launches that complete a natural gradient
-//     bucket have been enqueued, in arena order -- the hook the reference calls sync_bucket (:428-457).
+//     bucket have been enqueued, in arena order -- the hook the reference calls sync_bucket (:428-457);
+//   * weight-gradient products (and the bias column sums) can run on a second stream beside the chain of
+//     input-gradient kernels that the next layer waits for: a persistent GEMM leaves SMs idle during its last,
+//     partial wave of tiles, and CTAs of the other stream's kernel start on them.  Dependencies in both
+//     directions are CUDA events, so the whole backward pass is still one capturable graph.
 #include "attention.h"
 #include "gemm.h"
 
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -26,6 +31,8 @@ int cme_layernorm_bwd(int, const void*, const void*, const void*, const float*, 
                       void*, float*, int, int, int, void*);
 int cme_colsum_splits(int, int);
 int cme_dact_colsum(int, const void*, const void*, void*, void*, float*, int, int, int, int, void*);
+int cme_colsum_slabs_finalize(int, const float*, int, int, void*, int, void*);
+int cme_bias_act_residual(int, const void*, const void*, const void*, void*, void*, long long, int, int, void*);
 int cme_embedding_fwd(int, const int*, const void*, const void*, void*, int, int, int, int, void*);
 int cme_embedding_bwd(int, const int*, const void*, void*, void*, int, int, int, int, int, void*);
 int cme_cross_entropy(int, const void*, const int*, void*, float*, float*, int, int, long long, float, float, float,
@@ -39,6 +46,8 @@ struct CmeEngineDesc {
     int V, T, D, H, FF, L, B;
     int act;             // CME_ACT_RELU | CME_ACT_GELU
     int causal, head_flat, tied, final_ln, fused_qkv;
+    int fuse_epilogues;  // 0: bias / activation / residual adds and the activation derivative run as separate kernels
+                         // after plain products (the ablation the reference measures with CME213_LT_FUSION)
     float ln_eps, prob_eps;
     int dtype;           // CME_BF16 | CME_F32
     int gemm_backend;    // 0 auto, 1 tcgen05, 2 simt
@@ -82,6 +91,12 @@ struct Engine {
     float *delta, *dq_accum, *ln_scratch, *col_scratch;
     void* attn_ws; long long attn_ws_bytes;
     void* gemm_ws; long long gemm_ws_bytes;
+    void* gemm_ws_side; long long gemm_ws_side_bytes;     // split-K partials of the products on the second stream
+    float* col_scratch_side;
+    float* slab_scratch;                                   // [ceil(BT / 32)][FF] column sums left by a GEMM epilogue
+    // second stream for the weight-gradient work (null: everything on the caller's stream)
+    cudaStream_t side = nullptr;
+    std::vector<cudaEvent_t> ev;                           // [L + 1][8]: four "inputs ready" + four "done" per layer
 
     char* P(long long off) const { return params + off * (long long)es; }
     char* G(long long off) const { return grads + off * (long long)es; }
@@ -139,6 +154,13 @@ size_t carve(Engine& e, char* base) {
     const long long want_ws = 4ll * (long long)BT * (long long)widest * 4ll;
     e.gemm_ws_bytes = want_ws > (64ll << 20) ? want_ws : (64ll << 20);
     e.gemm_ws = take((size_t)e.gemm_ws_bytes);
+    // the second stream's own scratch: eight splits of the largest per-layer weight gradient, column-sum partials
+    const long long side_ws = 8ll * (long long)D * (long long)widest * 4ll;
+    e.gemm_ws_side_bytes = side_ws > (64ll << 20) ? side_ws : (64ll << 20);
+    e.gemm_ws_side = take((size_t)e.gemm_ws_side_bytes);
+    e.slab_scratch = (float*)take((size_t)((BT + 31) / 32) * widest * 4);
+    e.col_scratch_side = (float*)take((size_t)(cme_colsum_splits((int)BT, (int)D) + cme_colsum_splits((int)BT, (int)FF)) *
+                                      widest * 4);
     return off;
 }
 
@@ -146,7 +168,7 @@ int gemm(const Engine& e, cudaStream_t st, int M, int N, int K, const void* A, l
          const void* B, long long ldb, int b_trans, void* C, long long ldc, int accumulate = 0,
          const void* bias = nullptr, int act = 0, void* aux_out = nullptr, int dact = 0, const void* aux_in = nullptr,
          long long ldaux = 0, const void* residual = nullptr, long long ldres = 0, int batch = 1, long long sA = 0,
-         long long sB = 0, long long sC = 0) {
+         long long sB = 0, long long sC = 0, int aux_deriv = 0, float* colsum = nullptr, int* colsum_slabs = nullptr) {
     CmeGemm g{};
     g.M = M; g.N = N; g.K = K; g.batch = batch;
     g.A = A; g.lda = lda; g.strideA = sA; g.a_trans = a_trans;
@@ -155,7 +177,10 @@ int gemm(const Engine& e, cudaStream_t st, int M, int N, int K, const void* A, l
     g.bias = bias; g.residual = residual; g.ldres = ldres;
     g.aux_out = aux_out; g.aux_in = aux_in; g.ldaux = ldaux;
     g.act = act; g.dact = dact; g.accumulate = accumulate;
-    g.workspace = e.gemm_ws; g.workspace_bytes = e.gemm_ws_bytes;
+    g.aux_deriv = aux_deriv; g.colsum = colsum; g.colsum_slabs = colsum_slabs;
+    const bool on_side = e.side != nullptr && st == e.side;
+    g.workspace = on_side ? e.gemm_ws_side : e.gemm_ws;
+    g.workspace_bytes = on_side ? e.gemm_ws_side_bytes : e.gemm_ws_bytes;
     return cme_gemm(&g, e.d.gemm_backend, st);
 }
 
@@ -183,6 +208,13 @@ void fill_attn(const Engine& e, int l, CmeAttn& a) {
 }
 
 #define TRY(expr) do { int rc__ = (expr); if (rc__) return rc__; } while (0)
+
+// CME213_FFN_DERIV=0 goes back to keeping the pre-activation and re-evaluating the derivative in backward, with the
+// bias gradient as a separate column-sum kernel (for A/B measurements of the fused form).
+bool ffn_deriv() {
+    static const bool on = !(getenv("CME213_FFN_DERIV") && getenv("CME213_FFN_DERIV")[0] == '0');
+    return on;
+}
 
 }  // namespace
 
@@ -215,7 +247,46 @@ CME_API int cme_engine_bind(void* h, void* params, void* grads, void* workspace,
     return CME_OK;
 }
 
-CME_API void cme_engine_destroy(void* h) { delete static_cast<Engine*>(h); }
+CME_API void cme_engine_destroy(void* h) {
+    Engine* e = static_cast<Engine*>(h);
+    for (cudaEvent_t v : e->ev) cudaEventDestroy(v);
+    if (e->side) cudaStreamDestroy(e->side);
+    delete e;
+}
+
+// Turns the second stream for weight-gradient work on (creating it and its events on the current device) or off.
+// Call outside stream capture.
+CME_API int cme_engine_set_overlap(void* h, int on) {
+    Engine* e = static_cast<Engine*>(h);
+    if (on && !e->side) {
+        CME_CUDA(cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking));
+        e->ev.resize((size_t)(e->d.L + 1) * 8);
+        for (cudaEvent_t& v : e->ev) CME_CUDA(cudaEventCreateWithFlags(&v, cudaEventDisableTiming));
+    } else if (!on && e->side) {
+        CME_CUDA(cudaStreamSynchronize(e->side));
+        for (cudaEvent_t v : e->ev) cudaEventDestroy(v);
+        e->ev.clear();
+        CME_CUDA(cudaStreamDestroy(e->side));
+        e->side = nullptr;
+    }
+    return CME_OK;
+}
+
+// Makes `target` wait for everything enqueued so far on `stream` and on the engine's second stream: what a
+// gradient-synchronisation stream needs before it may read a bucket that backward has just completed.
+CME_API int cme_engine_fence(void* h, void* stream, void* target) {
+    Engine* e = static_cast<Engine*>(h);
+    cudaEvent_t v;
+    CME_CUDA(cudaEventCreateWithFlags(&v, cudaEventDisableTiming));
+    CME_CUDA(cudaEventRecord(v, (cudaStream_t)stream));
+    CME_CUDA(cudaStreamWaitEvent((cudaStream_t)target, v, 0));
+    if (e->side) {
+        CME_CUDA(cudaEventRecord(v, e->side));
+        CME_CUDA(cudaStreamWaitEvent((cudaStream_t)target, v, 0));
+    }
+    CME_CUDA(cudaEventDestroy(v));           // released once the recorded work has completed
+    return CME_OK;
+}
 
 CME_API void* cme_engine_logits(void* h) { return static_cast<Engine*>(h)->logits; }
 CME_API long long cme_engine_logits_ld(void* h) { return static_cast<Engine*>(h)->VL; }
@@ -239,6 +310,7 @@ CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, f
     cudaStream_t st = (cudaStream_t)stream;
     CME_REQUIRE(e.ws != nullptr, CME_ERR_SHAPE, "engine: not bound");
     const int BT = e.BT, D = d.D, FF = d.FF, V = d.V, dt = d.dtype;
+    const bool fused = d.fuse_epilogues != 0;
     TRY(cme_embedding_fwd(dt, tokens, e.P(e.gs.tok), e.P(e.gs.pos), e.x[0], BT, d.T, D, V, st));
     for (int l = 0; l < d.L; ++l) {
         const CmeLayerSlots& s = e.ls[l];
@@ -255,16 +327,30 @@ CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, f
         at.o = a.attn;
         TRY(cme_attention_fwd(&at, d.attn_backend, st));
         // x_mid = x + attn @ Wo
-        TRY(gemm(e, st, BT, D, D, a.attn, D, 0, e.P(s.Wo), D, 0, a.xmid, D, 0, nullptr, 0, nullptr, 0, nullptr, 0,
-                 e.x[l], D));
+        if (fused) {
+            TRY(gemm(e, st, BT, D, D, a.attn, D, 0, e.P(s.Wo), D, 0, a.xmid, D, 0, nullptr, 0, nullptr, 0, nullptr, 0,
+                     e.x[l], D));
+        } else {
+            TRY(gemm(e, st, BT, D, D, a.attn, D, 0, e.P(s.Wo), D, 0, a.xmid, D));
+            TRY(cme_bias_act_residual(dt, a.xmid, nullptr, e.x[l], nullptr, a.xmid, BT, D, 0, st));
+        }
         TRY(cme_layernorm_fwd(dt, a.xmid, nullptr, nullptr, e.P(s.ln2g), e.P(s.ln2b), a.ln2, a.mean2, a.rstd2, BT, D,
                               d.ln_eps, st));
-        // ff_act = act(ln2 @ W1 + b1)   (GELU also keeps the pre-activation for its derivative)
-        TRY(gemm(e, st, BT, FF, D, a.ln2, D, 0, e.P(s.W1), FF, 0, a.ffact, FF, 0, e.P(s.b1), d.act, a.ffpre, 0, nullptr,
-                 FF));
-        // x_next = x_mid + ff_act @ W2 + b2
-        TRY(gemm(e, st, BT, D, FF, a.ffact, FF, 0, e.P(s.W2), D, 0, e.x[l + 1], D, 0, e.P(s.b2), 0, nullptr, 0, nullptr,
-                 0, a.xmid, D));
+        // ff_act = act(ln2 @ W1 + b1)   (GELU also keeps GELU'(pre-activation), from the same tanh, for backward)
+        if (fused) {
+            TRY(gemm(e, st, BT, FF, D, a.ln2, D, 0, e.P(s.W1), FF, 0, a.ffact, FF, 0, e.P(s.b1), d.act, a.ffpre, 0,
+                     nullptr, FF, nullptr, 0, 1, 0, 0, 0, /*aux_deriv=*/ffn_deriv() ? 1 : 0));
+            // x_next = x_mid + ff_act @ W2 + b2
+            TRY(gemm(e, st, BT, D, FF, a.ffact, FF, 0, e.P(s.W2), D, 0, e.x[l + 1], D, 0, e.P(s.b2), 0, nullptr, 0,
+                     nullptr, 0, a.xmid, D));
+        } else {
+            // plain products, then the reference's element-wise kernels: bias + activation (keeping the
+            // pre-activation), and bias + residual add (FINAL_CLEAN_CODE_/src/model/transformer.cu:387-399)
+            TRY(gemm(e, st, BT, FF, D, a.ln2, D, 0, e.P(s.W1), FF, 0, a.ffact, FF));
+            TRY(cme_bias_act_residual(dt, a.ffact, e.P(s.b1), nullptr, a.ffpre, a.ffact, BT, FF, d.act, st));
+            TRY(gemm(e, st, BT, D, FF, a.ffact, FF, 0, e.P(s.W2), D, 0, e.x[l + 1], D));
+            TRY(cme_bias_act_residual(dt, e.x[l + 1], e.P(s.b2), a.xmid, nullptr, e.x[l + 1], BT, D, 0, st));
+        }
     }
     const void* xlast = e.x[d.L];
     if (d.final_ln) {
@@ -289,26 +375,55 @@ CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, f
 
 // Backward from d(logits) left in the logits buffer by forward.  accumulate != 0 adds into the gradient
 // arena (micro-batches after the first); otherwise every gradient is overwritten.
+//
+// With the second stream on, the chain  dX products -> LayerNorm / attention backward  stays on `stream` and every
+// weight-gradient product and bias column sum goes to the second stream.  Event k of a layer's first four marks
+// "the k-th input of the side work exists" (recorded on `stream`), of its last four "the k-th piece of side work is
+// done" (recorded on the second stream); the main chain waits for a "done" event only where it is about to
+// overwrite a buffer that piece reads, which is up to one layer later.
 CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeBucketFn bucket_ready, void* user,
                                 void* stream) {
     Engine& e = *static_cast<Engine*>(h);
     const CmeEngineDesc& d = e.d;
     cudaStream_t st = (cudaStream_t)stream;
+    const bool ov = e.side != nullptr;
+    cudaStream_t ws = ov ? e.side : st;                     // stream of the weight-gradient work
     const int BT = e.BT, D = d.D, FF = d.FF, V = d.V, dt = d.dtype;
     int bucket = 0;
     auto emit = [&]() { if (bucket_ready) bucket_ready(user, bucket); ++bucket; };
-    float* col_a = e.col_scratch;
+    // slot L = output head, slot l = layer l; k in [0, 4) inputs ready, [4, 8) side work done
+    auto evt = [&](int slot, int k) { return e.ev[(size_t)slot * 8 + k]; };
+    auto ready = [&](int slot, int k) -> int {              // side work may start: its inputs are enqueued on `st`
+        if (!ov) return CME_OK;
+        CME_CUDA(cudaEventRecord(evt(slot, k), st));
+        CME_CUDA(cudaStreamWaitEvent(ws, evt(slot, k), 0));
+        return CME_OK;
+    };
+    auto done = [&](int slot, int k) -> int {               // marks the end of a piece of side work
+        if (!ov) return CME_OK;
+        CME_CUDA(cudaEventRecord(evt(slot, 4 + k), ws));
+        return CME_OK;
+    };
+    auto need = [&](int slot, int k) -> int {               // `st` is about to overwrite what that piece reads
+        if (!ov) return CME_OK;
+        CME_CUDA(cudaStreamWaitEvent(st, evt(slot, 4 + k), 0));
+        return CME_OK;
+    };
+    float* col_s = ov ? e.col_scratch_side : e.col_scratch;
     const void* xlast = d.final_ln ? e.xf : e.x[d.L];
     char* dx = e.dxa;       // gradient w.r.t. the residual stream entering the part being processed
     char* dx_other = e.dxb;
-    // ---- output head
+    // ---- output head (the logits buffer holds d(logits); forward already ran on `st`)
+    TRY(ready(d.L, 0));
     if (d.tied) {
         TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.P(e.gs.tok), D, 0, dx, D));                 // dX = dL @ tok
-        TRY(gemm(e, st, V, D, BT, e.logits, e.VL, 1, xlast, D, 0, e.G(e.gs.tok), D, accumulate));  // dtok = dL^T @ X
+        TRY(gemm(e, ws, V, D, BT, e.logits, e.VL, 1, xlast, D, 0, e.G(e.gs.tok), D, accumulate));  // dtok = dL^T @ X
+        TRY(done(d.L, 0));
     } else {
         if (e.wout_pad) TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.wout_pad, e.VL, 1, dx, D));   // dX = dL @ Wout^T
         else TRY(gemm(e, st, BT, D, V, e.logits, e.VL, 0, e.P(e.gs.Wout), V, 1, dx, D));
-        TRY(gemm(e, st, D, V, BT, xlast, D, 1, e.logits, e.VL, 0, e.G(e.gs.Wout), V, accumulate)); // dWout = X^T @ dL
+        TRY(gemm(e, ws, D, V, BT, xlast, D, 1, e.logits, e.VL, 0, e.G(e.gs.Wout), V, accumulate)); // dWout = X^T @ dL
+        TRY(done(d.L, 0));
         emit();
     }
     if (d.final_ln) {
@@ -320,50 +435,86 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
     for (int l = d.L - 1; l >= 0; --l) {
         const CmeLayerSlots& s = e.ls[l];
         LayerAct& a = e.la[l];
+        const bool below_top = l < d.L - 1;     // the layer above left side work that reads the shared temporaries
         // ---- FFN2:  x_next = x_mid + ff_act @ W2 + b2
-        const void* aux = d.act == CME_ACT_GELU ? a.ffpre : a.ffact;       // relu'(pre) == (act > 0)
-        TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF, 0, nullptr, 0, nullptr, d.act, aux, FF));
-        TRY(gemm(e, st, FF, D, BT, a.ffact, FF, 1, dx, D, 0, e.G(s.W2), D, accumulate));
-        TRY(cme_dact_colsum(dt, dx, nullptr, nullptr, e.G(s.b2), col_a, BT, D, 0, accumulate, st));
+        // a.ffpre holds GELU'(pre-activation); relu'(pre) == (act > 0).  The product's epilogue also sums d ff_pre
+        // over rows (the gradient of b1) when the kernel that runs can; the sums are finished on the side stream.
+        const void* aux = d.act == CME_ACT_GELU ? a.ffpre : a.ffact;
+        const bool fused = d.fuse_epilogues != 0;
+        const bool deriv = fused && ffn_deriv();
+        int slabs = 0;
+        TRY(ready(l, 0));                                                   // dx exists
+        if (below_top) TRY(need(l + 1, 1));                                 // dff is still read by the layer above's dW1
+        bool db1_done = false;
+        if (fused) {
+            TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF, 0, nullptr, 0, nullptr, d.act, aux, FF, nullptr,
+                     0, 1, 0, 0, 0, /*aux_deriv=*/deriv ? 1 : 0, deriv ? e.slab_scratch : nullptr, &slabs));
+        } else {
+            // plain product, then the derivative and the bias gradient in one element-wise pass (the reference's
+            // fused_relu_backward_bias_backward_kernel, FINAL_CLEAN_CODE_/src/kernels/activations.cu:247-283)
+            TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF));
+            TRY(cme_dact_colsum(dt, e.dff, aux, e.dff, e.G(s.b1), e.col_scratch, BT, FF, d.act, accumulate, st));
+            db1_done = true;
+        }
+        TRY(gemm(e, ws, FF, D, BT, a.ffact, FF, 1, dx, D, 0, e.G(s.W2), D, accumulate));
+        TRY(cme_dact_colsum(dt, dx, nullptr, nullptr, e.G(s.b2), col_s, BT, D, 0, accumulate, ws));
+        TRY(done(l, 0));
         emit();
         // ---- FFN1:  ff_pre = ln2 @ W1 + b1   (e.dff now holds d ff_pre)
+        TRY(ready(l, 1));                                                   // dff exists
         TRY(gemm(e, st, BT, D, FF, e.dff, FF, 0, e.P(s.W1), FF, 1, e.dln, D));
-        TRY(gemm(e, st, D, FF, BT, a.ln2, D, 1, e.dff, FF, 0, e.G(s.W1), FF, accumulate));
-        TRY(cme_dact_colsum(dt, e.dff, nullptr, nullptr, e.G(s.b1), col_a, BT, FF, 0, accumulate, st));
+        TRY(gemm(e, ws, D, FF, BT, a.ln2, D, 1, e.dff, FF, 0, e.G(s.W1), FF, accumulate));
+        if (slabs) TRY(cme_colsum_slabs_finalize(dt, e.slab_scratch, slabs, FF, e.G(s.b1), accumulate, ws));
+        else if (!db1_done) TRY(cme_dact_colsum(dt, e.dff, nullptr, nullptr, e.G(s.b1), col_s, BT, FF, 0, accumulate, ws));
+        TRY(done(l, 1));
         emit();
         // ---- LN2 (+ residual gradient): d x_mid = LN'(d ln2) + dx
+        if (below_top) TRY(need(l + 1, 2));                                 // dx_other is read by the layer above's dWo
         TRY(cme_layernorm_bwd(dt, e.dln, a.xmid, e.P(s.ln2g), a.mean2, a.rstd2, dx, dx_other, e.G(s.ln2g), e.G(s.ln2b),
                               e.ln_scratch, BT, D, accumulate, st));
         std::swap(dx, dx_other);                                            // dx = d x_mid
         emit();
         // ---- attention output projection:  x_mid = x + attn @ Wo
+        TRY(ready(l, 2));                                                   // d x_mid exists
         TRY(gemm(e, st, BT, D, D, dx, D, 0, e.P(s.Wo), D, 1, e.dattn, D));
-        TRY(gemm(e, st, D, D, BT, a.attn, D, 1, dx, D, 0, e.G(s.Wo), D, accumulate));
+        TRY(gemm(e, ws, D, D, BT, a.attn, D, 1, dx, D, 0, e.G(s.Wo), D, accumulate));
+        TRY(done(l, 2));
         emit();
         // ---- attention
         CmeAttn at;
         fill_attn(e, l, at);
         at.o = a.attn; at.d_o = e.dattn;
+        if (below_top) TRY(need(l + 1, 3));                                 // dqkv is read by the layer above's dWqkv
         TRY(cme_attention_bwd(&at, d.attn_backend, st));
         // ---- QKV projection
+        TRY(ready(l, 3));                                                   // dqkv exists
         if (d.fused_qkv) {
             TRY(gemm(e, st, BT, D, 3 * D, e.dqkv, 3 * D, 0, e.P(s.Wqkv), 3 * D, 1, e.dln, D));
-            TRY(gemm(e, st, D, 3 * D, BT, a.ln1, D, 1, e.dqkv, 3 * D, 0, e.G(s.Wqkv), 3 * D, accumulate));
+            TRY(gemm(e, ws, D, 3 * D, BT, a.ln1, D, 1, e.dqkv, 3 * D, 0, e.G(s.Wqkv), 3 * D, accumulate));
         } else {
             const long long pl = (long long)BT * D * e.es, wm = (long long)D * D * e.es;
             for (int i = 0; i < 3; ++i)
                 TRY(gemm(e, st, BT, D, D, e.dqkv + i * pl, D, 0, e.P(s.Wq) + i * wm, D, 1, e.dln, D, i > 0));
-            TRY(gemm(e, st, D, D, BT, a.ln1, D, 1, e.dqkv, D, 0, e.G(s.Wq), D, accumulate, nullptr, 0, nullptr, 0,
+            TRY(gemm(e, ws, D, D, BT, a.ln1, D, 1, e.dqkv, D, 0, e.G(s.Wq), D, accumulate, nullptr, 0, nullptr, 0,
                      nullptr, 0, nullptr, 0, 3, 0, (long long)BT * D, (long long)D * D));
         }
+        TRY(done(l, 3));
         emit();
         // ---- LN1 (+ residual gradient): d x = LN'(d ln1) + d x_mid
+        TRY(need(l, 0));                                                    // dx_other is still read by this layer's dW2
         TRY(cme_layernorm_bwd(dt, e.dln, e.x[l], e.P(s.ln1g), a.mean1, a.rstd1, dx, dx_other, e.G(s.ln1g), e.G(s.ln1b),
                               e.ln_scratch, BT, D, accumulate, st));
         std::swap(dx, dx_other);
         emit();
     }
-    // ---- embeddings (tied: the table gradient already holds the output-head part, so the scatter adds)
+    // ---- embeddings (tied: the table gradient already holds the output-head part, so the scatter adds).  Everything
+    // on the second stream joins here: the head's table gradient before the scatter adds to it, and the rest so that
+    // the caller's stream alone orders the end of backward.
+    if (ov) {
+        cudaEvent_t fin = evt(d.L, 5);
+        CME_CUDA(cudaEventRecord(fin, ws));
+        CME_CUDA(cudaStreamWaitEvent(st, fin, 0));
+    }
     TRY(cme_embedding_bwd(dt, tokens, dx, e.G(e.gs.tok), nullptr, BT, d.T, D, V, (d.tied || accumulate) ? 1 : 0, st));
     TRY(cme_embedding_bwd(dt, tokens, dx, nullptr, e.G(e.gs.pos), BT, d.T, D, V, accumulate, st));
     emit();

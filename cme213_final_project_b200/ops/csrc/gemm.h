@@ -14,6 +14,14 @@ enum CmeAct : int { CME_ACT_NONE = 0, CME_ACT_RELU = 1, CME_ACT_GELU = 2 };
 //   batch strides are in elements; 0 means the operand is shared by all batches.
 // Epilogue, in this order:  acc += bias[n];  aux_out[m,n] = acc (pre-activation, optional);
 //   acc = act(acc);  acc *= act'(aux_in[m,n]) (dact);  acc += residual[m,n];  acc += C_old (accumulate).
+// aux_deriv != 0 changes what the auxiliary tensor holds: the forward product stores act'(pre-activation) in
+//   aux_out instead of the pre-activation (one tanh serves GELU and its derivative), and the backward product
+//   multiplies by aux_in as it is -- the derivative is evaluated once, in forward, instead of once more per
+//   backward element.  (For ReLU the derivative is the sign of the activation; aux_deriv is ignored.)
+// colsum != null asks for column sums of the stored C (a bias gradient when C is the gradient of a pre-activation):
+//   the kernel writes one fp32 row of partial sums per 32 rows of C, [ceil(M / 32)][N], and *colsum_slabs receives
+//   the number of such rows -- or 0 when the kernel that ran cannot produce them (the caller then sums C itself).
+//   cme_colsum_slabs_finalize adds the rows up in a fixed order.
 struct CmeGemm {
     int M, N, K, batch;
     const void* A; long long lda, strideA; int a_trans;
@@ -26,6 +34,8 @@ struct CmeGemm {
     int act, dact, accumulate;
     void* workspace; long long workspace_bytes;           // fp32 scratch for split-K partial sums (may be null)
     int force_bn, force_splits;                           // 0 = choose automatically
+    int aux_deriv;                                        // aux tensors hold act'(pre-activation), see above
+    float* colsum; int* colsum_slabs;                     // optional column sums of C (device scratch, host count)
 };
 
 int gemm_tcgen05_supported(const CmeGemm* g);

@@ -21,7 +21,7 @@ struct SimtParams {
     long long ldc, ldres, ldaux;
     const void* A; const void* B; void* C;
     const void* bias; const void* residual; void* aux_out; const void* aux_in;
-    int act, dact, accumulate;
+    int act, dact, accumulate, aux_deriv;
     int batch, splits, k_per_split;        // grid.z = batch * splits; split > 0 writes fp32 partials to `partial`
     float* partial;
 };
@@ -114,12 +114,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
             if (n >= p.N) continue;
             float v = acc[i][j];
             if (bias) v += to_f32<TI>(bias[n]);
-            if (XO) XO[m * p.ldaux + n] = from_f32<TO>(v);
+            if (XO) XO[m * p.ldaux + n] = from_f32<TO>((p.aux_deriv && p.act == CME_ACT_GELU) ? dgelu_f(v) : v);
             if (p.act == CME_ACT_RELU) v = fmaxf(v, 0.f);
             else if (p.act == CME_ACT_GELU) v = gelu_f(v);
             if (p.dact) {
                 const float x = to_f32<TO>(XI[m * p.ldaux + n]);
-                v = (p.dact == CME_ACT_RELU) ? (x > 0.f ? v : 0.f) : v * dgelu_f(x);
+                v = (p.dact == CME_ACT_RELU) ? (x > 0.f ? v : 0.f) : p.aux_deriv ? v * x : v * dgelu_f(x);
             }
             if (R) v += to_f32<TO>(R[m * p.ldres + n]);
             if (p.accumulate) v += to_f32<TO>(C[m * p.ldc + n]);
@@ -154,8 +154,9 @@ int gemm_simt_launch(const CmeGemm* g, cudaStream_t stream) {
     p.ldc = g->ldc; p.ldres = g->ldres; p.ldaux = g->ldaux;
     p.A = g->A; p.B = g->B; p.C = g->C;
     p.bias = g->bias; p.residual = g->residual; p.aux_out = g->aux_out; p.aux_in = g->aux_in;
-    p.act = g->act; p.dact = g->dact; p.accumulate = g->accumulate;
+    p.act = g->act; p.dact = g->dact; p.accumulate = g->accumulate; p.aux_deriv = g->aux_deriv;
     p.batch = g->batch;
+    if (g->colsum_slabs) *g->colsum_slabs = 0;              // this kernel does not sum columns; the caller does
     // Split K when the output has few tiles and the reduction is long (skinny weight gradients).
     const long long tiles = (long long)cme_cdiv(g->N, TN) * cme_cdiv(g->M, TM) * g->batch;
     const bool plain = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;

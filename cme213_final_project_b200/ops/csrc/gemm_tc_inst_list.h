@@ -56,6 +56,22 @@ CME_GEMM_TC_EXTERN(64, false, false, SPEC_BIAS_GELU_AUX)
 CME_GEMM_TC_EXTERN(64, false, false, SPEC_DGELU)
 #endif
 
+#if CME_GEMM_TC_GROUP == -1 || CME_GEMM_TC_GROUP == 8      // MLP pair with the derivative kept by forward: forward side
+CME_GEMM_TC_EXTERN(256, false, true, SPEC_BIAS_GELU_AUXD)
+CME_GEMM_TC_EXTERN(128, false, false, SPEC_BIAS_GELU_AUXD)
+CME_GEMM_TC_EXTERN(64, false, false, SPEC_BIAS_GELU_AUXD)
+#endif
+#if CME_GEMM_TC_GROUP == -1 || CME_GEMM_TC_GROUP == 9      // ... backward side, with the bias gradient's column sums
+CME_GEMM_TC_EXTERN(256, false, true, SPEC_DMUL_COLSUM)
+CME_GEMM_TC_EXTERN(128, false, false, SPEC_DMUL_COLSUM)
+CME_GEMM_TC_EXTERN(64, false, false, SPEC_DMUL_COLSUM)
+#endif
+#if CME_GEMM_TC_GROUP == -1 || CME_GEMM_TC_GROUP == 10     // ReLU derivative with column sums
+CME_GEMM_TC_EXTERN(256, false, true, SPEC_DRELU_COLSUM)
+CME_GEMM_TC_EXTERN(128, false, false, SPEC_DRELU_COLSUM)
+CME_GEMM_TC_EXTERN(64, false, false, SPEC_DRELU_COLSUM)
+#endif
+
 #ifdef CME_GEMM_TC_GROUP_DEFAULTED
 #undef CME_GEMM_TC_GROUP
 #undef CME_GEMM_TC_GROUP_DEFAULTED

@@ -274,7 +274,9 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         ep.residual = g->residual; ep.ldres = g->ldres;
         ep.aux_out = g->aux_out; ep.aux_in = g->aux_in; ep.ldaux = g->ldaux;
         ep.act = g->act; ep.dact = g->dact; ep.accumulate = g->accumulate;
+        ep.aux_deriv = (g->aux_deriv && (g->act == CME_ACT_GELU || g->dact == CME_ACT_GELU)) ? 1 : 0;
     }
+    if (g->colsum_slabs) *g->colsum_slabs = 0;
     // Outputs through shared-memory staging + TMA tile stores when rows are 16-byte addressable.
     CUtensorMap tc = ta, tx = ta, ti = ta;
     {
@@ -314,23 +316,31 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     const bool a_mn = g->a_trans != 0, b_mn = g->b_trans == 0;
     const bool simple = ep.tma_store && !ep.c_f32 && !ep.bias && !ep.residual && !ep.aux_out && !ep.aux_in &&
                         !ep.act && !ep.dact && !ep.accumulate;
-    int spec = -1;
+    int spec = -1, spec_colsum = -1;
     if (!simple) {
-        if (ep.tma_store && !ep.c_f32)
+        if (ep.tma_store && !ep.c_f32) {
             spec = spec_pack(ep.bias != nullptr, ep.act, ep.dact, ep.residual != nullptr, ep.accumulate != 0,
-                             ep.aux_out != nullptr, ep.in_kind, ep.aux_ring != 0);
-        else if (ep.tma_store && ep.c_f32 && !ep.accumulate)
+                             ep.aux_out != nullptr, ep.in_kind, ep.aux_ring != 0, ep.aux_deriv != 0, false);
+            // column sums ride in the variants whose input arrives through the ring (one output buffer per chunk)
+            if (g->colsum && g->colsum_slabs && splits == 1 && g->batch == 1 && ep.in_kind == 1 && ep.dact)
+                spec_colsum = spec | (1 << 13);
+        } else if (ep.tma_store && ep.c_f32 && !ep.accumulate) {
             spec = SPEC_F32;
+        }
     }
-    // the instantiation with this tile, pairing and compile-time epilogue; else the run-time epilogue of that tile
+    // the instantiation with this tile, pairing and compile-time epilogue (first with the column sums, if asked
+    // for); else the run-time epilogue of that tile
     rc = -1;
-    for (int attempt = 0; attempt < 2 && rc == -1; ++attempt) {
-        const int want = attempt == 0 ? spec : -1;
+    for (int attempt = 0; attempt < 3 && rc == -1; ++attempt) {
+        const int want = attempt == 0 ? spec_colsum : attempt == 1 ? spec : -1;
+        if (attempt == 0 && want < 0) continue;
+        ep.colsum = attempt == 0 ? g->colsum : nullptr;
 #define CME_GEMM_TC_EXTERN(BN, SIMPLE, PAIR, SPEC)                                              \
     if (rc == -1 && bn == BN && simple == SIMPLE && pair == PAIR && want == SPEC)               \
         rc = launch_bn<BN, SIMPLE, PAIR, SPEC>(a_mn, b_mn, ta, tb, tc, tx, ti, ep, grid, stream);
 #include "gemm_tc_inst_list.h"
 #undef CME_GEMM_TC_EXTERN
+        if (rc == CME_OK && attempt == 0) *g->colsum_slabs = cme_cdiv(g->M, 32);
     }
     CME_REQUIRE(rc != -1, CME_ERR_SHAPE, "gemm: no kernel instantiation for tile %d pair %d", bn, (int)pair);
     if (rc) return rc;

@@ -82,6 +82,8 @@ struct EpiParams {
     const void* residual; long long ldres;
     void* aux_out; const void* aux_in; long long ldaux;
     int act, dact, accumulate;
+    int aux_deriv;                 // aux tensors hold the activation's derivative instead of the pre-activation
+    float* colsum;                 // [ceil(M / 32)][N] partial column sums of the stored C, or null
     int tma_store;                 // outputs go through shared memory and TMA tile stores
     int in_kind;                   // operand delivered by TMA through tmI: 0 none, 1 aux_in, 2 residual, 3 old C
     int aux_ring;                  // aux_out leaves through the ring + tmX (else direct 16-byte stores)
@@ -123,11 +125,14 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
     __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off_c + n;
     if (p.aux_out) {
         __nv_bfloat16* X = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + row_off_aux + n;
+        float xo[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) xo[j] = (p.aux_deriv && p.act == CME_ACT_GELU) ? dgelu_fast(acc[j]) : acc[j];
         if (full) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) *reinterpret_cast<Bf16x8*>(X + j) = pack8(acc + j);
+            for (int j = 0; j < 32; j += 8) *reinterpret_cast<Bf16x8*>(X + j) = pack8(xo + j);
         } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) X[j] = __float2bfloat16_rn(acc[j]);
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) X[j] = __float2bfloat16_rn(xo[j]);
         }
     }
     if (p.act == CME_ACT_RELU) {
@@ -151,7 +156,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, l
             for (int j = 0; j < 32; ++j) acc[j] = x[j] > 0.f ? acc[j] : 0.f;
         } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] *= dgelu_fast(x[j]);
+            for (int j = 0; j < 32; ++j) acc[j] *= p.aux_deriv ? x[j] : dgelu_fast(x[j]);
         }
     }
     if (p.residual) {
@@ -204,10 +209,12 @@ __device__ __forceinline__ void load8_guard(const __nv_bfloat16* rowp, int n, in
 // kernel holds every combination -- large code whose instruction fetches miss in the caches while L2 is saturated
 // by the main loops).  SPEC >= 0: a bit set fixed at compile time, so the hot loop holds only what it executes:
 //   bit 0 bias | bits 1-2 act | bits 3-4 dact | bit 5 residual | bit 6 accumulate | bit 7 aux_out |
-//   bits 8-9 in_kind | bit 10 aux_ring | bit 11 fp32 output (split-K partials; nothing else set)
-constexpr int spec_pack(bool bias, int act, int dact, bool res, bool accum, bool aux, int in_kind, bool aux_ring) {
+//   bits 8-9 in_kind | bit 10 aux_ring | bit 11 fp32 output (split-K partials; nothing else set) |
+//   bit 12 aux tensors hold the activation's derivative | bit 13 column sums of C
+constexpr int spec_pack(bool bias, int act, int dact, bool res, bool accum, bool aux, int in_kind, bool aux_ring,
+                        bool aux_deriv = false, bool colsum = false) {
     return int(bias) | (act << 1) | (dact << 3) | (int(res) << 5) | (int(accum) << 6) | (int(aux) << 7) |
-           (in_kind << 8) | (int(aux_ring) << 10);
+           (in_kind << 8) | (int(aux_ring) << 10) | (int(aux_deriv) << 12) | (int(colsum) << 13);
 }
 template <int SPEC> struct Spec {
     static constexpr bool RT = SPEC < 0;
@@ -230,6 +237,11 @@ template <int SPEC> struct Spec {
     __device__ __forceinline__ static bool c_f32(const EpiParams& p) {
         return RT ? p.c_f32 != 0 : ((SPEC >> 11) & 1) != 0;
     }
+    __device__ __forceinline__ static bool aux_deriv(const EpiParams& p) {
+        return RT ? p.aux_deriv != 0 : ((SPEC >> 12) & 1) != 0;
+    }
+    // column sums exist only in compile-time variants
+    __device__ __forceinline__ static bool colsum(const EpiParams&) { return !RT && ((SPEC >> 13) & 1) != 0; }
 };
 
 // Fused epilogue arithmetic on 32 columns of one row (bf16 outputs).  `pre` receives the pre-activation.
@@ -251,16 +263,23 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
             for (int q = 0; q < 8; ++q) acc[g * 8 + q] += b[q];
         }
     }
-    if (S::aux_out(p)) {
+    const bool deriv = S::aux_deriv(p);
+    if (S::aux_out(p) && deriv && act == CME_ACT_GELU) {
+        // activation and its derivative from one tanh; the derivative is what backward multiplies by
 #pragma unroll
-        for (int j = 0; j < 32; ++j) pre[j] = acc[j];
-    }
-    if (act == CME_ACT_RELU) {
+        for (int j = 0; j < 32; ++j) gelu_and_grad_fast(acc[j], acc[j], pre[j]);
+    } else {
+        if (S::aux_out(p)) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
-    } else if (act == CME_ACT_GELU) {
+            for (int j = 0; j < 32; ++j) pre[j] = acc[j];
+        }
+        if (act == CME_ACT_RELU) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = gelu_fast(acc[j]);
+            for (int j = 0; j < 32; ++j) acc[j] = fmaxf(acc[j], 0.f);
+        } else if (act == CME_ACT_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] = gelu_fast(acc[j]);
+        }
     }
     if (dact) {
         const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + offa;
@@ -271,7 +290,8 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
 #pragma unroll
             for (int q = 0; q < 8; ++q)
                 acc[g * 8 + q] = (dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
-                                                          : acc[g * 8 + q] * dgelu_fast(x[q]);
+                                 : deriv              ? acc[g * 8 + q] * x[q]
+                                                      : acc[g * 8 + q] * dgelu_fast(x[q]);
         }
     }
     if (S::residual(p)) {
@@ -705,6 +725,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         if (aux_ring) tma_store_3d(&tmX, sbX, n, m0 + quarter * 32, bidx);
                         tma_store_commit();
                     }
+                    if (S::colsum(p)) {
+                        // Column sums of the 32 x 64 slab just staged (the bf16 values that are stored): lane l owns
+                        // columns 2l, 2l + 1 and walks down the rows; for a fixed row the lanes read the 32 words of
+                        // one 128-byte line, so there are no bank conflicts.  The buffer is not refilled before the
+                        // next chunk ends, and the TMA store only reads it.
+                        const int row0 = m0 + quarter * 32;
+                        const int nvalid = min(32, p.M - row0);
+                        float s0 = 0.f, s1 = 0.f;
+#pragma unroll 8
+                        for (int r = 0; r < 32; ++r) {
+                            if (r < nvalid) {
+                                const uint32_t w = *reinterpret_cast<const uint32_t*>(
+                                    sbC + r * 128 + (((lane >> 2) ^ (r & 7)) * 16) + (lane & 3) * 4);
+                                const float2 f = bf2_to_f2(w);
+                                s0 += f.x; s1 += f.y;
+                            }
+                        }
+                        const int col = n + 2 * lane;
+                        float* dst = p.colsum + (long long)(row0 >> 5) * p.N + col;
+                        if (nvalid > 0) {
+                            if (col + 1 < p.N && (p.N & 1) == 0) *reinterpret_cast<float2*>(dst) = make_float2(s0, s1);
+                            else { if (col < p.N) dst[0] = s0; if (col + 1 < p.N) dst[1] = s1; }
+                        }
+                    }
                     slot += aux_ring ? 2 : 1;
                     if (in_kind) {
                         // refill the buffer stored one chunk ago with the chunk NB - 1 ahead
@@ -790,6 +834,10 @@ constexpr int SPEC_BIAS_RELU = spec_pack(true, CME_ACT_RELU, 0, false, false, fa
 constexpr int SPEC_DRELU = spec_pack(false, 0, CME_ACT_RELU, false, false, false, 1, false);
 constexpr int SPEC_RES = spec_pack(false, 0, 0, true, false, false, 2, false);
 constexpr int SPEC_F32 = 1 << 11;
+// the pair the transformer's MLP uses: forward leaves GELU'(pre-activation), backward multiplies by it and sums columns
+constexpr int SPEC_BIAS_GELU_AUXD = spec_pack(true, CME_ACT_GELU, 0, false, false, true, 0, true, true);
+constexpr int SPEC_DMUL_COLSUM = spec_pack(false, 0, CME_ACT_GELU, false, false, false, 1, false, true, true);
+constexpr int SPEC_DRELU_COLSUM = spec_pack(false, 0, CME_ACT_RELU, false, false, false, 1, false, false, true);
 constexpr int SPEC_ACC = spec_pack(false, 0, 0, false, true, false, 3, false);
 
 }  // namespace gemm_tc

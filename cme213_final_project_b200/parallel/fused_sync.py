@@ -125,7 +125,16 @@ class FusedSync:
         self.world = ctx.world_size
         single = self.world == 1
         elem = 2
-        self.buckets: List[Bucket] = model.layout.coalesced_buckets(min_bucket_elems(run.bucket_kb, elem))
+        # CME213_COMM_MERGE_TAIL=0 keeps the plain rule (the embeddings as a bucket of their own behind the last
+        # layer bucket)
+        self.buckets: List[Bucket] = model.layout.coalesced_buckets(
+            min_bucket_elems(run.bucket_kb, elem), merge_tail=os.environ.get("CME213_COMM_MERGE_TAIL", "1") != "0")
+        grad_mb = n * elem / (1024.0 * 1024.0)
+        self.overlap = run.sync_mode == "overlap" or (run.sync_mode == "auto" and grad_mb <= run.auto_overlap_max_mb)
+        if not self.overlap:
+            # --sync-mode blocking (or auto above its size limit): one call over the whole arena after backward, the
+            # reference's blocking whole-buffer synchronisation (FINAL_CLEAN_CODE_/src/main.cu:373-374)
+            self.buckets = [Bucket(0, 0, n, tuple(s.name for s in model.layout.specs))]
         bad = [b for b in self.buckets if b.numel % (8 * self.world) or b.start % 8]
         if bad:
             raise ops.NativeError(
@@ -185,7 +194,8 @@ class FusedSync:
         per = ", ".join(f"{k} x{self.algos.count(k)}" for k in kinds)
         form = "reduce per bucket + one clip/AdamW/all-gather kernel" if self.clip else \
                "reduce-scatter + AdamW + all-gather per bucket"
-        return f"fused device kernels ({form}); {len(self.buckets)} buckets: {per}"
+        when = "overlapped with backward" if self.overlap else "after backward"
+        return f"fused device kernels ({form}), {when}; {len(self.buckets)} buckets: {per}"
 
     def _opt_args(self):
         m, o = self.model, self.model.optim
@@ -196,12 +206,14 @@ class FusedSync:
 
     def launch_bucket(self, b: Bucket) -> None:
         """Called on the host as soon as backward has enqueued the last kernel of bucket ``b``."""
-        cur = torch.cuda.current_stream()
-        ev = torch.cuda.Event()
-        ev.record(cur)
-        self.stream.wait_event(ev)
-        opt, nd = self._opt_args()
         last = b.index == len(self.buckets) - 1
+        if last:
+            # End of backward on the compute stream.  Recorded before the fence, so the last synchronisation kernel is
+            # ordered behind this timestamp: a node beside it in a captured graph could be run after it.
+            nlog = self.tlog.numel()
+            ops._check(self.lib.cme_record_time(ctypes.c_void_p(self.tlog.data_ptr() + 8 * (nlog - 2)), ops._stream()))
+        self.model.fence(self.stream)                 # the bucket's producers, on either of the engine's streams
+        opt, nd = self._opt_args()
         ops._check(self.lib.cme_comm_fused_adamw(
             self.world, self.comm.rank, self.grads.c_ptrs, self.params.c_ptrs, self.comm.flags.c_ptrs,
             ctypes.c_void_p(self.grads.multicast_ptr), ctypes.c_void_p(self.params.multicast_ptr),
@@ -233,9 +245,7 @@ class FusedSync:
         stream sits idle behind the last bucket kernels is the step's exposed synchronisation time."""
         cur = torch.cuda.current_stream()
         nlog = self.tlog.numel()
-        tl = self.tlog.data_ptr()
-        ops._check(self.lib.cme_record_time(ctypes.c_void_p(tl + 8 * (nlog - 2)), ctypes.c_void_p(cur.cuda_stream)))
-        ops._check(self.lib.cme_record_time(ctypes.c_void_p(tl + 8 * (nlog - 1)),
+        ops._check(self.lib.cme_record_time(ctypes.c_void_p(self.tlog.data_ptr() + 8 * (nlog - 1)),
                                             ctypes.c_void_p(self.stream.cuda_stream)))
         ev = torch.cuda.Event()
         ev.record(self.stream)

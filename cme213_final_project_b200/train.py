@@ -24,11 +24,13 @@ from .utils import logfmt
 
 
 def fused_sync_obstacle(model_cfg, optim_cfg, run: RunConfig, dist_ctx: DistributedContext) -> Optional[str]:
-    """Why this run cannot use the fused device synchronisation path, or ``None`` if it can."""
-    if dist_ctx.world_size <= 1:
-        return "a single rank has nothing to synchronise"
+    """Why this run cannot use the fused device synchronisation path, or ``None`` if it can.  A single rank uses it
+    too: its world-of-one form is the optimizer applied bucket by bucket on a second stream while backward is still
+    running, instead of one pass over the whole arena afterwards."""
     if dist_ctx.device.type != "cuda":
         return "the fused device path needs GPUs"
+    if dist_ctx.world_size <= 1 and run.sync_mode != "overlap":
+        return "a single rank keeps the one-pass optimizer unless --sync-mode overlap asks for the bucketed one"
     if run.comm_backend not in ("auto", "fused"):
         return f"comm backend '{run.comm_backend}' was requested"
     if run.engine not in ("auto", "native"):
@@ -53,7 +55,9 @@ def build_model(model_cfg, optim_cfg, run: RunConfig, dist_ctx: DistributedConte
             from .parallel.fused_sync import attach_fused_sync, shard_align
             model = NativeEngine(model_cfg, optim_cfg, run, dist_ctx, seed=seed, align=shard_align(dist_ctx.world_size))
             attach_fused_sync(model, dist_ctx, run)
-            dist_ctx.backend, dist_ctx.backend_note = "fused", model.fused.describe()
+            if dist_ctx.world_size > 1:
+                dist_ctx.backend = "fused"
+            dist_ctx.backend_note = model.fused.describe()
             return model
         if dist_ctx.world_size > 1:
             dist_ctx.fall_back(why)
@@ -195,6 +199,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         say(logfmt.epoch_line(epoch + 1, logged_sum / logged_n if logged_n else step_loss, steps_per_epoch,
                               max_ms, tokens / (max_ms / 1e3), d.world_size, trainer.use_overlap,
                               start_ms, sync_ms, span))
+        if getattr(model, "fused", None) is not None:
+            # device timestamps of the last step's bucket kernels (ms relative to the end of backward) and the exposed
+            # synchronisation time, max over ranks; parsed by benchmarks/run_experiments.py
+            import json
+            tl = model.fused.timeline()
+            tl["exposed_ms"] = d.max_double(tl["exposed_ms"])
+            say("SYNC_TIMELINE " + json.dumps(tl))
 
     if run.save_checkpoint:
         # every rank takes part: under the fused path the optimizer state is sharded and `state` gathers it

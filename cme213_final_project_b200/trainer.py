@@ -50,7 +50,12 @@ class Trainer:
 
     # ---------------------------------------------------------------------------------------------
     def _bucket_ready(self, b: Bucket) -> None:
-        self.dist.start_async_gradient_sync(self.model.grads[b.start:b.end])
+        m = self.model
+        if hasattr(m, "fence") and m.grads.is_cuda:
+            # the bucket's last producer may sit on the engine's second stream: order the current stream behind it,
+            # since the communication path takes its dependency from the current stream
+            m.fence(torch.cuda.current_stream(m.device))
+        self.dist.start_async_gradient_sync(m.grads[b.start:b.end])
 
     def step(self, tokens: Sequence[torch.Tensor], targets: Sequence[torch.Tensor]) -> None:
         """One optimizer step over ``len(tokens)`` micro-batches (``grad_accum`` of them)."""

@@ -197,3 +197,47 @@ def test_output_narrower_than_a_vector_unit_on_the_tensor_core_path():
     logits = ops.gemm(x, w, b_trans=True, backend="tcgen05")
     assert ops.gemm_check_status() == 0
     _check(logits, x.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("bn", [64, 128, 512])
+@pytest.mark.parametrize("M,N", [(1024, 512), (1000, 520)])
+def test_derivative_kept_by_forward_and_bias_gradient_in_the_epilogue(bn, M, N):
+    """The MLP pair: the forward product stores GELU'(pre-activation) beside the activation (one tanh for both), the
+    backward product multiplies by the stored derivative and also sums its output over rows -- the bias gradient
+    (the reference's cuBLASLt DRELU_BGRAD epilogue, FINAL_CLEAN_CODE_/src/kernels/gemm.cu:243, and its fused
+    ReLU-backward + bias-backward kernel, src/kernels/activations.cu:247-283).  M = 1000 leaves a ragged last slab."""
+    ops = _ops()
+    K = 192
+    if bn == 512:
+        N = N * 3
+    a, b, bias = _mk((M, K), 61), _mk((K, N), 62), _mk((N,), 63)
+    kw = dict(backend="tcgen05", force_bn=bn)
+    pre = (a.float() @ b.float() + bias.float()).requires_grad_(True)
+    act = torch.nn.functional.gelu(pre, approximate="tanh")
+    act.sum().backward()
+    d = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    out = ops.gemm(a, b, bias=bias, act="gelu", aux_out=d, aux_deriv=True, **kw)
+    _check(out, act.detach())
+    _check(d, pre.grad)
+    # backward: dC = (g @ w) * d, with its column sums
+    g, w = _mk((M, 128), 64), _mk((128, N), 65)
+    ref = (g.float() @ w.float()) * d.float()
+    for dact, aux, want in (("gelu", d, ref), ("relu", d, (g.float() @ w.float()) * (d.float() > 0))):
+        dbias = torch.zeros(N, dtype=torch.bfloat16, device="cuda")
+        got = ops.gemm(g, w, dact=dact, aux_in=aux, aux_deriv=True, dbias=dbias, **kw)
+        torch.cuda.synchronize()
+        assert ops.gemm_check_status() == 0
+        _check(got, want)
+        assert ops.gemm.last_colsum_slabs == (M + 31) // 32, "the epilogue variant with column sums did not run"
+        colref = got.float().sum(0)                      # sums of the stored (bf16) values, like the separate kernel
+        err = (dbias.float() - colref).abs().max().item()
+        assert err <= 1e-2 * colref.abs().max().item() + 1e-3, err
+        again = torch.zeros_like(dbias)
+        ops.gemm(g, w, dact=dact, aux_in=aux, aux_deriv=True, dbias=again, **kw)
+        assert torch.equal(dbias, again), "column sums must be bit-reproducible"
+    # the SIMT kernel honours the same flags (column sums then come from the separate pass)
+    dbias = torch.zeros(N, dtype=torch.bfloat16, device="cuda")
+    got = ops.gemm(g, w, dact="gelu", aux_in=d, aux_deriv=True, dbias=dbias, backend="simt")
+    _check(got, ref)
+    assert ops.gemm.last_colsum_slabs == 0
+    _check(dbias, got.float().sum(0), tol=1e-2)

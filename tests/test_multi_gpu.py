@@ -21,7 +21,7 @@ def test_fused_kernel_world_of_one_equals_unfused_update():
     ctx.device = torch.device("cuda", 0)
     a = NativeEngine(cfg, optim, RunConfig(), device="cuda", seed=3)
     b = NativeEngine(cfg, optim, RunConfig(bucket_kb=128), device="cuda", seed=3)
-    fs = attach_fused_sync(b, ctx, RunConfig(bucket_kb=128))
+    fs = attach_fused_sync(b, ctx, RunConfig(bucket_kb=128, sync_mode="overlap"))
     g = torch.Generator().manual_seed(1)
     n = cfg.tokens_per_step
     for _ in range(3):
@@ -52,7 +52,7 @@ def test_two_phase_clip_kernels_world_of_one_equal_norm_plus_adam():
     ctx.device = torch.device("cuda", 0)
     a = NativeEngine(cfg, optim, RunConfig(), device="cuda", seed=3)
     b = NativeEngine(cfg, optim, RunConfig(bucket_kb=64), device="cuda", seed=3)
-    fs = attach_fused_sync(b, ctx, RunConfig(bucket_kb=64))
+    fs = attach_fused_sync(b, ctx, RunConfig(bucket_kb=64, sync_mode="overlap"))
     assert fs.clip and len(fs.buckets) > 1
     g = torch.Generator().manual_seed(1)
     n = cfg.tokens_per_step
@@ -70,6 +70,30 @@ def test_two_phase_clip_kernels_world_of_one_equal_norm_plus_adam():
     assert torch.allclose(a.params.float(), b.params.float(), rtol=8e-3, atol=1e-6)
     tl = fs.timeline()
     assert len(tl["buckets"]) == len(fs.buckets) + 1 and all(e >= s for s, e in tl["buckets"])
+
+
+def test_blocking_mode_on_the_fused_path_is_one_call_after_backward():
+    from cme213_final_project_b200.config import RunConfig, preset
+    from cme213_final_project_b200.models.engine import NativeEngine
+    from cme213_final_project_b200.parallel.dist import DistributedContext
+    from cme213_final_project_b200.parallel.fused_sync import attach_fused_sync
+    cfg, optim = preset("tiny-gpt")
+    ctx = DistributedContext()
+    ctx.device = torch.device("cuda", 0)
+    a = NativeEngine(cfg, optim, RunConfig(), device="cuda", seed=3)
+    b = NativeEngine(cfg, optim, RunConfig(), device="cuda", seed=3)
+    fs = attach_fused_sync(b, ctx, RunConfig(sync_mode="blocking", bucket_kb=64))
+    assert len(fs.buckets) == 1 and fs.buckets[0].numel == b.layout.total and not fs.overlap
+    g = torch.Generator().manual_seed(2)
+    n = cfg.tokens_per_step
+    for _ in range(2):
+        x = torch.randint(0, cfg.vocab_size, (n,), generator=g, dtype=torch.int32).cuda()
+        y = torch.randint(0, cfg.vocab_size, (n,), generator=g, dtype=torch.int32).cuda()
+        a.train_step([x], [y]); a.update()
+        b.train_step([x], [y]); b.update()
+    torch.cuda.synchronize()
+    assert fs.check_status() == 0 and fs.launched == 2
+    assert (a.master - b.master).abs().max().item() < 1e-6
 
 
 def test_bounded_wait_reports_instead_of_hanging():
