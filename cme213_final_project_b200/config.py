@@ -104,7 +104,7 @@ class RunConfig:
     cuda_graph: bool = False
     grad_accum: int = 1
     gemm_backend: str = "auto"     # auto | tcgen05 | simt
-    compute_dtype: str = "bf16"    # bf16 | fp32
+    compute_dtype: str = "bf16"    # bf16 | tf32 (fp32 storage, tf32 tensor-core products) | fp32 (strict: SIMT)
     synthetic: bool = False
     seed: int = 42
     save_checkpoint: Optional[str] = None
@@ -230,7 +230,7 @@ def validate_run(model: ModelConfig, run: RunConfig, world_size: int) -> List[st
         errs.append("--grad-accum must be >= 1")
     if run.bucket_kb < 0:
         errs.append("--bucket-kb must be >= 0")
-    if run.compute_dtype not in ("bf16", "fp32"):
+    if run.compute_dtype not in ("bf16", "tf32", "fp32"):
         errs.append(f"unknown compute dtype '{run.compute_dtype}'")
     if run.gemm_backend not in ("auto", "tcgen05", "simt"):
         errs.append(f"unknown gemm backend '{run.gemm_backend}'")

@@ -23,7 +23,7 @@ from ..config import ModelConfig, OptimConfig, RunConfig
 
 class _EngineDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("V", "T", "D", "H", "FF", "L", "B", "act", "causal", "head_flat", "tied",
-                                             "final_ln", "fused_qkv", "fuse_epilogues")] + \
+                                             "final_ln", "fused_qkv", "allow_tf32", "fuse_epilogues")] + \
                [("ln_eps", ctypes.c_float), ("prob_eps", ctypes.c_float)] + \
                [(n, ctypes.c_int) for n in ("dtype", "gemm_backend", "attn_backend")]
 
@@ -54,7 +54,12 @@ class NativeEngine:
         self.lib = ops.lib()
         with torch.cuda.device(self.device):
             ops._check(self.lib.cme_init_device())               # status words exist before any stream capture
-        self.strict = run.compute_dtype == "fp32"
+        # "fp32": fp32 storage and exact fp32 products on the SIMT kernels (the reference's CME213_STRICT_FP32);
+        # "tf32": fp32 storage, products on the tensor cores with tf32 inputs and fp32 accumulation, element-wise work
+        # in separate fp32 kernels (the reference's default: fp32 storage with tensor-core math through cuBLAS,
+        # FINAL_CLEAN_CODE_/src/kernels/gemm.cu:274-289); "bf16": bf16 storage with fp32 master weights.
+        self.tf32 = run.compute_dtype == "tf32"
+        self.strict = run.compute_dtype in ("fp32", "tf32")          # fp32 storage: params are the master copy
         self.dtype = torch.float32 if self.strict else torch.bfloat16
         # `align` (elements) is 64 unless the arena has to split into per-rank slices for a world size whose
         # 8 * world does not divide 64 (parallel.fused_sync.shard_align)
@@ -92,9 +97,11 @@ class NativeEngine:
                         B=cfg.batch_size, act=ops.ACT[cfg.activation], causal=int(cfg.causal),
                         head_flat=int(cfg.head_layout == "flat"), tied=int(cfg.tied_embeddings),
                         final_ln=int(cfg.final_layernorm), fused_qkv=int(cfg.mode == "gpt"),
-                        fuse_epilogues=int(run.epilogue_fusion), ln_eps=cfg.ln_eps,
+                        allow_tf32=int(self.tf32), fuse_epilogues=int(run.epilogue_fusion and not self.tf32),
+                        ln_eps=cfg.ln_eps,
                         prob_eps=1e-9 if cfg.mode == "parity" else 0.0, dtype=ops.F32 if self.strict else ops.BF16,
-                        gemm_backend=2 if self.strict else gemm_backend, attn_backend=2 if self.strict else 0)
+                        gemm_backend=gemm_backend if (self.tf32 or not self.strict) else 2,
+                        attn_backend=2 if self.strict else 0)
         off = lambda name: self.layout.by_name[name].offset if name in self.layout.by_name else -1
         layers = (_LayerSlots * cfg.layers)()
         for l in range(cfg.layers):

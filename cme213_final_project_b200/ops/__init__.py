@@ -44,6 +44,7 @@ class CmeGemm(ctypes.Structure):
         ("force_bn", ctypes.c_int), ("force_splits", ctypes.c_int),
         ("aux_deriv", ctypes.c_int),
         ("colsum", ctypes.c_void_p), ("colsum_slabs", ctypes.POINTER(ctypes.c_int)),
+        ("allow_tf32", ctypes.c_int),
     ]
 
 
@@ -129,7 +130,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_trans: bool = False, b_trans: bo
          bias: Optional[torch.Tensor] = None, act: Optional[str] = None, aux_out: Optional[torch.Tensor] = None,
          dact: Optional[str] = None, aux_in: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
          accumulate: bool = False, backend: str = "auto", force_bn: int = 0, force_splits: int = 0,
-         aux_deriv: bool = False, dbias: Optional[torch.Tensor] = None) -> torch.Tensor:
+         aux_deriv: bool = False, dbias: Optional[torch.Tensor] = None, allow_tf32: bool = True) -> torch.Tensor:
     """``out (+)= epilogue(op(a) @ op(b))`` for 2-D or batched 3-D row-major operands.
 
     ``a``: ``[M, K]`` (or ``[K, M]`` with ``a_trans``); ``b``: ``[K, N]`` (or ``[N, K]`` with ``b_trans``);
@@ -139,6 +140,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_trans: bool = False, b_trans: bo
     ``aux_deriv``: the auxiliary tensor holds ``act'(pre-activation)`` instead of the pre-activation (forward
     stores it, backward multiplies by it).  ``dbias`` (a ``[N]`` tensor): receives the column sums of ``out`` --
     from the GEMM's own epilogue when the kernel that runs can produce them, else from a separate pass.
+    fp32 operands: ``backend="simt"`` multiplies them exactly; the tcgen05 kernel takes them as tf32 (plain products
+    with fp32 output only) unless ``allow_tf32=False``.
     """
     _cuda(a, b, out, bias, aux_out, aux_in, residual)
     batch = 1
@@ -171,6 +174,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_trans: bool = False, b_trans: bo
     g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel() * 4
     g.force_bn, g.force_splits = force_bn, force_splits
     g.aux_deriv = int(aux_deriv)
+    g.allow_tf32 = int(allow_tf32)
     slabs = ctypes.c_int(0)
     if dbias is not None:
         part = torch.empty((M + 31) // 32 * N, dtype=torch.float32, device=a.device)

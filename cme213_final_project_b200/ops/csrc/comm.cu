@@ -18,6 +18,8 @@
 // phase and returns, so a rank that never arrives cannot hang the GPU.
 #include "common.h"
 
+#include <cstdlib>
+
 namespace {
 
 constexpr int MAX_RANKS = 16;
@@ -290,9 +292,12 @@ __device__ __forceinline__ uint4 adamw8(const OptArgs& o, long long el, const fl
         }
         if (!(lo < o.n_nodecay && o.nodecay[2 * lo] <= el)) decay = 1.f - lr * o.weight_decay;
     }
-    float4 m0 = *reinterpret_cast<const float4*>(o.m + el), m1 = *reinterpret_cast<const float4*>(o.m + el + 4);
-    float4 v0 = *reinterpret_cast<const float4*>(o.v + el), v1 = *reinterpret_cast<const float4*>(o.v + el + 4);
-    float4 p0 = *reinterpret_cast<const float4*>(o.master + el), p1 = *reinterpret_cast<const float4*>(o.master + el + 4);
+    // The optimizer state is touched once per step: streaming (evict-first) accesses keep it from displacing the
+    // operands of the backward products that run beside this kernel out of L2.
+    const float4 m0 = __ldcs(reinterpret_cast<const float4*>(o.m + el)), m1 = __ldcs(reinterpret_cast<const float4*>(o.m + el + 4));
+    const float4 v0 = __ldcs(reinterpret_cast<const float4*>(o.v + el)), v1 = __ldcs(reinterpret_cast<const float4*>(o.v + el + 4));
+    const float4 p0 = __ldcs(reinterpret_cast<const float4*>(o.master + el)),
+                 p1 = __ldcs(reinterpret_cast<const float4*>(o.master + el + 4));
     float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
     float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
@@ -303,12 +308,12 @@ __device__ __forceinline__ uint4 adamw8(const OptArgs& o, long long el, const fl
         vv[j] = o.beta2 * vv[j] + (1.f - o.beta2) * gj * gj;
         pp[j] = pp[j] * decay - lr * (mm[j] * ibc1) / (sqrtf(vv[j] * ibc2) + o.eps);
     }
-    *reinterpret_cast<float4*>(o.m + el) = make_float4(mm[0], mm[1], mm[2], mm[3]);
-    *reinterpret_cast<float4*>(o.m + el + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
-    *reinterpret_cast<float4*>(o.v + el) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-    *reinterpret_cast<float4*>(o.v + el + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
-    *reinterpret_cast<float4*>(o.master + el) = make_float4(pp[0], pp[1], pp[2], pp[3]);
-    *reinterpret_cast<float4*>(o.master + el + 4) = make_float4(pp[4], pp[5], pp[6], pp[7]);
+    __stcs(reinterpret_cast<float4*>(o.m + el), make_float4(mm[0], mm[1], mm[2], mm[3]));
+    __stcs(reinterpret_cast<float4*>(o.m + el + 4), make_float4(mm[4], mm[5], mm[6], mm[7]));
+    __stcs(reinterpret_cast<float4*>(o.v + el), make_float4(vv[0], vv[1], vv[2], vv[3]));
+    __stcs(reinterpret_cast<float4*>(o.v + el + 4), make_float4(vv[4], vv[5], vv[6], vv[7]));
+    __stcs(reinterpret_cast<float4*>(o.master + el), make_float4(pp[0], pp[1], pp[2], pp[3]));
+    __stcs(reinterpret_cast<float4*>(o.master + el + 4), make_float4(pp[4], pp[5], pp[6], pp[7]));
     return pack8(pp);
 }
 
@@ -556,6 +561,13 @@ CME_API int cme_comm_fused_adamw(int world, int rank, void* const* grads, void* 
                                  int n_nodecay, int algo, int bucket, int max_buckets, int ctas, void* ctl,
                                  int* status, double budget_ms, float* gred, float* norm_part, float* norm_bucket,
                                  unsigned long long* tlog, void* stream) {
+    // Threads per CTA: COMM_THREADS unless CME213_COMM_THREADS asks for thinner CTAs (a multiple of 32 that holds one
+    // thread per rank); fewer warps per SM take fewer issue slots from the compute kernels running beside them.
+    static const int threads = [] {
+        const char* e = getenv("CME213_COMM_THREADS");
+        const int t = e ? atoi(e) : COMM_THREADS;
+        return (t >= 32 && t <= COMM_THREADS && t % 32 == 0) ? t : COMM_THREADS;
+    }();
     CME_REQUIRE(world >= 1 && world <= MAX_RANKS && rank >= 0 && rank < world, CME_ERR_SHAPE, "comm: bad world/rank");
     CME_REQUIRE(count > 0 && count % (8ll * world) == 0 && start % 8 == 0, CME_ERR_SHAPE,
                 "comm: bucket [%lld, +%lld) is not aligned to 8 * world elements", start, count);
@@ -574,8 +586,9 @@ CME_API int cme_comm_fused_adamw(int world, int rank, void* const* grads, void* 
     a.ctl = static_cast<uint32_t*>(ctl); a.status = status;
     a.budget_ns = (unsigned long long)(budget_ms * 1e6);
     a.gred = gred; a.norm_part = norm_part; a.norm_bucket = norm_bucket; a.tlog = tlog;
-    if (gred) fused_rs_adamw_ag_kernel<false><<<ctas, COMM_THREADS, 0, (cudaStream_t)stream>>>(a);
-    else fused_rs_adamw_ag_kernel<true><<<ctas, COMM_THREADS, 0, (cudaStream_t)stream>>>(a);
+    const int block = ctas > 296 ? COMM_THREADS : threads;      // the tail call has the GPU to itself: full CTAs
+    if (gred) fused_rs_adamw_ag_kernel<false><<<ctas, block, 0, (cudaStream_t)stream>>>(a);
+    else fused_rs_adamw_ag_kernel<true><<<ctas, block, 0, (cudaStream_t)stream>>>(a);
     CME_LAUNCH_CHECK();
     return CME_OK;
 }

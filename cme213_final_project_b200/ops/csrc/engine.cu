@@ -46,6 +46,7 @@ struct CmeEngineDesc {
     int V, T, D, H, FF, L, B;
     int act;             // CME_ACT_RELU | CME_ACT_GELU
     int causal, head_flat, tied, final_ln, fused_qkv;
+    int allow_tf32;      // fp32 storage: plain products may run on the tensor cores with tf32 inputs
     int fuse_epilogues;  // 0: bias / activation / residual adds and the activation derivative run as separate kernels
                          // after plain products (the ablation the reference measures with CME213_LT_FUSION)
     float ln_eps, prob_eps;
@@ -178,6 +179,7 @@ int gemm(const Engine& e, cudaStream_t st, int M, int N, int K, const void* A, l
     g.aux_out = aux_out; g.aux_in = aux_in; g.ldaux = ldaux;
     g.act = act; g.dact = dact; g.accumulate = accumulate;
     g.aux_deriv = aux_deriv; g.colsum = colsum; g.colsum_slabs = colsum_slabs;
+    g.allow_tf32 = e.d.allow_tf32;
     const bool on_side = e.side != nullptr && st == e.side;
     g.workspace = on_side ? e.gemm_ws_side : e.gemm_ws;
     g.workspace_bytes = on_side ? e.gemm_ws_side_bytes : e.gemm_ws_bytes;

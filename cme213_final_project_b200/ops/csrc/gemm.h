@@ -27,7 +27,8 @@ struct CmeGemm {
     const void* A; long long lda, strideA; int a_trans;
     const void* B; long long ldb, strideB; int b_trans;
     void* C; long long ldc, strideC; int c_dtype;        // CME_BF16 or CME_F32
-    int ab_dtype;                                         // CME_BF16 or CME_F32 (SIMT path only)
+    int ab_dtype;                                         // CME_BF16, or CME_F32: exact on the SIMT kernel, tf32 tensor-core
+                                                          // math on the tcgen05 kernel when allow_tf32 is set
     const void* bias;                                     // [N], same dtype as A/B, or null
     const void* residual; long long ldres;                // [M, N] same dtype as C, or null (batch stride = strideC)
     void* aux_out; const void* aux_in; long long ldaux;   // [M, N] same dtype as C
@@ -36,6 +37,8 @@ struct CmeGemm {
     int force_bn, force_splits;                           // 0 = choose automatically
     int aux_deriv;                                        // aux tensors hold act'(pre-activation), see above
     float* colsum; int* colsum_slabs;                     // optional column sums of C (device scratch, host count)
+    int allow_tf32;                                       // fp32 operands may be multiplied as tf32 (10-bit mantissa
+                                                          // inputs, fp32 accumulation): plain products with fp32 output
 };
 
 int gemm_tcgen05_supported(const CmeGemm* g);

@@ -72,6 +72,13 @@ CME_GEMM_TC_EXTERN(128, false, false, SPEC_DRELU_COLSUM)
 CME_GEMM_TC_EXTERN(64, false, false, SPEC_DRELU_COLSUM)
 #endif
 
+#if CME_GEMM_TC_GROUP == -1 || CME_GEMM_TC_GROUP == 11     // fp32 storage multiplied as tf32 (plain fp32 output)
+CME_GEMM_TC_EXTERN(64, false, false, SPEC_TF32)
+CME_GEMM_TC_EXTERN(128, false, false, SPEC_TF32)
+CME_GEMM_TC_EXTERN(256, false, false, SPEC_TF32)
+CME_GEMM_TC_EXTERN(256, false, true, SPEC_TF32)
+#endif
+
 #ifdef CME_GEMM_TC_GROUP_DEFAULTED
 #undef CME_GEMM_TC_GROUP
 #undef CME_GEMM_TC_GROUP_DEFAULTED

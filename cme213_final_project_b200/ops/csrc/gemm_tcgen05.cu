@@ -72,6 +72,27 @@ __global__ void splitk_reduce_vec4_kernel(const float4* __restrict__ P, int spli
     }
 }
 
+// out[b][c][r] = in[b][r][c] for fp32 matrices (32 x 32 tiles through shared memory).  The tf32 products take
+// K-major operands only -- with an MN-major fp32 operand the tensor core returned zeros here -- so operands stored
+// the other way are copied into the workspace transposed first.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float* __restrict__ in, float* __restrict__ out, int rows,
+                                                            int cols, long long ld_in, long long stride_in,
+                                                            long long stride_out) {
+    __shared__ float tile[32][33];
+    pdl_wait();
+    const float* src = in + (long long)blockIdx.z * stride_in;
+    float* dst = out + (long long)blockIdx.z * stride_out;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8)
+        if (r0 + j < rows && c0 + tx < cols) tile[j][tx] = src[(long long)(r0 + j) * ld_in + c0 + tx];
+    __syncthreads();
+#pragma unroll
+    for (int j = ty; j < 32; j += 8)
+        if (c0 + j < cols && r0 + tx < rows) dst[(long long)(c0 + j) * rows + r0 + tx] = tile[tx][j];
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
@@ -146,8 +167,9 @@ CME_API int cme_gemm_status_word(int** out) {
 //   force_splits: 0 = choose.  Split-K needs the plain epilogue, a workspace for the fp32 partials and at least
 //   four 64-deep k-blocks per split.
 static void plan_tiles(int M, int N, int K, int batch, bool plain_epi, long long workspace_bytes, int num_sms,
-                       int max_pairs, int force_bn, int force_splits, int* bn_out, bool* pair_out, int* splits_out) {
-    const int num_kb = cme_cdiv(K, BK);
+                       int max_pairs, int force_bn, int force_splits, int* bn_out, bool* pair_out, int* splits_out,
+                       int bk = 64) {
+    const int num_kb = cme_cdiv(K, bk);
     int bn = force_bn, splits = force_splits;
     bool pair = false;
     if (bn == 512) { bn = 256; pair = true; }
@@ -199,15 +221,28 @@ CME_API int cme_gemm_plan(int M, int N, int K, int batch, int plain_epilogue, lo
 }
 
 int gemm_tcgen05_supported(const CmeGemm* g) {
-    if (g->ab_dtype != CME_BF16) return 0;
+    const bool tf32 = g->ab_dtype == CME_F32;
+    // fp32 operands run as tf32, and only where the caller allows the reduced input precision: plain products
+    // (fp32 output, optionally accumulated), rows of C addressable in 16-byte units
+    if (tf32 && (!g->allow_tf32 || g->c_dtype != CME_F32 || g->bias || g->residual || g->aux_out || g->aux_in ||
+                 g->act || g->dact || g->N % 4 || g->ldc % 4 || (g->batch > 1 && g->strideC % 4)))
+        return 0;
+    if (tf32 && (g->a_trans || !g->b_trans)) {
+        // an operand stored MN-major is transposed into the workspace first: its new row pitch is K
+        const long long na = g->a_trans ? (long long)(g->strideA ? g->batch : 1) * g->M * g->K : 0;
+        const long long nb = !g->b_trans ? (long long)(g->strideB ? g->batch : 1) * g->N * g->K : 0;
+        if (g->K % 4 || !g->workspace || (na + nb) * 4 + 512 > g->workspace_bytes / 2) return 0;
+    }
+    if (!tf32 && g->ab_dtype != CME_BF16) return 0;
     if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->batch <= 0) return 0;
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (!al16(g->A) || !al16(g->B) || !al16(g->C)) return 0;
-    if (g->lda % 8 || g->ldb % 8 || g->strideA % 8 || g->strideB % 8) return 0;
+    const int unit = tf32 ? 4 : 8;                           // elements per 16 bytes
+    if (g->lda % unit || g->ldb % unit || g->strideA % unit || g->strideB % unit) return 0;
     // Extents need not be multiples of the 16-byte unit: row pitches are (checked above), and a box that reaches
     // past an extent reads zeros.  Degenerate extents go to the SIMT kernel.
     const long long innerA = g->a_trans ? g->M : g->K, innerB = g->b_trans ? g->K : g->N;
-    if (innerA < 8 || innerB < 8) return 0;
+    if (innerA < unit || innerB < unit) return 0;
     if (g->c_dtype == CME_F32 && (g->act || g->dact || g->residual || g->aux_out)) return 0;
     return 1;
 }
@@ -225,13 +260,53 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     }
     const int g_num_sms = ds->num_sms, g_max_pairs = ds->max_pairs;
     int* const g_status = ds->status + CME_STATUS_GEMM;
+    const bool tf32 = g->ab_dtype == CME_F32;
+    if (tf32 && (g->a_trans || !g->b_trans)) {
+        // K-major copies of the operands that are stored MN-major (see transpose_f32_kernel), carved from the front
+        // of the workspace; the product then runs on the copies with what is left of the workspace
+        CmeGemm gg = *g;
+        char* w = static_cast<char*>(g->workspace);
+        auto carve = [&](long long floats) {
+            float* p = reinterpret_cast<float*>(w);
+            w += (floats * 4 + 255) / 256 * 256;
+            return p;
+        };
+        if (g->a_trans) {                                     // stored [K, M] -> [M, K]
+            const int nb = g->strideA ? g->batch : 1;
+            float* t = carve((long long)nb * g->M * g->K);
+            CME_CUDA(cme_launch_dependent(transpose_f32_kernel, dim3(cme_cdiv(g->M, 32), cme_cdiv(g->K, 32), nb), dim3(256),
+                                          0, stream, static_cast<const float*>(g->A), t, g->K, g->M, g->lda, g->strideA,
+                                          (long long)g->M * g->K));
+            CME_LAUNCH_CHECK();
+            gg.A = t; gg.lda = g->K; gg.a_trans = 0; gg.strideA = g->strideA ? (long long)g->M * g->K : 0;
+        }
+        if (!g->b_trans) {                                    // stored [K, N] -> [N, K]
+            const int nb = g->strideB ? g->batch : 1;
+            float* t = carve((long long)nb * g->N * g->K);
+            CME_CUDA(cme_launch_dependent(transpose_f32_kernel, dim3(cme_cdiv(g->N, 32), cme_cdiv(g->K, 32), nb), dim3(256),
+                                          0, stream, static_cast<const float*>(g->B), t, g->K, g->N, g->ldb, g->strideB,
+                                          (long long)g->N * g->K));
+            CME_LAUNCH_CHECK();
+            gg.B = t; gg.ldb = g->K; gg.b_trans = 1; gg.strideB = g->strideB ? (long long)g->N * g->K : 0;
+        }
+        gg.workspace = w;
+        gg.workspace_bytes = g->workspace_bytes - (w - static_cast<char*>(g->workspace));
+        return gemm_tcgen05_launch(&gg, stream);
+    }
+    const int BK = tf32 ? 32 : 64;                            // K elements per 128-byte k-block
     int tiles_m = cme_cdiv(g->M, BM);
     const int num_kb = cme_cdiv(g->K, BK);
     const bool plain_epi = !g->bias && !g->residual && !g->aux_out && !g->act && !g->dact;
     int bn = 0, splits = 0;
     bool pair = false;
     plan_tiles(g->M, g->N, g->K, g->batch, plain_epi, g->workspace ? g->workspace_bytes : 0, g_num_sms, g_max_pairs,
-               g->force_bn, g->force_splits, &bn, &pair, &splits);
+               g->force_bn, g->force_splits, &bn, &pair, &splits, BK);
+    // A tf32 product that accumulates into C goes through the fp32 workspace like a split-K product (one "split"
+    // is then added to C by the reduction kernel): the tf32 kernel variants only store.
+    const bool via_ws = splits > 1 || (tf32 && g->accumulate);
+    if (tf32 && g->accumulate)
+        CME_REQUIRE(g->workspace && (long long)splits * g->batch * g->M * g->N * 4 <= g->workspace_bytes, CME_ERR_LIMIT,
+                    "tf32 accumulate needs an fp32 workspace of M x N");
     CME_REQUIRE(bn == 64 || bn == 128 || bn == 256, CME_ERR_SHAPE, "tile width must be 64, 128, 256 or 512 (pair)");
     CME_REQUIRE(!pair || g_max_pairs > 0, CME_ERR_SHAPE, "CTA-pair tiles are not available on this device");
     if (pair) tiles_m = cme_cdiv(g->M, 2 * BM);
@@ -252,13 +327,13 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     CUtensorMap ta, tb;
     int rc;
     // A: K-major -> map (K, M), box (64, 128); MN-major -> map (M, K), box (64, 64)
-    if (!g->a_trans) rc = make_tmap(&ta, g->A, g->K, g->M, g->lda, g->strideA ? g->batch : 1, g->strideA, BM);
-    else             rc = make_tmap(&ta, g->A, g->M, g->K, g->lda, g->strideA ? g->batch : 1, g->strideA, BK);
+    if (!g->a_trans) rc = make_tmap(&ta, g->A, g->K, g->M, g->lda, g->strideA ? g->batch : 1, g->strideA, BM, tf32);
+    else             rc = make_tmap(&ta, g->A, g->M, g->K, g->lda, g->strideA ? g->batch : 1, g->strideA, BK, tf32);
     if (rc) return rc;
     // B: stored [N, K] (b_trans) is K-major -> map (K, N), box (64, bn); stored [K, N] -> map (N, K), box (64, 64)
     if (g->b_trans) rc = make_tmap(&tb, g->B, g->K, g->N, g->ldb, g->strideB ? g->batch : 1, g->strideB,
-                                   pair ? bn / 2 : bn);
-    else            rc = make_tmap(&tb, g->B, g->N, g->K, g->ldb, g->strideB ? g->batch : 1, g->strideB, BK);
+                                   pair ? bn / 2 : bn, tf32);
+    else            rc = make_tmap(&tb, g->B, g->N, g->K, g->ldb, g->strideB ? g->batch : 1, g->strideB, BK, tf32);
     if (rc) return rc;
 
     EpiParams ep{};
@@ -266,7 +341,7 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     ep.tiles_m = tiles_m; ep.tiles_n = tiles_n; ep.splits = splits; ep.kb_per_split = kb_per; ep.num_kb = num_kb;
     ep.a_batched = g->strideA != 0 && g->batch > 1; ep.b_batched = g->strideB != 0 && g->batch > 1;
     ep.status = g_status;
-    if (splits > 1) {
+    if (via_ws) {
         ep.C = g->workspace; ep.ldc = g->N; ep.strideC = (long long)g->M * g->N; ep.c_f32 = 1;
     } else {
         ep.C = g->C; ep.ldc = g->ldc; ep.strideC = g->strideC; ep.c_f32 = g->c_dtype == CME_F32;
@@ -325,9 +400,10 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
             if (g->colsum && g->colsum_slabs && splits == 1 && g->batch == 1 && ep.in_kind == 1 && ep.dact)
                 spec_colsum = spec | (1 << 13);
         } else if (ep.tma_store && ep.c_f32 && !ep.accumulate) {
-            spec = SPEC_F32;
+            spec = tf32 ? SPEC_TF32 : SPEC_F32;
         }
     }
+    CME_REQUIRE(!tf32 || spec == SPEC_TF32, CME_ERR_SHAPE, "tf32 product: output rows are not 16-byte addressable");
     // the instantiation with this tile, pairing and compile-time epilogue (first with the column sums, if asked
     // for); else the run-time epilogue of that tile
     rc = -1;
@@ -344,7 +420,7 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     }
     CME_REQUIRE(rc != -1, CME_ERR_SHAPE, "gemm: no kernel instantiation for tile %d pair %d", bn, (int)pair);
     if (rc) return rc;
-    if (splits > 1) {
+    if (via_ws) {
         const long long per = (long long)g->batch * g->M * g->N;
         const bool f32 = g->c_dtype == CME_F32;
         const bool vec = g->N % 4 == 0 && g->ldc % 4 == 0 && (g->batch == 1 || g->strideC % 4 == 0) &&

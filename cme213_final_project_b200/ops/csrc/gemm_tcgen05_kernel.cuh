@@ -1,4 +1,4 @@
-// bf16 GEMM on the 5th-generation tensor cores: TMA-fed, mbarrier-pipelined, accumulators in TMEM,
+// bf16 (and, for fp32 storage, tf32) GEMM on the 5th-generation tensor cores: TMA-fed, mbarrier-pipelined, accumulators in TMEM,
 // persistent over output tiles with a double-buffered accumulator so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
@@ -32,9 +32,12 @@ using namespace sm100;
 
 
 constexpr int BM = 128;
-constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
-constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int BK_BYTES = 128;          // a k-block is one 128-byte swizzle row of K: 64 bf16 or 32 fp32 (tf32) elements
+constexpr int MMA_K_BYTES = 32;        // one MMA consumes 32 bytes of K per row: 16 bf16 or 8 tf32 elements
+constexpr int A_TILE_BYTES = BM * BK_BYTES;
+// Operand element type of a kernel variant: SPEC bit 14 set = fp32 storage multiplied as tf32 (kind::tf32), output
+// fp32.  The tile geometry is the same in bytes; only element counts and the instruction kind differ.
+constexpr bool spec_tf32(int spec) { return spec >= 0 && ((spec >> 14) & 1) != 0; }
 constexpr int NUM_THREADS = 192;          // TMA warp + MMA warp + 4 epilogue warps
 constexpr int NUM_THREADS_WIDE = 320;     // ... + 8 epilogue warps (two per scheduler) for the arithmetic-heavy epilogues
 
@@ -50,7 +53,11 @@ constexpr int NUM_THREADS_WIDE = 320;     // ... + 8 epilogue warps (two per sch
 constexpr int SMEM_LIMIT = 232448;     // 227 KB per CTA
 template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
     static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN;       // B columns staged by this CTA
-    static constexpr int B_TILE_BYTES = BN_LOCAL * BK * 2;
+    static constexpr bool TF32 = spec_tf32(SPEC);
+    static constexpr int ES = TF32 ? 4 : 2;                   // operand element size
+    static constexpr int BK = BK_BYTES / ES;                  // K elements per k-block
+    static constexpr int GW = 128 / ES;                       // elements per 128-byte row of an MN-major operand tile
+    static constexpr int B_TILE_BYTES = BN_LOCAL * BK_BYTES;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
     // Compile-time variants with a TMA-fed input or a second (pre-activation) output run eight epilogue warps, two
@@ -210,7 +217,8 @@ __device__ __forceinline__ void load8_guard(const __nv_bfloat16* rowp, int n, in
 // by the main loops).  SPEC >= 0: a bit set fixed at compile time, so the hot loop holds only what it executes:
 //   bit 0 bias | bits 1-2 act | bits 3-4 dact | bit 5 residual | bit 6 accumulate | bit 7 aux_out |
 //   bits 8-9 in_kind | bit 10 aux_ring | bit 11 fp32 output (split-K partials; nothing else set) |
-//   bit 12 aux tensors hold the activation's derivative | bit 13 column sums of C
+//   bit 12 aux tensors hold the activation's derivative | bit 13 column sums of C |
+//   bit 14 fp32 operands multiplied as tf32 (with bit 11: fp32 output)
 constexpr int spec_pack(bool bias, int act, int dact, bool res, bool accum, bool aux, int in_kind, bool aux_ring,
                         bool aux_deriv = false, bool colsum = false) {
     return int(bias) | (act << 1) | (dact << 3) | (int(res) << 5) | (int(accum) << 6) | (int(aux) << 7) |
@@ -323,6 +331,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmI, const EpiParams p) {
     using C = Cfg<BN, PAIR, SIMPLE, SPEC>;
     using S = Spec<SPEC>;
+    constexpr int BK = C::BK, GW = C::GW;
+    constexpr int GROUP_BYTES = BK * 128;           // one GW-wide column group of an MN-major tile: BK rows of 128 bytes
     static_assert(!PAIR || BN == 256, "CTA pairs use 256-wide tiles");
     static_assert(!SIMPLE || SPEC < 0, "the plain epilogue has no compile-time variants");
     extern __shared__ uint8_t smem_raw[];
@@ -401,15 +411,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             tma_load_3d_pair(sA, &tmA, fb, kb * BK, m0, za);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < BM / 64; ++j)
-                                tma_load_3d_pair(sA + j * (64 * BK * 2), &tmA, fb, m0 + j * 64, kb * BK, za);
+                            for (int j = 0; j < BM / GW; ++j)
+                                tma_load_3d_pair(sA + j * GROUP_BYTES, &tmA, fb, m0 + j * GW, kb * BK, za);
                         }
                         if (!B_MN) {
                             tma_load_3d_pair(sB, &tmB, fb, kb * BK, n0, zb);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < C::BN_LOCAL / 64; ++j)
-                                tma_load_3d_pair(sB + j * (64 * BK * 2), &tmB, fb, n0 + j * 64, kb * BK, zb);
+                            for (int j = 0; j < C::BN_LOCAL / GW; ++j)
+                                tma_load_3d_pair(sB + j * GROUP_BYTES, &tmB, fb, n0 + j * GW, kb * BK, zb);
                         }
                     } else {
                         mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_BYTES);
@@ -417,15 +427,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, m0, za);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < BM / 64; ++j)
-                                tma_load_3d(sA + j * (64 * BK * 2), &tmA, &full_bar[stage], m0 + j * 64, kb * BK, za);
+                            for (int j = 0; j < BM / GW; ++j)
+                                tma_load_3d(sA + j * GROUP_BYTES, &tmA, &full_bar[stage], m0 + j * GW, kb * BK, za);
                         }
                         if (!B_MN) {
                             tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, n0, zb);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < BN / 64; ++j)
-                                tma_load_3d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK, zb);
+                            for (int j = 0; j < BN / GW; ++j)
+                                tma_load_3d(sB + j * GROUP_BYTES, &tmB, &full_bar[stage], n0 + j * GW, kb * BK, zb);
                         }
                     }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -439,7 +449,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------
         if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc = make_idesc(1 /*bf16*/, A_MN, B_MN, BMT, BN);
+            constexpr uint32_t idesc = make_idesc(C::TF32 ? 2 /*tf32*/ : 1 /*bf16*/, A_MN, B_MN, BMT, BN);
+            constexpr int KROWS = MMA_K_BYTES / C::ES;      // k-rows one MMA consumes of an MN-major tile: 16 or 8
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -460,15 +471,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t sA = smem_u32(smem + stage * C::STAGE_BYTES);
                     const uint32_t sB = sA + A_TILE_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // K-major: step 16 elements (32 bytes) inside the 128-byte row.
-                        // MN-major: step 16 k-rows of 128 bytes; 64-wide groups are BK*128 bytes apart.
-                        const uint64_t da = A_MN ? make_smem_desc(sA + k * UMMA_K * 128, BK * 128, 1024)
-                                                 : make_smem_desc(sA + k * UMMA_K * 2, 0, 1024);
-                        const uint64_t db = B_MN ? make_smem_desc(sB + k * UMMA_K * 128, BK * 128, 1024)
-                                                 : make_smem_desc(sB + k * UMMA_K * 2, 0, 1024);
-                        if constexpr (PAIR) mma_f16_ss_pair(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                        else                mma_f16_ss(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK_BYTES / MMA_K_BYTES; ++k) {
+                        // K-major: step 32 bytes (16 bf16 / 8 tf32 elements) inside the 128-byte row.
+                        // MN-major: step KROWS k-rows of 128 bytes; column groups are GROUP_BYTES apart.
+                        const uint64_t da = A_MN ? make_smem_desc(sA + k * KROWS * 128, GROUP_BYTES, 1024)
+                                                 : make_smem_desc(sA + k * MMA_K_BYTES, 0, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc(sB + k * KROWS * 128, GROUP_BYTES, 1024)
+                                                 : make_smem_desc(sB + k * MMA_K_BYTES, 0, 1024);
+                        const uint32_t accf = (kb > kb0 || k > 0) ? 1u : 0u;
+                        if constexpr (C::TF32) {
+                            if constexpr (PAIR) mma_tf32_ss_pair(tmem_d, da, db, idesc, accf);
+                            else                mma_tf32_ss(tmem_d, da, db, idesc, accf);
+                        } else {
+                            if constexpr (PAIR) mma_f16_ss_pair(tmem_d, da, db, idesc, accf);
+                            else                mma_f16_ss(tmem_d, da, db, idesc, accf);
+                        }
                     }
                     // stage is free (in both CTAs of a pair) once these MMAs have read it
                     if constexpr (PAIR) mma_commit_pair(&empty_bar[stage], 3); else mma_commit(&empty_bar[stage]);
@@ -834,6 +851,7 @@ constexpr int SPEC_BIAS_RELU = spec_pack(true, CME_ACT_RELU, 0, false, false, fa
 constexpr int SPEC_DRELU = spec_pack(false, 0, CME_ACT_RELU, false, false, false, 1, false);
 constexpr int SPEC_RES = spec_pack(false, 0, 0, true, false, false, 2, false);
 constexpr int SPEC_F32 = 1 << 11;
+constexpr int SPEC_TF32 = (1 << 11) | (1 << 14);      // fp32 operands multiplied as tf32, fp32 output
 // the pair the transformer's MLP uses: forward leaves GELU'(pre-activation), backward multiplies by it and sums columns
 constexpr int SPEC_BIAS_GELU_AUXD = spec_pack(true, CME_ACT_GELU, 0, false, false, true, 0, true, true);
 constexpr int SPEC_DMUL_COLSUM = spec_pack(false, 0, CME_ACT_GELU, false, false, false, 1, false, true, true);

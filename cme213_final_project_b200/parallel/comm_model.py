@@ -34,16 +34,3 @@ def gradient_floats(hidden: int, ff: int, vocab: int, seq_len: int) -> int:
     """Parameter count of the reference's one-block model (H128 -> 222,592; H256 -> 838,400; H512 -> 3,249,664)."""
     d = hidden
     return d * vocab + (ff * d + d) + (d * ff + ff) + 2 * d + d * d + 3 * d * d + 2 * d + vocab * d + seq_len * d
-
-
-def best_bucket_count(alpha: float, beta: float, total_bytes: float, backward_time: float, max_buckets: int = 64) -> int:
-    """Bucket count minimising exposed time when buckets become ready uniformly during a backward pass of
-    ``backward_time``: the last bucket is always exposed, every bucket pays ``alpha``."""
-    best, best_t = 1, float("inf")
-    for k in range(1, max_buckets + 1):
-        per = alpha + beta * total_bytes / k
-        comm_total = k * per
-        exposed = per + max(0.0, comm_total - per - backward_time * (k - 1) / k)
-        if exposed < best_t:
-            best, best_t = k, exposed
-    return best

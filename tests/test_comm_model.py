@@ -15,11 +15,6 @@ def test_reference_gradient_sizes():
     assert cm.gradient_floats(512, 2048, 65, 64) == 3249664
 
 
-def test_bucket_count_trades_latency_for_overlap():
-    assert cm.best_bucket_count(alpha=1.0, beta=1e-9, total_bytes=1e6, backward_time=1.0) == 1
-    assert cm.best_bucket_count(alpha=1e-3, beta=1e-6, total_bytes=1e6, backward_time=2.0) > 4
-
-
 def test_shard_alignment_makes_every_bucket_split_for_any_world():
     """Arena alignment lcm(64, 8 * world): every natural and coalesced bucket divides into `world` slices of whole
     16-byte bf16 vectors, also for worlds of 3, 5, 6, 7 (the reference validates 3 ranks,

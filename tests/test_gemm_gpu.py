@@ -241,3 +241,32 @@ def test_derivative_kept_by_forward_and_bias_gradient_in_the_epilogue(bn, M, N):
     _check(got, ref)
     assert ops.gemm.last_colsum_slabs == 0
     _check(dbias, got.float().sum(0), tol=1e-2)
+
+
+@pytest.mark.parametrize("a_trans,b_trans", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K,bn", [(128, 128, 64, 0), (256, 512, 256, 0), (384, 192, 320, 64), (1000, 520, 328, 128),
+                                      (1024, 256, 4096, 0), (512, 768, 256, 512), (1024, 1024, 96, 256)])
+def test_tf32_products_on_fp32_storage(M, N, K, bn, a_trans, b_trans):
+    """fp32 operands multiplied as tf32 on the tcgen05 kernel (every tile shape, both storage orders of both operands
+    -- the tensor core takes tf32 operands K-major only, the launcher transposes the others into the workspace --
+    split-K through the workspace, ragged edges) against an fp64 product.  tf32 keeps 10 mantissa bits of each
+    input: the tolerance is the reference's for its tensor-core backend on fp32 data (5e-3 of the output scale,
+    FINAL_CLEAN_CODE_/tests/test_gemm.cu:28-105)."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(70)
+    a = torch.randn((K, M) if a_trans else (M, K), generator=g, device="cuda") * 0.5
+    b = torch.randn((N, K) if b_trans else (K, N), generator=g, device="cuda") * 0.5
+    ref = _ref(a.double(), b.double(), a_trans, b_trans)
+    out = ops.gemm(a, b, a_trans=a_trans, b_trans=b_trans, backend="tcgen05", force_bn=bn)
+    torch.cuda.synchronize()
+    assert ops.gemm_check_status() == 0 and out.dtype == torch.float32
+    err = (out.double() - ref.double()).abs().max().item()
+    assert err <= 2e-3 * ref.abs().max().item(), err
+    # accumulate goes through the workspace
+    base = torch.randn(M, N, generator=g, device="cuda")
+    acc = base.clone()
+    ops.gemm(a, b, a_trans=a_trans, b_trans=b_trans, out=acc, accumulate=True, backend="tcgen05", force_bn=bn)
+    assert (acc.double() - (ref.double() + base.double())).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    # without the permission the tensor-core kernel refuses fp32 data and the dispatcher uses the exact kernel
+    exact = ops.gemm(a, b, a_trans=a_trans, b_trans=b_trans, allow_tf32=False)
+    assert (exact.double() - ref.double()).abs().max().item() <= 1e-4 * ref.abs().max().item()

@@ -44,6 +44,13 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
         assert (g.float() - g_ref.float()).abs().max().item() <= tol
         scale = max(1.0, db_ref.float().abs().max().item())
         assert (db.float() - db_ref.float()).abs().max().item() <= tol * scale
+        # and against the same arithmetic in plain PyTorch fp32 (not only against the sibling entry point)
+        x = pre.float().requires_grad_(True)
+        (torch.nn.functional.gelu(x, approximate="tanh") if act == "gelu" else torch.relu(x)).sum().backward()
+        g_torch = dout.float() * x.grad
+        assert (g.float() - g_torch).abs().max().item() <= tol * max(1.0, g_torch.abs().max().item())
+        db_torch = g.float().sum(0)                 # column sums of the values the kernel stored
+        assert (db.float() - db_torch).abs().max().item() <= tol * max(1.0, db_torch.abs().max().item())
     # plain column sum with accumulation into an existing gradient
     dout = torch.randn(1000, 72, generator=gen, device="cuda").to(dtype)
     base = torch.randn(72, generator=gen, device="cuda").to(dtype)
@@ -51,6 +58,8 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
     rc, _, got = _call(lib, ops, dout, None, None, False, dbias=base.clone(), accumulate=True)
     assert rc == 0
     assert (got.float() - want.float()).abs().max().item() <= tol * max(1.0, want.float().abs().max().item())
+    ref = base.float() + dout.float().sum(0)
+    assert (got.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
 
 
 def test_noalloc_refuses_sizes_beyond_its_scratch():
