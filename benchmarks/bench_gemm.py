@@ -31,10 +31,10 @@ def sites(m):
     return qkv + [
         # name, M, N, K, a_trans, b_trans, batch, epilogue
         ("attn_out_fwd", BT, D, D, False, False, 1, "res"),
-        ("ffn1_fwd", BT, FF, D, False, False, 1, "bias_" + act + ("_aux" if act == "gelu" else "")),
+        ("ffn1_fwd", BT, FF, D, False, False, 1, "bias_" + act + ("_auxd" if act == "gelu" else "")),
         ("ffn2_fwd", BT, D, FF, False, False, 1, "bias_res"),
         ("lm_head_fwd", BT, V, D, False, tied, 1, None),
-        ("ffn2_dgrad", BT, FF, D, False, True, 1, "d" + act),
+        ("ffn2_dgrad", BT, FF, D, False, True, 1, ("dmul" if act == "gelu" else "drelu") + "_colsum"),
         ("ffn1_dgrad", BT, D, FF, False, True, 1, None),
         ("attn_out_dgrad", BT, D, D, False, True, 1, None),
         ("lm_head_dgrad", BT, D, V, False, not tied, 1, None),
@@ -61,6 +61,15 @@ def epilogue_args(kind, M, N, dev="cuda"):
     if kind == "bias_gelu_aux":
         return {"bias": bias, "act": "gelu", "aux_out": torch.empty(M, N, device=dev, dtype=bf)}, \
             lambda y: gelu(y + bias.float())
+    if kind == "bias_gelu_auxd":          # what the engine runs: the epilogue also leaves GELU'(pre-activation)
+        return {"bias": bias, "act": "gelu", "aux_out": torch.empty(M, N, device=dev, dtype=bf), "aux_deriv": True}, \
+            lambda y: gelu(y + bias.float())
+    if kind == "dmul_colsum":             # ... and multiplies by it in backward, summing the bias gradient on the way
+        return {"dact": "gelu", "aux_in": pre, "aux_deriv": True, "dbias": torch.empty(N, device=dev, dtype=bf)}, \
+            lambda y: y * pre.float()
+    if kind == "drelu_colsum":
+        return {"dact": "relu", "aux_in": pre, "dbias": torch.empty(N, device=dev, dtype=bf)}, \
+            lambda y: y * (pre.float() > 0)
     if kind == "bias_relu":
         return {"bias": bias, "act": "relu"}, lambda y: torch.relu(y + bias.float())
     if kind == "dgelu":

@@ -365,6 +365,7 @@ class CmeAttn(ctypes.Structure):
         ("d_o", ctypes.c_void_p), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
         ("delta", ctypes.c_void_p), ("dq_accum", ctypes.c_void_p),
         ("ws", ctypes.c_void_p), ("ws_bytes", ctypes.c_longlong),
+        ("dq_sem", ctypes.c_void_p),
     ]
 
 
@@ -406,7 +407,10 @@ def attention_fwd(q, k, v, B: int, H: int, T: int, layout: str = "split", causal
 
 
 def attention_bwd(q, k, v, out, lse, dout, B: int, H: int, T: int, layout: str = "split", causal: bool = False,
-                  backend: str = "auto"):
+                  backend: str = "auto", ordered_dq: bool = False):
+    """Returns ``(dq, dk, dv)``.  ``ordered_dq`` (tensor-core kernel): the key blocks' parts of dQ are added in a fixed
+    order and dQ is finished inside the kernel (bit-reproducible, slower); default: unordered reduce-adds into a
+    cleared fp32 scratch and a conversion kernel."""
     _cuda(q, k, v, out, lse, dout)
     a = _attn_desc(q, B, H, T, layout, causal)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -415,6 +419,9 @@ def attention_bwd(q, k, v, out, lse, dout, B: int, H: int, T: int, layout: str =
     a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     a.d_o, a.dq, a.dk, a.dv = dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     a.delta, a.dq_accum = delta.data_ptr(), acc.data_ptr()
+    if ordered_dq:
+        sem = torch.zeros(B * H * ((T + 127) // 128), dtype=torch.int32, device=q.device)
+        a.dq_sem = sem.data_ptr()
     _check(lib().cme_attention_bwd(ctypes.byref(a), _BACKENDS[backend], _stream()))
     return dq, dk, dv
 

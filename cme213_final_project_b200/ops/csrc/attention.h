@@ -26,6 +26,9 @@ struct CmeAttn {
     float* delta;                // [nb*nh, T] scratch: rowsum(dO * O)
     float* dq_accum;             // fp32 scratch [nb*nh*T*HD] for the tcgen05 backward (may be null)
     void* ws; long long ws_bytes;    // scratch of attention_gemm_ws_bytes() for the batched-GEMM path (may be null)
+    int* dq_sem;                 // [nb*nh * ceil(T / 128)] ints, zero before the first launch (the kernel leaves them zero):
+                                 // lets the tcgen05 backward add the key blocks' parts of dQ in a fixed order and finish
+                                 // dQ itself; null = unordered adds into a cleared scratch plus a conversion kernel
 };
 
 int attention_simt_fwd(const CmeAttn* a, cudaStream_t st);

@@ -14,8 +14,14 @@
 // Backward, per CTA = one (batch, head) and 128 keys, looping over query blocks (thread = query row, so the
 // row's log-sum-exp and delta are two registers):
 //     S = Q_i K^T,  dP = dO_i V^T (TMEM)  ->  P, dS (bf16, shared, double buffered)
-//     dV += P^T dO_i,  dK += dS^T Q_i (A operand read transposed; TMEM accumulators),  dQ_i = dS K (TMEM, added
-//     to fp32 global with vector reductions; a small kernel scales and casts dQ at the end).
+//     dV += P^T dO_i,  dK += dS^T Q_i (A operand read transposed; TMEM accumulators),  dQ_i = dS K (TMEM).
+//     dQ_i gets a part from every key block that sees query block i.  Default: the parts are added to a cleared
+//     fp32 scratch with bulk reduce-adds in whatever order the CTAs arrive, and a small kernel scales and casts the
+//     sums (fast; the last bits of dQ depend on the order).  Deterministic form (a counter array is passed): the
+//     highest key block stores its part, each lower one adds its own when the tile's counter says it is its turn,
+//     and key block 0, whose turn is last, adds the sum to its part in registers, scales, casts and writes dQ --
+//     bit-reproducible, no clearing or conversion pass, but the chain of turns makes CTAs wait for one another
+//     (measured 0.32 ms against 0.25 ms per call at 16 x 12 heads x 1024 tokens).
 //     The scores of block i+1 are issued before the gradient MMAs of block i, so the arithmetic of block i+1
 //     overlaps them.
 // Every mbarrier wait is bounded; on expiry the CTA flags the status word, frees TMEM and returns.
@@ -211,9 +217,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     if (key >= p.T || (p.causal && key > q)) r[i] = 0xff800000u;     // -inf
                 }
             }
-            float mx = -INFINITY;
+            // eight independent chains (a single one would be 128 dependent operations long)
+            float mx8[8];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+            for (int c = 0; c < 8; ++c) mx8[c] = __uint_as_float(r[c]);
+#pragma unroll
+            for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(r[i]));
+            float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             mx *= p.scale_log2;                            // scale > 0, so the maximum commutes with it
             // Raise the reference maximum only when it would grow by more than the threshold: the accumulated
             // output then needs a rescale, which is rare after the first blocks.
@@ -242,18 +253,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 l *= alpha;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float sum = 0.f;
+            float sum8[8];                                 // one partial row sum per position in a group: independent chains
+#pragma unroll
+            for (int c = 0; c < 8; ++c) sum8[c] = 0.f;
 #pragma unroll
             for (int g = 0; g < 16; ++g) {                 // 16 groups of 8 keys = 16-byte chunks of the P row
                 float pr[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     pr[i] = ex2_approx(fmaf(__uint_as_float(r[g * 8 + i]), p.scale_log2, -m_use));
-                    sum += pr[i];
+                    sum8[i] += pr[i];
                 }
                 *reinterpret_cast<uint4*>(sP + (g >> 3) * TILE_BYTES + swz(row, g & 7)) = pack8(pr);
             }
-            l += sum;
+            l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
             tc_fence_before();
             fence_proxy_async();
             mbar_arrive(p_ready);
@@ -302,11 +315,32 @@ struct BwdParams {
     float scale, scale_log2;
     const float* lse;
     const float* delta;
-    float* dq_accum;               // fp32 [nb*nh, T, HD] accumulator (zeroed by the launcher); unused by the kernel body
+    float* dq_accum;               // fp32 [nb*nh, T, HD] scratch for the partial sums of dQ
     __nv_bfloat16* dk; __nv_bfloat16* dv;
-    long long sb, sh, st;          // strides of dK / dV
+    long long sb, sh, st;          // strides of dQ / dK / dV
     int* status;
+    int* dq_sem;                   // [nb*nh, query blocks] contribution counters (zero between launches), or null:
+                                   // unordered reduce-adds into a zeroed dq_accum, converted by dq_convert_kernel
+    __nv_bfloat16* dq;             // final dQ (ordered form only)
 };
+
+// Bounded wait until *sem >= want (acquire).  Lane 0 of the calling warp polls; the warp then synchronises.
+__device__ __forceinline__ bool sem_wait_warp(const int* sem, int want, volatile int* abort_flag) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        uint32_t i = 0;
+        for (;; ++i) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(sem) : "memory");
+            if (v >= want) break;
+            if ((i & 255u) == 255u && *abort_flag) { ok = false; break; }
+            if (i >= (1u << 22)) { *abort_flag = 1; ok = false; break; }
+            __nanosleep(32);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    return ok;
+}
 
 // shared: K 16K | V 16K | Q[2] 32K | dO[2] 32K | P 32K | dS[2] 64K | dQ staging (fp32) 32K | barriers   (one CTA per SM)
 constexpr int BWD_SMEM = 14 * TILE_BYTES + 128;
@@ -346,9 +380,17 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kb = blockIdx.x, k0 = kb * BKV;
+    // Ordered form: higher key blocks are dispatched first, so a CTA only ever waits for the dQ parts of key blocks
+    // above its own, which are then resident or finished.  Unordered form: the key blocks with the most query blocks
+    // (the lowest) first.
+    const int nkb = gridDim.x;
+    const bool ordered = p.dq_sem != nullptr;
+    const int kb = ordered ? nkb - 1 - (int)blockIdx.x : (int)blockIdx.x, k0 = kb * BKV;
     const int bh = blockIdx.y, b = bh / p.nh, h = bh % p.nh;
     const int nq = (p.T + BQ - 1) / BQ;
+    // first key block to contribute to query block qi (the highest one that sees it); key block kb's turn comes when
+    // first_kb(qi) - kb parts are in, key block 0 finishes the tile
+    auto first_kb = [&](int qi) { return p.causal ? min(qi, nkb - 1) : nkb - 1; };
     const int i_begin = p.causal ? kb : 0;     // query blocks that see this key block
     const int n_it = nq - i_begin;
 
@@ -453,16 +495,42 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (!ok) for (int i = 0; i < 2000; ++i) __nanosleep(500);
         }
     } else if (warp == BWD_STORE_WARP) {
-        // ---------------- dQ reduce-store issuer: adds each staged 128 x 64 fp32 tile into the global accumulator
-        if (lane == 0) {
+        // ---------------- dQ store issuer: moves each staged 128 x 64 fp32 tile into the global scratch.  Ordered form:
+        // when it is this key block's turn -- a plain tile store if it is the first part, else a bulk reduce-add --
+        // and the tile's counter is raised once the write has completed.  Key block 0 does not come through here.
+        if (lane == 0 && !(ordered && kb == 0)) {
             for (int f = 0; f < n_it; ++f) {
                 if (!mbar_wait(dqs_full, f & 1, abort_flag)) break;
-                const int q0 = (i_begin + f) * BQ;
-                tma_reduce_add_3d(&tmdQ, sdQ, 0, q0, bh);
-                tma_reduce_add_3d(&tmdQ, sdQ + TILE_BYTES, 32, q0, bh);
+                const int qi = i_begin + f, q0 = qi * BQ;
+                int* sem = ordered ? p.dq_sem + (long long)bh * nq + qi : nullptr;
+                const int turn = ordered ? first_kb(qi) - kb : 1;
+                if (ordered) {
+                    bool mine = false;
+                    for (uint32_t i = 0; i < (1u << 22); ++i) {
+                        int v;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(sem) : "memory");
+                        if (v >= turn) { mine = true; break; }
+                        if ((i & 255u) == 255u && *abort_flag) break;
+                        __nanosleep(32);
+                    }
+                    if (!mine) { *abort_flag = 1; break; }
+                }
+                if (turn == 0) {
+                    tma_store_3d(&tmdQ, sdQ, 0, q0, bh);
+                    tma_store_3d(&tmdQ, sdQ + TILE_BYTES, 32, q0, bh);
+                } else {
+                    tma_reduce_add_3d(&tmdQ, sdQ, 0, q0, bh);
+                    tma_reduce_add_3d(&tmdQ, sdQ + TILE_BYTES, 32, q0, bh);
+                }
                 tma_store_commit();
                 tma_store_wait_read<0>();
-                mbar_arrive(dqs_free);
+                mbar_arrive(dqs_free);                  // the staging tile may be refilled
+                if (ordered) {
+                    tma_store_wait<0>();                // the tile is in global memory
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(sem), "r"(turn + 1) : "memory");
+                }
             }
             tma_store_wait<0>();
         }
@@ -477,12 +545,42 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // store warp then adds the tile into the global accumulator with one bulk reduce per 32-column half
         // `signal`: false leaves the proxy fence and the arrival on dqs_full to the caller, who then covers the P / dS
         // stores of the current block and this staging write with one fence
+        const bool finisher = ordered && kb == 0;       // this CTA completes dQ of every query block it sees
         auto flush_dq = [&](int f, bool signal) -> bool {
             if (!mbar_wait(dq_full, f & 1, abort_flag)) return false;
             tc_fence_after();
             uint32_t t[16];
             tmem_ld16(tmem_dQ + lane_addr + cg * 16, t);
             tmem_wait_ld();
+            if (finisher) {
+                // every other key block's part of this query block is in the scratch tile (their counters say so):
+                // add it to this thread's 16 columns, scale, cast, store dQ
+                const int qi = i_begin + f, need = first_kb(qi);
+                const int qrow = qi * BQ + row;
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(t[i]);
+                if (need > 0) {
+                    if (!sem_wait_warp(p.dq_sem + (long long)bh * nq + qi, need, abort_flag)) return false;
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    if (qrow < p.T) {
+                        const float4* src = reinterpret_cast<const float4*>(p.dq_accum + ((long long)bh * p.T + qrow) * HD + cg * 16);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const float4 a = __ldcg(src + g);
+                            v[4 * g] += a.x; v[4 * g + 1] += a.y; v[4 * g + 2] += a.z; v[4 * g + 3] += a.w;
+                        }
+                    }
+                }
+                if (qrow < p.T) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] *= p.scale;
+                    __nv_bfloat16* dst = p.dq + (long long)b * p.sb + (long long)h * p.sh + (long long)qrow * p.st + cg * 16;
+                    *reinterpret_cast<uint4*>(dst) = pack8(v);
+                    *reinterpret_cast<uint4*>(dst + 8) = pack8(v + 8);
+                }
+                return true;
+            }
             if (f > 0 && !mbar_wait(dqs_free, (f - 1) & 1, abort_flag)) return false;
             uint8_t* atom = sdQ + (cg >> 1) * TILE_BYTES;
 #pragma unroll
@@ -543,7 +641,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (it > 0 && !flush_dq(it - 1, false)) { ok = false; break; }
             tc_fence_before();
             fence_proxy_async();                        // one fence for P, dS and the dQ staging tile
-            if (it > 0) mbar_arrive(dqs_full);
+            if (it > 0 && !finisher) mbar_arrive(dqs_full);
             mbar_arrive(p_ready);
         }
         if (ok && n_it > 0) ok = flush_dq(n_it - 1, true);
@@ -572,6 +670,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     tc_fence_before();
     __syncthreads();
+    // every warp of the finishing CTA is past its waits and no other CTA touches these counters again: back to zero
+    // for the next launch
+    if (ordered && kb == 0 && (int)threadIdx.x < n_it) p.dq_sem[(long long)bh * nq + i_begin + threadIdx.x] = 0;
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, CME_ERR_TIMEOUT);
     if (warp == BWD_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, BWD_TMEM_COLS); }
 }
@@ -717,7 +818,8 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
     if ((rc = make_map4(&mv, a->v, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mdo, a->d_o, a->T, a->nh, a->nb, a->ost, a->osh, a->osb, 128))) return rc;
     if ((rc = make_map_dq(&mdq, a->dq_accum, a->T, a->nb * a->nh))) return rc;
-    CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
+    const bool ordered = a->dq_sem != nullptr;
+    if (!ordered) CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
     static bool attr[CME_MAX_DEVICES] = {};               // function attributes are per device
     int dev = 0;
     CME_CUDA(cudaGetDevice(&dev));
@@ -726,10 +828,12 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
         attr[dev % CME_MAX_DEVICES] = true;
     }
     BwdParams p{a->T, a->nh, a->causal, a->scale, a->scale * LOG2E, a->lse, a->delta, a->dq_accum,
-                (__nv_bfloat16*)a->dk, (__nv_bfloat16*)a->dv, a->sb, a->sh, a->st, g_attn_status};
+                (__nv_bfloat16*)a->dk, (__nv_bfloat16*)a->dv, a->sb, a->sh, a->st, g_attn_status, a->dq_sem,
+                (__nv_bfloat16*)a->dq};
     dim3 grid(cme_cdiv(a->T, BKV), a->nb * a->nh);
     attn_bwd_tc_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, mdo, mdq, p);
     CME_LAUNCH_CHECK();
+    if (ordered) return CME_OK;                    // dQ was completed inside the kernel
     const long long nthreads = rows * (HD / 8);
     CME_CUDA(cme_launch_dependent(dq_convert_kernel, dim3(cme_cdiv(nthreads, 256)), dim3(256), 0, st,
                                   (const float*)a->dq_accum, (__nv_bfloat16*)a->dq, a->T, a->nh, a->sb, a->sh, a->st,

@@ -90,6 +90,7 @@ struct Engine {
     // backward temporaries
     char *dxa, *dxb, *dff, *dln, *dqkv, *dattn;
     float *delta, *dq_accum, *ln_scratch, *col_scratch;
+    int* dq_sem = nullptr;          // per (batch, head, query block) counters ordering the dQ parts; zero between launches
     void* attn_ws; long long attn_ws_bytes;
     void* gemm_ws; long long gemm_ws_bytes;
     void* gemm_ws_side; long long gemm_ws_side_bytes;     // split-K partials of the products on the second stream
@@ -144,6 +145,7 @@ size_t carve(Engine& e, char* base) {
     e.dattn = take(BT * D * es);
     e.delta = (float*)take((size_t)e.BH * d.T * 4);
     e.dq_accum = (float*)take(BT * D * 4);
+    e.dq_sem = (int*)take((size_t)e.BH * ((d.T + 127) / 128) * 4);
     e.attn_ws_bytes = (d.head_flat && d.T <= 512) ? attention_gemm_ws_bytes(e.BH, d.T) : 0;
     e.attn_ws = e.attn_ws_bytes ? take((size_t)e.attn_ws_bytes) : nullptr;
     const size_t widest = FF > D ? FF : D;
@@ -186,6 +188,13 @@ int gemm(const Engine& e, cudaStream_t st, int M, int N, int K, const void* A, l
     return cme_gemm(&g, e.d.gemm_backend, st);
 }
 
+// CME213_DETERMINISTIC=1: the attention backward adds the key blocks' parts of dQ in a fixed order (bit-reproducible
+// gradients, about 0.07 ms per layer slower at GPT-2 small shapes); default: unordered reduce-adds.
+bool attn_ordered_dq() {
+    static const bool on = getenv("CME213_DETERMINISTIC") && getenv("CME213_DETERMINISTIC")[0] == '1';
+    return on;
+}
+
 void fill_attn(const Engine& e, int l, CmeAttn& a) {
     const CmeEngineDesc& d = e.d;
     const int HD = d.D / d.H;
@@ -206,6 +215,7 @@ void fill_attn(const Engine& e, int l, CmeAttn& a) {
     if (d.head_flat) { a.osb = (long long)d.T * HD; a.osh = 0; a.ost = HD; }
     else { a.osb = (long long)d.T * D; a.osh = HD; a.ost = D; }
     a.lse = e.la[l].lse; a.delta = e.delta; a.dq_accum = e.dq_accum;
+    a.dq_sem = attn_ordered_dq() ? e.dq_sem : nullptr;
     a.ws = e.attn_ws; a.ws_bytes = e.attn_ws_bytes;
 }
 
@@ -246,6 +256,8 @@ CME_API int cme_engine_bind(void* h, void* params, void* grads, void* workspace,
     CME_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, CME_ERR_SHAPE, "engine: workspace must be 256-byte aligned");
     e->params = (char*)params; e->grads = (char*)grads; e->ws = (char*)workspace;
     carve(*e, e->ws);
+    // the attention backward's ordering counters start at zero; every launch leaves them at zero again
+    CME_CUDA(cudaMemset(e->dq_sem, 0, (size_t)e->BH * ((e->d.T + 127) / 128) * 4));
     return CME_OK;
 }
 

@@ -115,7 +115,7 @@ EncodeTiledFn get_encoder() {
 
 // 3-D tensor map: dims (inner, rows, batch), 128-byte swizzle, box (128 bytes of inner, box_rows, 1).
 int make_tmap(CUtensorMap* out, const void* base, long long inner, long long rows, long long ld, long long batch,
-              long long batch_stride, int box_rows, bool f32 = false) {
+              long long batch_stride, int box_rows, bool f32 = false, bool round_tf32 = false) {
     EncodeTiledFn enc = get_encoder();
     CME_REQUIRE(enc != nullptr, CME_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const int es = f32 ? 4 : 2;
@@ -123,7 +123,11 @@ int make_tmap(CUtensorMap* out, const void* base, long long inner, long long row
     cuuint64_t strides[2] = {(cuuint64_t)ld * es, (cuuint64_t)(batch_stride > 0 ? batch_stride : ld * rows) * es};
     cuuint32_t box[3] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+    // operands of a tf32 product are rounded to tf32 (to nearest) by the copy engine on their way into shared
+    // memory; the tensor core would otherwise just drop the low mantissa bits, a one-sided error
+    const CUtensorMapDataType dt = !f32 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                        : round_tf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    CUresult r = enc(out, dt, 3,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CME_REQUIRE(r == CUDA_SUCCESS, CME_ERR_CUDA,
@@ -327,13 +331,13 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     CUtensorMap ta, tb;
     int rc;
     // A: K-major -> map (K, M), box (64, 128); MN-major -> map (M, K), box (64, 64)
-    if (!g->a_trans) rc = make_tmap(&ta, g->A, g->K, g->M, g->lda, g->strideA ? g->batch : 1, g->strideA, BM, tf32);
-    else             rc = make_tmap(&ta, g->A, g->M, g->K, g->lda, g->strideA ? g->batch : 1, g->strideA, BK, tf32);
+    if (!g->a_trans) rc = make_tmap(&ta, g->A, g->K, g->M, g->lda, g->strideA ? g->batch : 1, g->strideA, BM, tf32, tf32);
+    else             rc = make_tmap(&ta, g->A, g->M, g->K, g->lda, g->strideA ? g->batch : 1, g->strideA, BK, tf32, tf32);
     if (rc) return rc;
     // B: stored [N, K] (b_trans) is K-major -> map (K, N), box (64, bn); stored [K, N] -> map (N, K), box (64, 64)
     if (g->b_trans) rc = make_tmap(&tb, g->B, g->K, g->N, g->ldb, g->strideB ? g->batch : 1, g->strideB,
-                                   pair ? bn / 2 : bn, tf32);
-    else            rc = make_tmap(&tb, g->B, g->N, g->K, g->ldb, g->strideB ? g->batch : 1, g->strideB, BK, tf32);
+                                   pair ? bn / 2 : bn, tf32, tf32);
+    else            rc = make_tmap(&tb, g->B, g->N, g->K, g->ldb, g->strideB ? g->batch : 1, g->strideB, BK, tf32, tf32);
     if (rc) return rc;
 
     EpiParams ep{};

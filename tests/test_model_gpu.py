@@ -257,10 +257,12 @@ def test_tf32_engine_tracks_oracle(preset_name):
         sl = slice(s.offset, s.offset + s.numel)
         if ref.grads[sl].abs().max() < 1e-7:
             continue
-        # tensors whose whole gradient is a cancellation residual far below the others' scale are held to an
-        # absolute bound instead
+        # with random targets on an untrained model most gradient tensors are residuals of cancelling terms, so the
+        # 2^-11 relative rounding of each tf32 input shows up amplified: direction per tensor, relative error for
+        # the tensors that are not residuals far below the others' scale
+        assert _cos(g[sl], ref.grads[sl]) > 0.98, (s.name, _cos(g[sl], ref.grads[sl]))
         small = (g[sl] - ref.grads[sl]).abs().max().item() < 1e-3 * gmax
-        assert _rel(g[sl], ref.grads[sl]) < 5e-2 or small, (s.name, _rel(g[sl], ref.grads[sl]))
+        assert _rel(g[sl], ref.grads[sl]) < 0.25 or small, (s.name, _rel(g[sl], ref.grads[sl]))
     p0 = strict.master.clone()
     for _ in range(3):
         for m in (eng, strict):
