@@ -89,7 +89,7 @@ def main():
                     ops._p(am), ops._p(av), ops._p(step), ops._p(lr), ctypes.c_float(0.9), ctypes.c_float(0.95),
                     ctypes.c_float(1e-8), ctypes.c_float(0.1), ctypes.c_float(1.0 / W), None, 0, fused_algo[0], 3,
                     comm.max_buckets, ctas, ops._p(comm.ctl), ops._p(comm.status), ctypes.c_double(comm.budget_ms),
-                    None, None, None, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+                    None, None, None, None, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
         nbytes = a.min_kb * 1024
         while nbytes <= a.max_mb * (1 << 20):
             n = max(nbytes // es, (16 // es) * W)

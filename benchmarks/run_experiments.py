@@ -168,7 +168,7 @@ def cmd_trajectory(a):
         traj[name] = parse_trajectory(out)
         print(f"[trajectory] {name}: {len(traj[name])} steps rc={rc}")
     res = {name: compare_trajectories(traj["blocking"], t) for name, t in traj.items() if name != "blocking"}
-    spans = {name: max([max(s.sum_span, s.sumsq_span, s.maxabs_span) for s in t] or [float("nan")])
+    spans = {name: max([max(abs(s["sum_span"]), abs(s["sumsq_span"]), abs(s["maxabs_span"])) for s in t] or [float("nan")])
              for name, t in traj.items()}
     rows = [[name, len(traj[name]), res[name]["ok"] if name in res else True, spans[name]] for name in modes]
     save(a, f"trajectory_{a.preset}_g{a.gpus[0]}",

@@ -113,6 +113,7 @@ class RunConfig:
     device: str = "auto"           # auto | cuda | cpu
     engine: str = "auto"           # auto | native | torch
     log_every: int = 100
+    step_timeout_s: float = 0.0    # > 0: end the process if no step completes for this long (host watchdog)
     epilogue_fusion: bool = True   # False: bias / activation / residual as separate kernels (ablation)
 
 
@@ -307,6 +308,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--device", default="auto")
     p.add_argument("--engine", default="auto")
     p.add_argument("--log-every", type=int, default=100)
+    p.add_argument("--step-timeout", type=float, default=0.0,
+                   help="seconds without a completed step after which the process ends itself (0 = off)")
     p.add_argument("--no-epilogue-fusion", action="store_true",
                    help="run bias / activation / residual / activation-derivative as separate kernels (ablation)")
     return p
@@ -334,7 +337,7 @@ def parse_args(argv: Optional[Sequence[str]] = None) -> Tuple[ModelConfig, Optim
                     compute_dtype=a.compute_dtype, synthetic=a.synthetic, seed=a.seed,
                     save_checkpoint=a.save_checkpoint, load_checkpoint=a.load_checkpoint, profile=a.profile,
                     device=a.device, engine=a.engine, log_every=a.log_every,
-                    epilogue_fusion=not a.no_epilogue_fusion)
+                    epilogue_fusion=not a.no_epilogue_fusion, step_timeout_s=a.step_timeout)
     return model, optim, apply_environment(run)
 
 

@@ -89,6 +89,8 @@ struct FwdParams {
 constexpr int FWD_SMEM = 7 * TILE_BYTES + 128;      // two CTAs per SM must fit: 2 x (this + 1 KB reserved) <= 228 KB
 constexpr int FWD_THREADS = 160;
 constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O accumulator: [128,192)
+static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM's shared memory");
+static_assert(128 + HD <= FWD_TMEM_COLS && 2 * FWD_TMEM_COLS <= 512, "forward TMEM budget: S + O per CTA, two CTAs per SM");
 constexpr float RESCALE_THRESHOLD = 8.f;   // log2 units: the running maximum is only raised when it grows by > 2^8
 
 __global__ void __launch_bounds__(FWD_THREADS, 2)
@@ -348,6 +350,8 @@ constexpr int BWD_MMA_WARP = 16;           // warps 0..15 compute, warp 16 issue
 constexpr int BWD_STORE_WARP = 17;         // warp 17 issues the dQ reduce-stores
 constexpr int BWD_THREADS = 18 * 32;
 constexpr int BWD_TMEM_COLS = 512;     // S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ [384,448)
+static_assert(BWD_SMEM <= 227 * 1024, "backward shared-memory carve-up exceeds what one CTA may have");
+static_assert(2 * 128 + 3 * HD <= BWD_TMEM_COLS, "backward TMEM budget: S, dP, dV, dK, dQ");
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,

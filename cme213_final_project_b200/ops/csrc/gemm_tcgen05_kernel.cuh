@@ -78,6 +78,10 @@ template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
     static constexpr int STAGES = FIT > 8 ? 8 : FIT;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIXED_BYTES;
     static_assert(STAGES >= 3, "too few main-loop stages");
+    static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared-memory carve-up exceeds what one CTA may have");
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "two accumulators must fit TMEM (power of two)");
+    static_assert(STAGE_BYTES % 1024 == 0 && A_TILE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte aligned bases");
+    static_assert(BAR_BYTES >= (2 * 8 + 4 + EPI_WARPS * NB) * 8 + 8, "barrier block too small");
 };
 
 struct EpiParams {

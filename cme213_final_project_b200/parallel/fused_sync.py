@@ -28,6 +28,7 @@ import torch.distributed as dist
 from .. import ops
 from ..arena import Bucket
 from ..config import RunConfig, min_bucket_elems
+from ..utils.nvtx import nvtx_range
 from .symm import LocalPeers, SymmetricBuffer
 
 ALGOS = {"one_shot": 0, "two_shot": 1, "nvls": 2}
@@ -148,8 +149,9 @@ class FusedSync:
             self.params = SymmetricBuffer(n, torch.bfloat16, dev)
             self.params.tensor.copy_(model.params)
         model.rebind(self.params.tensor, self.grads.tensor)
-        # two flag / control indices past the gradient buckets serve the clip kernel (barrier, norm exchange)
-        self.comm = PeerComm(dev, max_buckets=len(self.buckets) + 2, budget_ms=budget_ms, single=single)
+        # flag / control indices past the gradient buckets: two serve the clip kernel (barrier, norm exchange), one the
+        # start-up measurement
+        self.comm = PeerComm(dev, max_buckets=len(self.buckets) + 3, budget_ms=budget_ms, single=single)
         # SM budget: one small CTA per SM while backward is still running (they share SMs with the compute
         # kernels); the last bucket has the GPU to itself and gets four per SM
         self.ctas = min(int(os.environ.get("CME213_COMM_CTAS", ctas)), MAX_CTAS)
@@ -164,9 +166,20 @@ class FusedSync:
         if forced == "nvls" and not self.has_multicast:
             raise ops.NativeError("comm algorithm 'nvls' requested but the buffers have no multicast mapping")
         tab = table if table is not None else table_for_world(load_table(getattr(run, "comm_table", None)), self.world)
+        # Which variant synchronises which bucket: forced by the caller, else measured right here on this machine's
+        # fabric (a few all-reduces per distinct bucket size, a few tens of milliseconds), else from the shipped table
+        # of earlier sweeps.  The measurement is the reference's alpha-beta sweep idea moved to start-up
+        # (FINAL_CLEAN_CODE_/tests/benchmark_allreduce_alpha_beta.cu): the fastest variant differs between world sizes
+        # and machines (at 2 ranks peer loads beat the in-switch reduction at every size, at 8 it is the reverse).
+        self.calibration: Dict[int, Dict[str, float]] = {}
+        measured: Dict[int, str] = {}
+        if (forced == "auto" and table is None and not single and self.has_multicast
+                and os.environ.get("CME213_COMM_CALIBRATE", "1") != "0"):
+            measured = self._calibrate()
         self.algos: List[str] = []
         for b in self.buckets:
-            a = forced if forced != "auto" else choose_algo(b.numel * elem, self.world, self.has_multicast, tab)
+            a = forced if forced != "auto" else measured.get(b.numel) or \
+                choose_algo(b.numel * elem, self.world, self.has_multicast, tab)
             if a == "one_shot" and (self.clip or single):
                 a = "two_shot"                       # the reduce-only form keeps slices; a world of one has one slice
             self.algos.append(a)
@@ -174,6 +187,7 @@ class FusedSync:
         self.grad_scale = 1.0 / self.world
         self.lib = ops.lib()
         self.launched = 0
+        self.profile = bool(getattr(run, "profile", False))      # NVTX range around every bucket launch
         self.measure_exposed = False
         self._exposed = []
         # device-side time log (ns, %globaltimer): [2b] / [2b + 1] = start / end of bucket b's kernel (index
@@ -188,6 +202,40 @@ class FusedSync:
         else:
             self.gred = self.norm_part = self.norm_bucket = self.ranges = None
 
+    def _calibrate(self) -> Dict[int, str]:
+        """Time the all-reduce variants on every distinct bucket size (same NVLink traffic pattern as the fused kernel:
+        reduce-scatter, then all-gather) with the CTA count that bucket will run with; the max over ranks decides, so
+        every rank picks the same variant.  Returns ``{bucket elements: variant}``."""
+        dev = self.model.device
+        sizes = sorted({b.numel for b in self.buckets})
+        tmp = SymmetricBuffer(max(sizes), torch.bfloat16, dev)
+        spare = len(self.buckets) + 2
+        out: Dict[int, str] = {}
+        for n in sizes:
+            last = self.buckets[-1].numel == n
+            ctas = self.tail_ctas if last else self.ctas
+            times: Dict[str, float] = {}
+            for algo in (("one_shot",) if (n * 2 <= (1 << 20) and not self.clip) else ()) + ("two_shot", "nvls"):
+                for _ in range(2):
+                    self.comm.allreduce(self.grads, tmp, n, algo=algo, bucket=spare, ctas=ctas)
+                dist.barrier(device_ids=[dev.index])
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    self.comm.allreduce(self.grads, tmp, n, algo=algo, bucket=spare, ctas=ctas)
+                e1.record()
+                e1.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / 5], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                times[algo] = t.item()
+            self.calibration[n] = times
+            out[n] = min(times, key=times.get)
+        if self.comm.check_status():
+            raise ops.NativeError("a peer did not arrive during the start-up measurement of the synchronisation kernels")
+        tmp.barrier()
+        del tmp
+        return out
+
     def describe(self) -> str:
         """One line for the training banner: which kernels synchronise which buckets."""
         kinds = sorted(set(self.algos))
@@ -195,7 +243,12 @@ class FusedSync:
         form = "reduce per bucket + one clip/AdamW/all-gather kernel" if self.clip else \
                "reduce-scatter + AdamW + all-gather per bucket"
         when = "overlapped with backward" if self.overlap else "after backward"
-        return f"fused device kernels ({form}), {when}; {len(self.buckets)} buckets: {per}"
+        how = ""
+        if self.calibration:
+            how = "; measured at start-up (ms): " + ", ".join(
+                f"{n * 2 / 2 ** 20:.0f} MB " + "/".join(f"{k} {v:.3f}" for k, v in t.items())
+                for n, t in sorted(self.calibration.items()))
+        return f"fused device kernels ({form}), {when}; {len(self.buckets)} buckets: {per}{how}"
 
     def _opt_args(self):
         m, o = self.model, self.model.optim
@@ -214,6 +267,14 @@ class FusedSync:
             ops._check(self.lib.cme_record_time(ctypes.c_void_p(self.tlog.data_ptr() + 8 * (nlog - 2)), ops._stream()))
         self.model.fence(self.stream)                 # the bucket's producers, on either of the engine's streams
         opt, nd = self._opt_args()
+        with nvtx_range(f"fused_sync_bucket_{b.index}", self.profile):
+            self._launch_bucket_kernel(b, opt, nd, last)
+        self.launched += 1
+        if last and self.clip:
+            with nvtx_range("fused_sync_clip_adamw", self.profile):
+                self._launch_clip()
+
+    def _launch_bucket_kernel(self, b: Bucket, opt, nd, last: bool) -> None:
         ops._check(self.lib.cme_comm_fused_adamw(
             self.world, self.comm.rank, self.grads.c_ptrs, self.params.c_ptrs, self.comm.flags.c_ptrs,
             ctypes.c_void_p(self.grads.multicast_ptr), ctypes.c_void_p(self.params.multicast_ptr),
@@ -222,9 +283,6 @@ class FusedSync:
             ops._p(self.comm.ctl), ops._p(self.comm.status), ctypes.c_double(self.comm.budget_ms),
             ops._p(self.gred), ops._p(self.norm_part), ops._p(self.norm_bucket), ops._p(self.tlog),
             ctypes.c_void_p(self.stream.cuda_stream)))
-        self.launched += 1
-        if last and self.clip:
-            self._launch_clip()
 
     def _launch_clip(self) -> None:
         """Second phase under clipping: global norm across ranks, clip, AdamW on the owned slices, all-gather."""

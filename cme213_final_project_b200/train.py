@@ -181,6 +181,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                     print(ckpt.trajectory_line(epoch + 1, step + 1, step_loss, st, spans), flush=True)
             if (step + 1) % run.log_every == 0 or step + 1 == steps_per_epoch:
                 trainer.check_device_status()                   # raises if a bounded device-side wait ran out
+                if trainer.watchdog is not None:
+                    trainer.watchdog.beat()                     # the status read synchronised: the device answers
             if root and ((step + 1) % run.log_every == 0 or step + 1 == steps_per_epoch):
                 step_loss = model.read_loss()
                 logged_sum += step_loss
@@ -214,6 +216,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         if root:
             st = ckpt.save_checkpoint(run.save_checkpoint, model.layout, p, m, v, t)
             say(f"Checkpoint: wrote {run.save_checkpoint} step={t} param_hash={st.hex_hash()}")
+    if trainer.watchdog is not None:
+        trainer.watchdog.stop()
     d.finalize()
     return 0
 

@@ -19,6 +19,47 @@ from .parallel.dist import DistributedContext
 from .utils.nvtx import nvtx_range
 
 
+class StepWatchdog:
+    """Host-side watchdog: if no step completes for ``timeout_s`` seconds the process is ended with a message.
+
+    The reference bounds every run from outside (``timeout --kill-after`` per case, ``scripts/common_env.sh:31-40``)
+    and has no detection of its own; here a stalled step -- a rank that never arrives at a collective, a device that
+    stopped answering -- ends the process from inside instead of leaving the job hanging until someone notices.
+    ``beat()`` is called after every step the trainer hands to the device and after every synchronising read.
+    ``on_expire`` (tests) replaces the default action, which prints to stderr and exits with status 3."""
+
+    def __init__(self, timeout_s: float, on_expire=None, poll_s: float = 0.25) -> None:
+        import threading
+        import time
+        self.timeout_s, self.on_expire, self.poll_s = timeout_s, on_expire, poll_s
+        self._last = time.monotonic()
+        self._stop = threading.Event()
+        self.expired = False
+        self._thread = threading.Thread(target=self._run, name="step-watchdog", daemon=True)
+        self._thread.start()
+
+    def beat(self) -> None:
+        import time
+        self._last = time.monotonic()
+
+    def stop(self) -> None:
+        self._stop.set()
+
+    def _run(self) -> None:
+        import os
+        import sys
+        import time
+        while not self._stop.wait(self.poll_s):
+            if time.monotonic() - self._last > self.timeout_s:
+                self.expired = True
+                if self.on_expire is not None:
+                    self.on_expire()
+                    return
+                print(f"Error: no training step completed for {self.timeout_s:.0f} s; ending the process",
+                      file=sys.stderr, flush=True)
+                os._exit(3)
+
+
 class Trainer:
     def __init__(self, model, dist_ctx: DistributedContext, run: RunConfig, optim: OptimConfig) -> None:
         self.model = model
@@ -33,6 +74,7 @@ class Trainer:
         self.async_start_ms_sum = 0.0
         self.steps = 0
         self.graphed = None
+        self.watchdog = StepWatchdog(run.step_timeout_s) if getattr(run, "step_timeout_s", 0) > 0 else None
 
     def enable_cuda_graph(self, warmup_steps: int = 3) -> bool:
         """Replay the whole step as one CUDA graph after ``warmup_steps`` eager steps (the reference's
@@ -72,6 +114,8 @@ class Trainer:
             self.steps += 1
         else:
             self._step(tokens, targets)
+        if self.watchdog is not None:
+            self.watchdog.beat()
 
     def _stage(self, tokens, targets):
         dev = self.model.device

@@ -101,3 +101,19 @@ def test_cli_trains_on_cpu_and_writes_checkpoint(tmp_path):
     r2 = subprocess.run(args[:-1 if args[-1] != "--synthetic" else len(args)] + (["--load-checkpoint", ck] + ([args[-1]] if args[-1] != "--synthetic" else [])),
                         capture_output=True, text=True, timeout=300, cwd=ROOT)
     assert r2.returncode == 0 and "Checkpoint: loaded" in r2.stdout, r2.stderr[-2000:]
+
+
+def test_step_watchdog_fires_when_steps_stop_and_not_while_they_run():
+    """Host-side failure detection: steps that keep completing keep the watchdog quiet; a stall longer than the
+    timeout triggers it (the failure is made on the host: the loop simply stops stepping)."""
+    import time
+    from cme213_final_project_b200.trainer import StepWatchdog
+    fired = []
+    wd = StepWatchdog(0.4, on_expire=lambda: fired.append(time.monotonic()), poll_s=0.05)
+    for _ in range(10):
+        time.sleep(0.1)
+        wd.beat()
+    assert not fired and not wd.expired
+    time.sleep(0.8)                       # the "stalled step"
+    assert fired and wd.expired
+    wd.stop()

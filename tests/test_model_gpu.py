@@ -269,8 +269,10 @@ def test_tf32_engine_tracks_oracle(preset_name):
             m.train_step([x.cuda()], [y.cuda()])
             m.update()
     torch.cuda.synchronize()
-    upd = (strict.master - p0).abs().max().item()
-    assert (eng.master - strict.master).abs().max().item() < 0.1 * upd + 1e-6
+    # Adam moves every parameter by about lr per step whatever the size of its gradient, so the few parameters whose
+    # near-zero gradient changes sign under tf32 rounding differ by whole steps: compare the updates as vectors
+    d_strict, d_tf32 = (strict.master - p0).double(), (eng.master - p0).double()
+    assert ((d_tf32 - d_strict).norm() / d_strict.norm()).item() < 0.2
     assert ops.gemm_check_status() == 0
 
 
