@@ -174,7 +174,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
             if run.trace_trajectory:
                 if d.device.type == "cuda":
                     torch.cuda.synchronize()
-                st = ckpt.param_stats(model.master_params() if hasattr(model, "master_params") else model.params)
+                # fp32 master values: under the fused path every rank owns a slice of them, so they are gathered
+                # (a collective all ranks enter; tracing mode only)
+                if getattr(model, "fused", None) is not None and d.world_size > 1:
+                    traced = model.state()[0]
+                else:
+                    traced = model.master_params() if hasattr(model, "master_params") else model.params
+                st = ckpt.param_stats(traced)
                 spans = tuple(d.max_double(x) - d.min_double(x) for x in (st.sum, st.sumsq, st.max_abs))
                 if root:
                     step_loss = model.read_loss()
