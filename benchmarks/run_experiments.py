@@ -423,6 +423,8 @@ def main():
     a.extra = [e for e in extra if e != "--"]
     if not a.synthetic and not os.path.exists(a.data):
         a.synthetic = True
+    if a.experiment in ("fusion", "graph", "null", "ucurve", "buckets", "scaling") and a.epochs < 2:
+        a.epochs = 2          # the first epoch carries start-up, warm-up steps and graph capture; the last one is reported
     fn = {"repeated": cmd_repeated, "buckets": cmd_buckets, "scaling": cmd_scaling, "trajectory": cmd_trajectory,
           "edge": cmd_edge, "matrix": cmd_matrix, "check": cmd_check, "fusion": cmd_fusion, "graph": cmd_graph,
           "null": cmd_null, "lr": cmd_lr, "ucurve": cmd_ucurve, "precision": cmd_precision}[a.experiment]
