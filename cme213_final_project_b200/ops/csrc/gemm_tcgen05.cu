@@ -344,6 +344,21 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
     ep.M = g->M; ep.N = g->N; ep.K = g->K; ep.batch = g->batch;
     ep.tiles_m = tiles_m; ep.tiles_n = tiles_n; ep.splits = splits; ep.kb_per_split = kb_per; ep.num_kb = num_kb;
     ep.a_batched = g->strideA != 0 && g->batch > 1; ep.b_batched = g->strideB != 0 && g->batch > 1;
+    {
+        // Tile order by estimated DRAM traffic.  The CTAs that run together walk K at about the same pace, so the
+        // operand they share is fetched once per wave of tiles from DRAM and served to the others from L2; the
+        // operand they do not share is needed again a wave later and comes from DRAM again unless it stays in L2
+        // (taken as half of its 126 MB).  So the order that shares the operand too large for L2 wins.
+        const int es = tf32 ? 4 : 2;
+        const double a_bytes = (double)g->M * g->K * es, b_bytes = (double)g->N * g->K * es, l2 = 63.0e6;
+        const double slots = pair ? (double)g_max_pairs : (double)g_num_sms;
+        const double waves = (double)tiles_m * tiles_n / slots > 1.0 ? (double)tiles_m * tiles_n / slots : 1.0;
+        const double ra = waves < tiles_n ? waves : tiles_n, rb = waves < tiles_m ? waves : tiles_m;
+        const double m_fast = a_bytes * (a_bytes > l2 ? ra : 1.0) + b_bytes;         // B stripe shared, A rows distinct
+        const double n_fast = b_bytes * (b_bytes > l2 ? rb : 1.0) + a_bytes;         // A rows shared
+        static const char* force = getenv("CME213_GEMM_NFAST");
+        ep.n_fast = force ? (force[0] == '1') : (n_fast < m_fast && tiles_n > 1);
+    }
     ep.status = g_status;
     if (via_ws) {
         ep.C = g->workspace; ep.ldc = g->N; ep.strideC = (long long)g->M * g->N; ep.c_f32 = 1;

@@ -87,6 +87,7 @@ template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
 struct EpiParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, splits, kb_per_split, num_kb;
+    int n_fast;                    // tile order: 0 = consecutive tiles walk down M (share a B stripe), 1 = across N (share A rows)
     int a_batched, b_batched;
     void* C; long long ldc, strideC; int c_f32;
     const __nv_bfloat16* bias;
@@ -100,6 +101,14 @@ struct EpiParams {
     int aux_ring;                  // aux_out leaves through the ring + tmX (else direct 16-byte stores)
     int* status;
 };
+
+// Tile index -> (row block, column block).  Co-running CTAs work on consecutive tiles, so the order decides which operand
+// they share in L2: walking down M they share a stripe of B and every row block of A is fetched once per column block;
+// walking across N they share rows of A.  The launcher picks the order with the smaller DRAM traffic.
+__device__ __forceinline__ void tile_mn(const EpiParams& p, int mn, int& tm, int& tn) {
+    if (p.n_fast) { tn = mn % p.tiles_n; tm = mn / p.tiles_n; }
+    else          { tm = mn % p.tiles_m; tn = mn / p.tiles_m; }
+}
 
 __device__ __forceinline__ void epilogue_chunk(const EpiParams& p, float* acc, long long row_off_c,
                                                long long row_off_res, long long row_off_aux, int n, int ncols,
@@ -398,8 +407,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int tile = tile0; tile < total_tiles && ok; tile += tile_step) {
                 const int mn = tile % tiles_mn, rest = tile / tiles_mn;
                 const int bidx = rest % p.batch, split = rest / p.batch;
-                const int m0 = (mn % p.tiles_m) * BMT + int(cta_rank) * BM;
-                const int n0 = (mn / p.tiles_m) * BN + int(cta_rank) * C::BN_LOCAL;
+                int tm, tn;
+                tile_mn(p, mn, tm, tn);
+                const int m0 = tm * BMT + int(cta_rank) * BM;
+                const int n0 = tn * BN + int(cta_rank) * C::BN_LOCAL;
                 const int kb0 = split * p.kb_per_split;
                 const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
                 const int za = p.a_batched ? bidx : 0, zb = p.b_batched ? bidx : 0;
@@ -535,10 +546,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int f_tile = tile0, f_c = eset;
         uint32_t f_cnt = 0;
         auto fetch_next = [&]() {
-            int fmn = 0, fn0 = 0;
+            int fmn = 0, fn0 = 0, fm_blk = 0;
             while (f_tile < total_tiles) {              // next tile that has a chunk for this warp set
                 fmn = f_tile % tiles_mn;
-                fn0 = (fmn / p.tiles_m) * BN;
+                int ftm, ftn;
+                tile_mn(p, fmn, ftm, ftn);
+                fn0 = ftn * BN;
+                fm_blk = ftm;
                 int nchf = (p.N - fn0 + 63) / 64;
                 nchf = nchf < BN / 64 ? nchf : BN / 64;
                 if (f_c < nchf) break;
@@ -547,7 +561,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             if (f_tile >= total_tiles) return;
             const int fb = (f_tile / tiles_mn) % p.batch;
-            const int fm0 = (fmn % p.tiles_m) * BMT + int(cta_rank) * BM + quarter * 32;
+            const int fm0 = fm_blk * BMT + int(cta_rank) * BM + quarter * 32;
             if (lane == 0) {
                 const uint32_t b = f_cnt % C::NB;
                 mbar_arrive_expect_tx(&my_in_bar[b], 4096);
@@ -562,7 +576,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const bool stage_bias = !SIMPLE && ring_epi && S::bias(p);
         auto bias_fetch = [&](int t) {                  // this lane's 8 bias values of tile t (zeros past N)
             float b8[8];
-            const int tn0 = ((t % tiles_mn) / p.tiles_m) * BN;
+            int btm, btn;
+            tile_mn(p, t % tiles_mn, btm, btn);
+            const int tn0 = btn * BN;
             load8_guard(p.bias, tn0 + lane * 8, p.N, true, b8);
             return pack8(b8);
         };
@@ -573,7 +589,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int tile = tile0; tile < total_tiles && ok; tile += tile_step, ++it) {
             const int mn = tile % tiles_mn, rest = tile / tiles_mn;
             const int bidx = rest % p.batch, split = rest / p.batch;
-            const int m0 = (mn % p.tiles_m) * BMT + int(cta_rank) * BM, n0 = (mn / p.tiles_m) * BN;
+            int etm, etn;
+            tile_mn(p, mn, etm, etn);
+            const int m0 = etm * BMT + int(cta_rank) * BM, n0 = etn * BN;
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             const __nv_bfloat16* bias_s = bias_w + (it % 3) * 256;
