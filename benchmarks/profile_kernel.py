@@ -100,12 +100,55 @@ def summarize(rep, out, kernel, cmd, flops, nbytes):
     return res
 
 
+def summarize_light(rep, out, kernel, cmd, flops, nbytes):
+    """One row per distinct kernel name: launches seen, mean duration, DRAM / L2 / SM throughput of the first one."""
+    r = subprocess.run(["ncu", "-i", rep, "--page", "raw", "--csv"], capture_output=True, text=True)
+    rows = list(csv.reader(io.StringIO(r.stdout)))
+    if len(rows) < 3:
+        return None
+    head = rows[0]
+    col = {n: i for i, n in enumerate(head)}
+    want = ["gpu__time_duration.sum", "gpu__dram_throughput.avg.pct_of_peak_sustained_elapsed",
+            "lts__throughput.avg.pct_of_peak_sustained_elapsed", "sm__throughput.avg.pct_of_peak_sustained_elapsed",
+            "launch__grid_size", "launch__block_size", "launch__registers_per_thread"]
+    unit = {n: rows[1][col[n]] for n in want if n in col}
+    agg = {}
+    for row in rows[2:]:
+        name = row[col["Kernel Name"]].split("(")[0][:70]
+        rec = agg.setdefault(name, {"n": 0, "dur": 0.0, "first": None})
+        try:
+            d = float(row[col["gpu__time_duration.sum"]].replace(",", ""))
+        except (KeyError, ValueError):
+            d = float("nan")
+        d *= {"ns": 1e-3, "nsecond": 1e-3, "us": 1.0, "usecond": 1.0, "ms": 1e3, "msecond": 1e3}.get(unit.get("gpu__time_duration.sum", "us"), 1.0)
+        rec["n"] += 1
+        rec["dur"] += d
+        if rec["first"] is None:
+            rec["first"] = {n: row[col[n]] for n in want if n in col}
+    lines = [f"# Kernels matching `{kernel}`: Nsight Compute SpeedOfLight summary", "",
+             "Command (one GPU, small case; the same command had exited 0 without the profiler):", "", "    " + " ".join(cmd), "",
+             "| kernel | launches | mean us | DRAM % of peak | L2 % | SM % | grid | block | regs |", "|---|---|---|---|---|---|---|---|---|"]
+    res = {"kernel": kernel, "kernels": {}}
+    for name, rec in agg.items():
+        f = rec["first"] or {}
+        g = lambda k: f.get(k, "")
+        lines.append(f"| `{name}` | {rec['n']} | {rec['dur'] / rec['n']:.1f} | {g(want[1])} | {g(want[2])} | {g(want[3])} | "
+                     f"{g(want[4])} | {g(want[5])} | {g(want[6])} |")
+        res["kernels"][name] = {"launches": rec["n"], "mean_us": rec["dur"] / rec["n"], **f}
+    open(out + ".md", "w").write("\n".join(lines) + "\n")
+    json.dump(res, open(out + ".json", "w"), indent=1)
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", required=True, help="regular expression matched against kernel names")
     ap.add_argument("--skip", type=int, default=0, help="matching launches to skip first (warm-up)")
     ap.add_argument("--count", type=int, default=1, help="launches to capture (1-3)")
     ap.add_argument("--full", action="store_true", help="--set full (about 40 passes per launch) instead of four sections")
+    ap.add_argument("--light", action="store_true",
+                    help="many short kernels of a small case: the SpeedOfLight section only, up to 80 launches, one "
+                         "table row per distinct kernel name")
     ap.add_argument("--flops", type=float, default=0, help="algorithmic FLOPs of one launch, for the roofline line")
     ap.add_argument("--bytes", type=float, default=0, help="algorithmic bytes of one launch")
     ap.add_argument("--out", required=True)
@@ -114,7 +157,7 @@ def main():
     cmd = [c for c in a.cmd if c != "--"]
     if not cmd:
         ap.error("give the command after --")
-    a.count = max(1, min(a.count, 3))
+    a.count = max(1, min(a.count, 80 if a.light else 3))
     os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
     t0 = time.time()
     plain = subprocess.run(cmd, capture_output=True, text=True)
@@ -127,9 +170,9 @@ def main():
     if shutil.which("ncu") is None:
         why = "ncu is not installed"
     else:
-        sel = ["--set", "full"] if a.full else ["--section", "SpeedOfLight", "--section", "MemoryWorkloadAnalysis",
-                                                "--section", "LaunchStats", "--section", "Occupancy",
-                                                "--section", "ComputeWorkloadAnalysis"]
+        sel = ["--set", "full"] if a.full else ["--section", "SpeedOfLight", "--section", "LaunchStats"] if a.light else \
+              ["--section", "SpeedOfLight", "--section", "MemoryWorkloadAnalysis", "--section", "LaunchStats",
+               "--section", "Occupancy", "--section", "ComputeWorkloadAnalysis"]
         ncu = ["ncu", "--clock-control", "none", "-k", "regex:" + a.kernel, "-s", str(a.skip), "-c", str(a.count),
                *sel, "-f", "-o", a.out] + cmd
         t1 = time.time()
@@ -140,7 +183,7 @@ def main():
             why = f"ncu exited {r.returncode}: " + (r.stdout + r.stderr).strip().splitlines()[-1][:160] if (r.stdout + r.stderr).strip() else "no output"
         else:
             print(f"[profile] captured in {time.time() - t1:.1f} s")
-            res = summarize(a.out + ".ncu-rep", a.out, a.kernel, ncu, a.flops, a.bytes)
+            res = (summarize_light if a.light else summarize)(a.out + ".ncu-rep", a.out, a.kernel, ncu, a.flops, a.bytes)
             if res is None:
                 why = "the report holds no matching launch"
     if why:

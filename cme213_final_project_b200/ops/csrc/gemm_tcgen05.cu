@@ -358,6 +358,10 @@ int gemm_tcgen05_launch(const CmeGemm* g, cudaStream_t stream) {
         const double n_fast = b_bytes * (b_bytes > l2 ? rb : 1.0) + a_bytes;         // A rows shared
         static const char* force = getenv("CME213_GEMM_NFAST");
         ep.n_fast = force ? (force[0] == '1') : (n_fast < m_fast && tiles_n > 1);
+        // the stored derivative is written once by forward and read once by backward, a layer's worth of other work
+        // apart: keep it from displacing what the neighbouring kernels re-read (CME213_GEMM_STREAM_AUX=0: off)
+        static const bool stream_aux = !(getenv("CME213_GEMM_STREAM_AUX") && getenv("CME213_GEMM_STREAM_AUX")[0] == '0');
+        ep.stream_aux = (stream_aux && g->aux_deriv && (g->act == CME_ACT_GELU || g->dact == CME_ACT_GELU)) ? 1 : 0;
     }
     ep.status = g_status;
     if (via_ws) {

@@ -87,6 +87,8 @@ template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
 struct EpiParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, splits, kb_per_split, num_kb;
+    int stream_aux;                // the auxiliary tensors (activation derivative written by forward, read once by backward)
+                                   // go through L2 with the evict-first policy
     int n_fast;                    // tile order: 0 = consecutive tiles walk down M (share a B stripe), 1 = across N (share A rows)
     int a_batched, b_batched;
     void* C; long long ldc, strideC; int c_f32;
@@ -565,7 +567,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (lane == 0) {
                 const uint32_t b = f_cnt % C::NB;
                 mbar_arrive_expect_tx(&my_in_bar[b], 4096);
-                tma_load_3d(ring + b * 4096, &tmI, &my_in_bar[b], fn0 + f_c * 64, fm0, fb);
+                if (p.stream_aux && in_kind == 1)
+                    tma_load_3d_hint(ring + b * 4096, &tmI, &my_in_bar[b], fn0 + f_c * 64, fm0, fb, l2_policy_evict_first());
+                else
+                    tma_load_3d(ring + b * 4096, &tmI, &my_in_bar[b], fn0 + f_c * 64, fm0, fb);
             }
             ++f_cnt;
             f_c += ESETS;
@@ -761,7 +766,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) {
                         tma_store_3d(&tmC, sbC, n, m0 + quarter * 32, (int)zoff);
-                        if (aux_ring) tma_store_3d(&tmX, sbX, n, m0 + quarter * 32, bidx);
+                        if (aux_ring) {
+                            if (p.stream_aux) tma_store_3d_hint(&tmX, sbX, n, m0 + quarter * 32, bidx, l2_policy_evict_first());
+                            else tma_store_3d(&tmX, sbX, n, m0 + quarter * 32, bidx);
+                        }
                         tma_store_commit();
                     }
                     if (S::colsum(p)) {
