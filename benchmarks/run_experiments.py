@@ -170,10 +170,14 @@ def cmd_trajectory(a):
     res = {name: compare_trajectories(traj["blocking"], t) for name, t in traj.items() if name != "blocking"}
     spans = {name: max([max(abs(s["sum_span"]), abs(s["sumsq_span"]), abs(s["maxabs_span"])) for s in t] or [float("nan")])
              for name, t in traj.items()}
-    rows = [[name, len(traj[name]), res[name]["ok"] if name in res else True, spans[name]] for name in modes]
+    g = lambda name, key: res[name][key] if name in res else 0.0
+    rows = [[name, len(traj[name]), res[name]["ok"] if name in res else True,
+             res[name]["identical_path"] if name in res else True, g(name, "max_loss_diff"),
+             g(name, "max_rel_sumsq_diff"), g(name, "max_rel_sum_diff"), spans[name]] for name in modes]
     save(a, f"trajectory_{a.preset}_g{a.gpus[0]}",
          {"comparisons": res, "cross_rank_span": spans, "all_ok": all(r["ok"] for r in res.values())},
-         (["mode", "steps", "within tolerance of blocking", "largest cross-rank span"], rows))
+         (["mode", "steps", "within tolerance of blocking", "same sums as blocking", "max loss diff",
+           "max rel diff of sum of squares", "max rel diff of sum", "largest cross-rank span"], rows))
 
 
 def cmd_edge(a):
@@ -274,7 +278,9 @@ def cmd_ucurve(a):
     fits = None
     if a.fits and os.path.exists(a.fits):
         f = json.load(open(a.fits)).get("fits", {})
-        fits = f.get("nvls") or f.get("two_shot")
+        fits = f.get("nvls") if (a.gpus[0] > 2 and f.get("nvls")) else f.get("two_shot")
+    elif a.fits:
+        print(f"[ucurve] fit file {a.fits} not found: no prediction column")
     rows = []
     for kb in a.bucket_kb:
         r, out = _one(a, f"bucket_kb={kb}", ["--sync-mode", "overlap", "--bucket-kb", str(kb), "--comm-backend", "fused"]
