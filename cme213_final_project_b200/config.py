@@ -115,6 +115,8 @@ class RunConfig:
     log_every: int = 100
     step_timeout_s: float = 0.0    # > 0: end the process if no step completes for this long (host watchdog)
     epilogue_fusion: bool = True   # False: bias / activation / residual as separate kernels (ablation)
+    ffn_precision: str = "full"    # fp32 storage only: full | store (feed-forward activation kept at bf16 precision)
+                                   # | bf16 (feed-forward products on bf16 copies of their operands, fp32 results)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -233,6 +235,11 @@ def validate_run(model: ModelConfig, run: RunConfig, world_size: int) -> List[st
         errs.append("--bucket-kb must be >= 0")
     if run.compute_dtype not in ("bf16", "tf32", "fp32"):
         errs.append(f"unknown compute dtype '{run.compute_dtype}'")
+    if run.ffn_precision not in ("full", "store", "bf16"):
+        errs.append(f"unknown feed-forward precision '{run.ffn_precision}'")
+    elif run.ffn_precision != "full" and run.compute_dtype == "bf16":
+        errs.append("--ffn-precision store|bf16 applies to fp32 storage (--compute-dtype tf32 or fp32); "
+                    "bf16 storage already runs the feed-forward products in bf16")
     if run.gemm_backend not in ("auto", "tcgen05", "simt"):
         errs.append(f"unknown gemm backend '{run.gemm_backend}'")
     if run.comm_algo not in ("auto", "one_shot", "two_shot", "nvls"):
@@ -258,6 +265,14 @@ def apply_environment(run: RunConfig, env: Optional[Dict[str, str]] = None) -> R
         run.epilogue_fusion = False
     if env_enabled("CME213_STRICT_FP32", e):
         run.compute_dtype = "fp32"
+    # the reference's reduced-precision feed-forward experiments act on its fp32 storage
+    # (FINAL_CLEAN_CODE_/src/model/transformer.cu:37-45); here they select fp32 storage with tf32 products unless
+    # strict fp32 was asked for, and 16-bit means bf16
+    for name, mode in (("CME213_FP16_STORAGE_ONLY", "store"), ("CME213_FFN_FP16", "bf16")):
+        if env_enabled(name, e):
+            run.ffn_precision = mode
+            if run.compute_dtype == "bf16":
+                run.compute_dtype = "tf32"
     b = e.get("CME213_GEMM_BACKEND")
     if b:
         run.gemm_backend = GEMM_BACKEND_MAP.get(b, b) if b != "auto" else "auto"
@@ -310,6 +325,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--log-every", type=int, default=100)
     p.add_argument("--step-timeout", type=float, default=0.0,
                    help="seconds without a completed step after which the process ends itself (0 = off)")
+    p.add_argument("--ffn-precision", default="full",
+                   help="fp32 storage: full | store (activation kept at bf16 precision) | bf16 (bf16 operand copies)")
     p.add_argument("--no-epilogue-fusion", action="store_true",
                    help="run bias / activation / residual / activation-derivative as separate kernels (ablation)")
     return p
@@ -337,7 +354,8 @@ def parse_args(argv: Optional[Sequence[str]] = None) -> Tuple[ModelConfig, Optim
                     compute_dtype=a.compute_dtype, synthetic=a.synthetic, seed=a.seed,
                     save_checkpoint=a.save_checkpoint, load_checkpoint=a.load_checkpoint, profile=a.profile,
                     device=a.device, engine=a.engine, log_every=a.log_every,
-                    epilogue_fusion=not a.no_epilogue_fusion, step_timeout_s=a.step_timeout)
+                    epilogue_fusion=not a.no_epilogue_fusion, step_timeout_s=a.step_timeout,
+                    ffn_precision=a.ffn_precision)
     return model, optim, apply_environment(run)
 
 

@@ -23,7 +23,7 @@ from ..config import ModelConfig, OptimConfig, RunConfig
 
 class _EngineDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("V", "T", "D", "H", "FF", "L", "B", "act", "causal", "head_flat", "tied",
-                                             "final_ln", "fused_qkv", "allow_tf32", "fuse_epilogues")] + \
+                                             "final_ln", "fused_qkv", "allow_tf32", "fuse_epilogues", "ffn_lowp")] + \
                [("ln_eps", ctypes.c_float), ("prob_eps", ctypes.c_float)] + \
                [(n, ctypes.c_int) for n in ("dtype", "gemm_backend", "attn_backend")]
 
@@ -98,6 +98,7 @@ class NativeEngine:
                         head_flat=int(cfg.head_layout == "flat"), tied=int(cfg.tied_embeddings),
                         final_ln=int(cfg.final_layernorm), fused_qkv=int(cfg.mode == "gpt"),
                         allow_tf32=int(self.tf32), fuse_epilogues=int(run.epilogue_fusion and not self.tf32),
+                        ffn_lowp={"full": 0, "store": 1, "bf16": 2}[run.ffn_precision] if self.strict else 0,
                         ln_eps=cfg.ln_eps,
                         prob_eps=1e-9 if cfg.mode == "parity" else 0.0, dtype=ops.F32 if self.strict else ops.BF16,
                         gemm_backend=gemm_backend if (self.tf32 or not self.strict) else 2,

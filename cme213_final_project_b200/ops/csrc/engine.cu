@@ -40,6 +40,7 @@ int cme_cross_entropy(int, const void*, const int*, void*, float*, float*, int, 
 int cme_attention_fwd(const CmeAttn*, int, void*);
 int cme_attention_bwd(const CmeAttn*, int, void*);
 int cme_gemm(const CmeGemm*, int, void*);
+int cme_cast(int, const void*, int, void*, long long, void*);
 }
 
 struct CmeEngineDesc {
@@ -49,6 +50,9 @@ struct CmeEngineDesc {
     int allow_tf32;      // fp32 storage: plain products may run on the tensor cores with tf32 inputs
     int fuse_epilogues;  // 0: bias / activation / residual adds and the activation derivative run as separate kernels
                          // after plain products (the ablation the reference measures with CME213_LT_FUSION)
+    int ffn_lowp;        // fp32 storage only.  1: the feed-forward activation is rounded to bf16 where it is stored (the
+                         // reference's CME213_FP16_STORAGE_ONLY experiment); 2: the four feed-forward products of a
+                         // layer take bf16 copies of their operands and give fp32 results (its CME213_FFN_FP16)
     float ln_eps, prob_eps;
     int dtype;           // CME_BF16 | CME_F32
     int gemm_backend;    // 0 auto, 1 tcgen05, 2 simt
@@ -96,6 +100,7 @@ struct Engine {
     void* gemm_ws_side; long long gemm_ws_side_bytes;     // split-K partials of the products on the second stream
     float* col_scratch_side;
     float* slab_scratch;                                   // [ceil(BT / 32)][FF] column sums left by a GEMM epilogue
+    char *lp_x = nullptr, *lp_h = nullptr, *lp_w = nullptr;  // bf16 copies for ffn_lowp: [BT, D], [BT, FF], [D, FF]
     // second stream for the weight-gradient work (null: everything on the caller's stream)
     cudaStream_t side = nullptr;
     std::vector<cudaEvent_t> ev;                           // [L + 1][8]: four "inputs ready" + four "done" per layer
@@ -164,6 +169,11 @@ size_t carve(Engine& e, char* base) {
     e.slab_scratch = (float*)take((size_t)((BT + 31) / 32) * widest * 4);
     e.col_scratch_side = (float*)take((size_t)(cme_colsum_splits((int)BT, (int)D) + cme_colsum_splits((int)BT, (int)FF)) *
                                       widest * 4);
+    if (d.ffn_lowp) {
+        e.lp_x = take(BT * D * 2);
+        e.lp_h = take(BT * FF * 2);
+        e.lp_w = take(D * FF * 2);
+    }
     return off;
 }
 
@@ -187,6 +197,21 @@ int gemm(const Engine& e, cudaStream_t st, int M, int N, int K, const void* A, l
     g.workspace_bytes = on_side ? e.gemm_ws_side_bytes : e.gemm_ws_bytes;
     return cme_gemm(&g, e.d.gemm_backend, st);
 }
+
+// A plain product of bf16 operands with an fp32 result (the reduced-precision feed-forward experiment).
+int gemm_lp(const Engine& e, cudaStream_t st, int M, int N, int K, const void* A, long long lda, int a_trans,
+            const void* B, long long ldb, int b_trans, void* C, long long ldc, int accumulate = 0) {
+    CmeGemm g{};
+    g.M = M; g.N = N; g.K = K; g.batch = 1;
+    g.A = A; g.lda = lda; g.a_trans = a_trans;
+    g.B = B; g.ldb = ldb; g.b_trans = b_trans;
+    g.C = C; g.ldc = ldc; g.c_dtype = CME_F32; g.ab_dtype = CME_BF16;
+    g.accumulate = accumulate;
+    g.workspace = e.gemm_ws; g.workspace_bytes = e.gemm_ws_bytes;
+    return cme_gemm(&g, 0, st);
+}
+
+int to_bf16(const void* x, void* y, long long n, cudaStream_t st) { return cme_cast(CME_F32, x, CME_BF16, y, n, st); }
 
 // CME213_DETERMINISTIC=1: the attention backward adds the key blocks' parts of dQ in a fixed order (bit-reproducible
 // gradients, about 0.07 ms per layer slower at GPT-2 small shapes); default: unordered reduce-adds.
@@ -235,6 +260,8 @@ CME_API int cme_engine_create(const CmeEngineDesc* desc, const CmeLayerSlots* la
     CME_REQUIRE(desc->L >= 1 && desc->D % desc->H == 0, CME_ERR_SHAPE, "engine: bad model shape");
     CME_REQUIRE(!(desc->fused_qkv && desc->head_flat), CME_ERR_SHAPE, "engine: fused QKV needs split heads");
     CME_REQUIRE(!desc->head_flat || desc->T % desc->H == 0, CME_ERR_SHAPE, "engine: flat heads need T %% H == 0");
+    CME_REQUIRE(desc->ffn_lowp >= 0 && desc->ffn_lowp <= 2 && (!desc->ffn_lowp || desc->dtype == CME_F32), CME_ERR_SHAPE,
+                "engine: the reduced-precision feed-forward modes need fp32 storage");
     Engine* e = new (std::nothrow) Engine();
     CME_REQUIRE(e != nullptr, CME_ERR_CUDA, "engine: out of host memory");
     e->d = *desc;
@@ -351,7 +378,18 @@ CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, f
         TRY(cme_layernorm_fwd(dt, a.xmid, nullptr, nullptr, e.P(s.ln2g), e.P(s.ln2b), a.ln2, a.mean2, a.rstd2, BT, D,
                               d.ln_eps, st));
         // ff_act = act(ln2 @ W1 + b1)   (GELU also keeps GELU'(pre-activation), from the same tanh, for backward)
-        if (fused) {
+        if (d.ffn_lowp == 2) {
+            // bf16 copies of the operands, fp32 products, fp32 element-wise work
+            // (FINAL_CLEAN_CODE_/src/model/transformer.cu:297-306)
+            TRY(to_bf16(a.ln2, e.lp_x, (long long)BT * D, st));
+            TRY(to_bf16(e.P(s.W1), e.lp_w, (long long)D * FF, st));
+            TRY(gemm_lp(e, st, BT, FF, D, e.lp_x, D, 0, e.lp_w, FF, 0, a.ffact, FF));
+            TRY(cme_bias_act_residual(dt, a.ffact, e.P(s.b1), nullptr, a.ffpre, a.ffact, BT, FF, d.act, st));
+            TRY(to_bf16(a.ffact, e.lp_h, (long long)BT * FF, st));
+            TRY(to_bf16(e.P(s.W2), e.lp_w, (long long)D * FF, st));
+            TRY(gemm_lp(e, st, BT, D, FF, e.lp_h, FF, 0, e.lp_w, D, 0, e.x[l + 1], D));
+            TRY(cme_bias_act_residual(dt, e.x[l + 1], e.P(s.b2), a.xmid, nullptr, e.x[l + 1], BT, D, 0, st));
+        } else if (fused && d.ffn_lowp == 0) {
             TRY(gemm(e, st, BT, FF, D, a.ln2, D, 0, e.P(s.W1), FF, 0, a.ffact, FF, 0, e.P(s.b1), d.act, a.ffpre, 0,
                      nullptr, FF, nullptr, 0, 1, 0, 0, 0, /*aux_deriv=*/ffn_deriv() ? 1 : 0));
             // x_next = x_mid + ff_act @ W2 + b2
@@ -362,6 +400,12 @@ CME_API int cme_engine_forward(void* h, const int* tokens, const int* targets, f
             // pre-activation), and bias + residual add (FINAL_CLEAN_CODE_/src/model/transformer.cu:387-399)
             TRY(gemm(e, st, BT, FF, D, a.ln2, D, 0, e.P(s.W1), FF, 0, a.ffact, FF));
             TRY(cme_bias_act_residual(dt, a.ffact, e.P(s.b1), nullptr, a.ffpre, a.ffact, BT, FF, d.act, st));
+            if (d.ffn_lowp == 1) {
+                // the stored activation keeps bf16 precision: what the second product and backward read is the
+                // rounded value (FINAL_CLEAN_CODE_/src/model/transformer.cu:317-320)
+                TRY(to_bf16(a.ffact, e.lp_h, (long long)BT * FF, st));
+                TRY(cme_cast(CME_BF16, e.lp_h, CME_F32, a.ffact, (long long)BT * FF, st));
+            }
             TRY(gemm(e, st, BT, D, FF, a.ffact, FF, 0, e.P(s.W2), D, 0, e.x[l + 1], D));
             TRY(cme_bias_act_residual(dt, e.x[l + 1], e.P(s.b2), a.xmid, nullptr, e.x[l + 1], BT, D, 0, st));
         }
@@ -454,34 +498,57 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         // a.ffpre holds GELU'(pre-activation); relu'(pre) == (act > 0).  The product's epilogue also sums d ff_pre
         // over rows (the gradient of b1) when the kernel that runs can; the sums are finished on the side stream.
         const void* aux = d.act == CME_ACT_GELU ? a.ffpre : a.ffact;
-        const bool fused = d.fuse_epilogues != 0;
+        const bool fused = d.fuse_epilogues != 0 && d.ffn_lowp == 0;
         const bool deriv = fused && ffn_deriv();
         int slabs = 0;
         TRY(ready(l, 0));                                                   // dx exists
         if (below_top) TRY(need(l + 1, 1));                                 // dff is still read by the layer above's dW1
         bool db1_done = false;
-        if (fused) {
-            TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF, 0, nullptr, 0, nullptr, d.act, aux, FF, nullptr,
-                     0, 1, 0, 0, 0, /*aux_deriv=*/deriv ? 1 : 0, deriv ? e.slab_scratch : nullptr, &slabs));
-        } else {
-            // plain product, then the derivative and the bias gradient in one element-wise pass (the reference's
-            // fused_relu_backward_bias_backward_kernel, FINAL_CLEAN_CODE_/src/kernels/activations.cu:247-283)
-            TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF));
+        if (d.ffn_lowp == 2) {
+            // the four feed-forward gradient products on bf16 copies, all on the caller's stream (the copies are
+            // shared temporaries); FINAL_CLEAN_CODE_/src/model/transformer.cu:468-489
+            TRY(to_bf16(dx, e.lp_x, (long long)BT * D, st));
+            TRY(to_bf16(e.P(s.W2), e.lp_w, (long long)D * FF, st));
+            TRY(gemm_lp(e, st, BT, FF, D, e.lp_x, D, 0, e.lp_w, D, 1, e.dff, FF));
             TRY(cme_dact_colsum(dt, e.dff, aux, e.dff, e.G(s.b1), e.col_scratch, BT, FF, d.act, accumulate, st));
-            db1_done = true;
+            TRY(to_bf16(a.ffact, e.lp_h, (long long)BT * FF, st));
+            TRY(gemm_lp(e, st, FF, D, BT, e.lp_h, FF, 1, e.lp_x, D, 0, e.G(s.W2), D, accumulate));
+            TRY(cme_dact_colsum(dt, dx, nullptr, nullptr, e.G(s.b2), e.col_scratch, BT, D, 0, accumulate, st));
+            TRY(ready(l, 0));
+            TRY(done(l, 0));
+            emit();
+            TRY(to_bf16(e.dff, e.lp_h, (long long)BT * FF, st));
+            TRY(to_bf16(e.P(s.W1), e.lp_w, (long long)D * FF, st));
+            TRY(gemm_lp(e, st, BT, D, FF, e.lp_h, FF, 0, e.lp_w, FF, 1, e.dln, D));
+            TRY(to_bf16(a.ln2, e.lp_x, (long long)BT * D, st));
+            TRY(gemm_lp(e, st, D, FF, BT, e.lp_x, D, 1, e.lp_h, FF, 0, e.G(s.W1), FF, accumulate));
+            TRY(ready(l, 1));
+            TRY(done(l, 1));
+            emit();
+        } else {
+            if (fused) {
+                TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF, 0, nullptr, 0, nullptr, d.act, aux, FF, nullptr,
+                         0, 1, 0, 0, 0, /*aux_deriv=*/deriv ? 1 : 0, deriv ? e.slab_scratch : nullptr, &slabs));
+            } else {
+                // plain product, then the derivative and the bias gradient in one element-wise pass (the reference's
+                // fused_relu_backward_bias_backward_kernel, FINAL_CLEAN_CODE_/src/kernels/activations.cu:247-283)
+                TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF));
+                TRY(cme_dact_colsum(dt, e.dff, aux, e.dff, e.G(s.b1), e.col_scratch, BT, FF, d.act, accumulate, st));
+                db1_done = true;
+            }
+            TRY(gemm(e, ws, FF, D, BT, a.ffact, FF, 1, dx, D, 0, e.G(s.W2), D, accumulate));
+            TRY(cme_dact_colsum(dt, dx, nullptr, nullptr, e.G(s.b2), col_s, BT, D, 0, accumulate, ws));
+            TRY(done(l, 0));
+            emit();
+            // ---- FFN1:  ff_pre = ln2 @ W1 + b1   (e.dff now holds d ff_pre)
+            TRY(ready(l, 1));                                                   // dff exists
+            TRY(gemm(e, st, BT, D, FF, e.dff, FF, 0, e.P(s.W1), FF, 1, e.dln, D));
+            TRY(gemm(e, ws, D, FF, BT, a.ln2, D, 1, e.dff, FF, 0, e.G(s.W1), FF, accumulate));
+            if (slabs) TRY(cme_colsum_slabs_finalize(dt, e.slab_scratch, slabs, FF, e.G(s.b1), accumulate, ws));
+            else if (!db1_done) TRY(cme_dact_colsum(dt, e.dff, nullptr, nullptr, e.G(s.b1), col_s, BT, FF, 0, accumulate, ws));
+            TRY(done(l, 1));
+            emit();
         }
-        TRY(gemm(e, ws, FF, D, BT, a.ffact, FF, 1, dx, D, 0, e.G(s.W2), D, accumulate));
-        TRY(cme_dact_colsum(dt, dx, nullptr, nullptr, e.G(s.b2), col_s, BT, D, 0, accumulate, ws));
-        TRY(done(l, 0));
-        emit();
-        // ---- FFN1:  ff_pre = ln2 @ W1 + b1   (e.dff now holds d ff_pre)
-        TRY(ready(l, 1));                                                   // dff exists
-        TRY(gemm(e, st, BT, D, FF, e.dff, FF, 0, e.P(s.W1), FF, 1, e.dln, D));
-        TRY(gemm(e, ws, D, FF, BT, a.ln2, D, 1, e.dff, FF, 0, e.G(s.W1), FF, accumulate));
-        if (slabs) TRY(cme_colsum_slabs_finalize(dt, e.slab_scratch, slabs, FF, e.G(s.b1), accumulate, ws));
-        else if (!db1_done) TRY(cme_dact_colsum(dt, e.dff, nullptr, nullptr, e.G(s.b1), col_s, BT, FF, 0, accumulate, ws));
-        TRY(done(l, 1));
-        emit();
         // ---- LN2 (+ residual gradient): d x_mid = LN'(d ln2) + dx
         if (below_top) TRY(need(l + 1, 2));                                 // dx_other is read by the layer above's dWo
         TRY(cme_layernorm_bwd(dt, e.dln, a.xmid, e.P(s.ln2g), a.mean2, a.rstd2, dx, dx_other, e.G(s.ln2g), e.G(s.ln2b),

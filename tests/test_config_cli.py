@@ -53,6 +53,14 @@ def test_environment_rules():
     run = C.apply_environment(C.RunConfig(), {"CME213_USE_CUDA_GRAPH": "1", "CME213_GEMM_BACKEND": "custom",
                                               "CME213_DEFER_GRAD_AVG_TO_ADAM": "1"})
     assert run.cuda_graph and run.gemm_backend == "simt" and run.defer_grad_avg
+    # the reduced-precision feed-forward experiments act on fp32 storage
+    run = C.apply_environment(C.RunConfig(), {"CME213_FFN_FP16": "1"})
+    assert run.ffn_precision == "bf16" and run.compute_dtype == "tf32"
+    run = C.apply_environment(C.RunConfig(), {"CME213_FP16_STORAGE_ONLY": "1", "CME213_STRICT_FP32": "1"})
+    assert run.ffn_precision == "store" and run.compute_dtype == "fp32"
+    m, _ = C.preset("parity-h128")
+    assert any("ffn-precision" in e for e in C.validate_run(m, C.RunConfig(ffn_precision="bf16"), 1))
+    assert not C.validate_run(m, C.RunConfig(ffn_precision="bf16", compute_dtype="tf32"), 1)
 
 
 def _run(args, env=None):

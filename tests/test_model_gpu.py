@@ -276,6 +276,48 @@ def test_tf32_engine_tracks_oracle(preset_name):
     assert ops.gemm_check_status() == 0
 
 
+@pytest.mark.parametrize("base", ["fp32", "tf32"])
+@pytest.mark.parametrize("mode", ["store", "bf16"])
+@pytest.mark.parametrize("preset_name", ["parity-h128", "tiny-gpt"])
+def test_reduced_precision_feed_forward_modes(preset_name, mode, base):
+    """fp32 storage with the feed-forward part at reduced precision (the reference's CME213_FP16_STORAGE_ONLY and
+    CME213_FFN_FP16 experiments, FINAL_CLEAN_CODE_/src/model/transformer.cu:297-324,468-489, with bf16 as the 16-bit
+    type): ``store`` rounds the stored activation to bf16, ``bf16`` runs the four feed-forward products of a block
+    on bf16 copies of their operands.  Both stay close to the float64 oracle, differ from the full-precision engine
+    (the switch does something) by no more than rounding, and train."""
+    from cme213_final_project_b200 import ops
+    from cme213_final_project_b200.config import RunConfig, preset
+    from cme213_final_project_b200.models.engine import NativeEngine
+    from cme213_final_project_b200.models.reference import ReferenceModel
+    cfg, optim = preset(preset_name)
+    eng = NativeEngine(cfg, optim, RunConfig(compute_dtype=base, ffn_precision=mode), device="cuda", seed=42)
+    full = NativeEngine(cfg, optim, RunConfig(compute_dtype=base), device="cuda", seed=42)
+    ref = ReferenceModel(cfg, optim, device="cpu", dtype=torch.float64, seed=42, layout=eng.layout)
+    with torch.no_grad():
+        ref.params.copy_(eng.master.cpu().double())
+    x, y = _tokens(cfg)
+    loss_ref = ref.forward(x, y)
+    for m in (eng, full):
+        m.train_step([x.cuda()], [y.cuda()])
+    torch.cuda.synchronize()
+    assert ops.gemm_check_status() == 0
+    assert abs(eng.read_loss() - loss_ref.item()) < 5e-3
+    ref.zero_grad()
+    ref.backward()
+    g, gf = eng.grads.cpu().double(), full.grads.cpu().double()
+    assert torch.isfinite(g).all()
+    assert _cos(g, ref.grads) > 0.97
+    assert not torch.equal(g, gf)                        # the mode changes the arithmetic ...
+    assert _cos(g, gf) > 0.97                            # ... by rounding, not by more
+    # ten optimizer steps on one batch: the loss falls and follows the full-precision engine
+    for _ in range(10):
+        for m in (eng, full):
+            m.train_step([x.cuda()], [y.cuda()])
+            m.update()
+    torch.cuda.synchronize()
+    assert eng.read_loss() < loss_ref.item() and abs(eng.read_loss() - full.read_loss()) < 3e-2
+
+
 def test_engine_at_gpt2_small_width_tracks_the_oracle():
     """The production kernels at the width of the headline model -- CTA-pair GEMM tiles with their fused epilogues,
     the tensor-core attention at 12 heads x 1024 tokens x head size 64, the register-resident cross-entropy at a
