@@ -30,6 +30,7 @@ Every experiment leaves one JSON file and one markdown table under --out.
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import time
@@ -162,22 +163,28 @@ def cmd_trajectory(a):
              "deferred": ["--sync-mode", "blocking", "--defer-grad-avg"] + nccl,
              "fused": ["--sync-mode", "overlap", "--bucket-kb", "256", "--comm-backend", "fused"],
              "fused_graph": ["--sync-mode", "overlap", "--bucket-kb", "256", "--comm-backend", "fused", "--cuda-graph"]}
-    traj = {}
+    traj, n_params = {}, 0
     for name, flags in modes.items():
         out, rc, _ = run(a.gpus[0], base_args(a) + ["--trace-trajectory"] + flags + a.extra)
         traj[name] = parse_trajectory(out)
+        m = re.search(r"^Parameters: (\d+)", out, re.M)
+        n_params = int(m.group(1)) if m else n_params
         print(f"[trajectory] {name}: {len(traj[name])} steps rc={rc}")
-    res = {name: compare_trajectories(traj["blocking"], t) for name, t in traj.items() if name != "blocking"}
+    res = {name: compare_trajectories(traj["blocking"], t, n_params=n_params) for name, t in traj.items()
+           if name != "blocking"}
     spans = {name: max([max(abs(s["sum_span"]), abs(s["sumsq_span"]), abs(s["maxabs_span"])) for s in t] or [float("nan")])
              for name, t in traj.items()}
     g = lambda name, key: res[name][key] if name in res else 0.0
     rows = [[name, len(traj[name]), res[name]["ok"] if name in res else True,
              res[name]["identical_path"] if name in res else True, g(name, "max_loss_diff"),
-             g(name, "max_rel_sumsq_diff"), g(name, "max_rel_sum_diff"), spans[name]] for name in modes]
+             g(name, "max_rel_sumsq_diff"), g(name, "max_rel_sum_diff"),
+             res[name].get("max_sum_diff_per_param", float("nan")) if name in res else 0.0, spans[name]]
+            for name in modes]
     save(a, f"trajectory_{a.preset}_g{a.gpus[0]}",
          {"comparisons": res, "cross_rank_span": spans, "all_ok": all(r["ok"] for r in res.values())},
          (["mode", "steps", "within tolerance of blocking", "same sums as blocking", "max loss diff",
-           "max rel diff of sum of squares", "max rel diff of sum", "largest cross-rank span"], rows))
+           "max rel diff of sum of squares", "max rel diff of sum", "max diff of sum per parameter",
+           "largest cross-rank span"], rows))
 
 
 def cmd_edge(a):

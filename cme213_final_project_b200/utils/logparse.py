@@ -97,7 +97,7 @@ def summarize_repeats(tok_s: List[float], valid: List[bool], min_repeat: int = 2
 
 
 def compare_trajectories(base: List[Dict], other: List[Dict], loss_tol: float = 5e-3, sum_rtol: float = 1e-4,
-                         sumsq_rtol: float = 1e-3, maxabs_rtol: float = 1e-2) -> Dict:
+                         sumsq_rtol: float = 1e-2, maxabs_rtol: float = 1e-2, n_params: int = 0) -> Dict:
     """Per-step comparison of a synchronisation mode against the blocking baseline; hashes need not match
     (floating-point reorder), statistics must agree within the tolerances.
 
@@ -107,7 +107,11 @@ def compare_trajectories(base: List[Dict], other: List[Dict], loss_tol: float = 
     they agree bit for bit).  ``ok``: loss, sum of squares and largest magnitude agree -- what a mode with different
     arithmetic has to meet (the fused path reduces bf16 gradients in fp32, the library all-reduce in bf16): under
     Adam a near-zero gradient that changes sign moves its parameter by a whole step the other way, so the plain sum,
-    a residual of cancelling signed values, drifts by many parameters' worth of lr while the magnitudes agree."""
+    a residual of cancelling signed values, drifts by many parameters' worth of lr while the magnitudes agree.
+    The library's own bucketed bf16 all-reduce deviates from its whole-arena all-reduce by the same amounts (measured
+    at 4 ranks), so the second level is the tolerance of the gradient precision, not of one implementation.
+    With ``n_params`` the absolute differences of sum and sum of squares are also given per parameter, the
+    normalisation the reference's summariser applies (``summarize_trajectory_validation.py:162-166``)."""
     n = min(len(base), len(other))
     rel = lambda key, floor: max((abs(base[i][key] - other[i][key]) / max(floor, abs(base[i][key])) for i in range(n)),
                                  default=float("nan"))
@@ -115,7 +119,12 @@ def compare_trajectories(base: List[Dict], other: List[Dict], loss_tol: float = 
     worst_sum, worst_sumsq, worst_maxabs = rel("sum", 1.0), rel("sumsq", 1e-12), rel("maxabs", 1e-12)
     span = max((o["sum_span"] for o in other), default=0.0)
     same_len = n > 0 and len(base) == len(other)
-    return {"steps": n, "max_loss_diff": worst_loss, "max_rel_sum_diff": worst_sum, "max_rel_sumsq_diff": worst_sumsq,
+    out = {}
+    if n_params > 0:
+        absd = lambda key: max((abs(base[i][key] - other[i][key]) for i in range(n)), default=float("nan"))
+        out = {"max_sum_diff_per_param": absd("sum") / n_params, "max_sumsq_diff_per_param": absd("sumsq") / n_params}
+    return {**out,
+            "steps": n, "max_loss_diff": worst_loss, "max_rel_sum_diff": worst_sum, "max_rel_sumsq_diff": worst_sumsq,
             "max_rel_maxabs_diff": worst_maxabs, "max_sum_span": span,
             "identical_path": same_len and worst_loss <= loss_tol and worst_sum <= sum_rtol,
             "ok": same_len and worst_loss <= loss_tol and worst_sumsq <= sumsq_rtol and worst_maxabs <= maxabs_rtol}
