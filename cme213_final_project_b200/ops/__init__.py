@@ -365,7 +365,7 @@ class CmeAttn(ctypes.Structure):
         ("d_o", ctypes.c_void_p), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
         ("delta", ctypes.c_void_p), ("dq_accum", ctypes.c_void_p),
         ("ws", ctypes.c_void_p), ("ws_bytes", ctypes.c_longlong),
-        ("dq_sem", ctypes.c_void_p),
+        ("dq_sem", ctypes.c_void_p), ("dq_mode", ctypes.c_int),
     ]
 
 
@@ -407,21 +407,29 @@ def attention_fwd(q, k, v, B: int, H: int, T: int, layout: str = "split", causal
 
 
 def attention_bwd(q, k, v, out, lse, dout, B: int, H: int, T: int, layout: str = "split", causal: bool = False,
-                  backend: str = "auto", ordered_dq: bool = False):
-    """Returns ``(dq, dk, dv)``.  ``ordered_dq`` (tensor-core kernel): the key blocks' parts of dQ are added in a fixed
-    order and dQ is finished inside the kernel (bit-reproducible, slower); default: unordered reduce-adds into a
-    cleared fp32 scratch and a conversion kernel."""
+                  backend: str = "auto", ordered_dq: bool = False, dq_mode: Optional[int] = None,
+                  scratch=None):
+    """Returns ``(dq, dk, dv)``.  How the tensor-core kernel completes dQ from the key blocks' parts (``dq_mode``):
+    2 (default up to 64 query blocks) adds them to an fp32 scratch in arrival order and lets the CTA whose part
+    comes last scale and cast the sums; 1 (``ordered_dq``) adds them in a fixed order (bit-reproducible, slower);
+    0 clears the scratch per launch and converts it with a second kernel.  ``scratch`` = (fp32 tensor of ``q.numel()``
+    zeros, int32 tensor of ``B * H * ceil(T / 128)`` zeros) lets calls share the buffers; modes 1 and 2 leave both
+    zero again."""
     _cuda(q, k, v, out, lse, dout)
     a = _attn_desc(q, B, H, T, layout, causal)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty_like(lse)
-    acc = torch.empty(q.numel(), dtype=torch.float32, device=q.device)
+    if dq_mode is None:
+        dq_mode = 1 if ordered_dq else 2 if (T + 127) // 128 <= 64 else 0
+    if scratch is not None:
+        acc, sem = scratch
+    else:
+        acc = torch.zeros(q.numel(), dtype=torch.float32, device=q.device)
+        sem = torch.zeros(B * H * ((T + 127) // 128), dtype=torch.int32, device=q.device)
     a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     a.d_o, a.dq, a.dk, a.dv = dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     a.delta, a.dq_accum = delta.data_ptr(), acc.data_ptr()
-    if ordered_dq:
-        sem = torch.zeros(B * H * ((T + 127) // 128), dtype=torch.int32, device=q.device)
-        a.dq_sem = sem.data_ptr()
+    a.dq_sem, a.dq_mode = sem.data_ptr(), int(dq_mode)
     _check(lib().cme_attention_bwd(ctypes.byref(a), _BACKENDS[backend], _stream()))
     return dq, dk, dv
 

@@ -26,10 +26,17 @@ struct CmeAttn {
     float* delta;                // [nb*nh, T] scratch: rowsum(dO * O)
     float* dq_accum;             // fp32 scratch [nb*nh*T*HD] for the tcgen05 backward (may be null)
     void* ws; long long ws_bytes;    // scratch of attention_gemm_ws_bytes() for the batched-GEMM path (may be null)
-    int* dq_sem;                 // [nb*nh * ceil(T / 128)] ints, zero before the first launch (the kernel leaves them zero):
-                                 // lets the tcgen05 backward add the key blocks' parts of dQ in a fixed order and finish
-                                 // dQ itself; null = unordered adds into a cleared scratch plus a conversion kernel
+    int* dq_sem;                 // [nb*nh * ceil(T / 128)] ints, zero before the first launch (the kernel leaves them zero);
+                                 // needed by dq_mode 1 and 2
+    int dq_mode;                 // how the tcgen05 backward completes dQ from the key blocks' parts:
+                                 //   0  the launch clears dq_accum, the parts are added in arrival order, a second kernel
+                                 //      scales and casts the sums
+                                 //   1  the parts are added in a fixed order (bit-reproducible); key block 0 finishes
+                                 //   2  arrival order; the CTA whose part comes last scales, casts and writes zeros back:
+                                 //      dq_accum must be zero before the first launch and is zero after every launch
 };
+
+constexpr int CME_ATTN_FINISH_MAX_QBLOCKS = 64;      // dq_mode 2: query blocks (of 128 rows) per sequence
 
 int attention_simt_fwd(const CmeAttn* a, cudaStream_t st);
 int attention_simt_bwd(const CmeAttn* a, cudaStream_t st);

@@ -15,9 +15,12 @@
 // row's log-sum-exp and delta are two registers):
 //     S = Q_i K^T,  dP = dO_i V^T (TMEM)  ->  P, dS (bf16, shared, double buffered)
 //     dV += P^T dO_i,  dK += dS^T Q_i (A operand read transposed; TMEM accumulators),  dQ_i = dS K (TMEM).
-//     dQ_i gets a part from every key block that sees query block i.  Default: the parts are added to a cleared
-//     fp32 scratch with bulk reduce-adds in whatever order the CTAs arrive, and a small kernel scales and casts the
-//     sums (fast; the last bits of dQ depend on the order).  Deterministic form (a counter array is passed): the
+//     dQ_i gets a part from every key block that sees query block i.  The parts are added to an fp32 scratch with
+//     bulk reduce-adds in whatever order the CTAs arrive (fast; the last bits of dQ depend on the order), and
+//     either (dq_mode 2, the engine's default) a counter per tile tells the CTA whose part arrived last to scale and
+//     cast the tile's sums itself -- a spare warp does it and writes zeros back, so the scratch is clear for the next
+//     launch and no clearing or conversion pass runs -- or (dq_mode 0) the launch clears the scratch first and a
+//     small kernel converts it afterwards.  Deterministic form (dq_mode 1): the
 //     highest key block stores its part, each lower one adds its own when the tile's counter says it is its turn,
 //     and key block 0, whose turn is last, adds the sum to its part in registers, scales, casts and writes dQ --
 //     bit-reproducible, no clearing or conversion pass, but the chain of turns makes CTAs wait for one another
@@ -62,9 +65,6 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const vo
                      reinterpret_cast<uint64_t>(m)),
                  "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
-}
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 // A descriptor whose start address is `bytes` further than that of `base` (the address field counts 16-byte
@@ -321,9 +321,10 @@ struct BwdParams {
     __nv_bfloat16* dk; __nv_bfloat16* dv;
     long long sb, sh, st;          // strides of dQ / dK / dV
     int* status;
-    int* dq_sem;                   // [nb*nh, query blocks] contribution counters (zero between launches), or null:
-                                   // unordered reduce-adds into a zeroed dq_accum, converted by dq_convert_kernel
-    __nv_bfloat16* dq;             // final dQ (ordered form only)
+    int* dq_sem;                   // [nb*nh, query blocks] contribution counters (zero between launches); null in mode 0
+    __nv_bfloat16* dq;             // final dQ (modes 1 and 2)
+    int dq_mode;                   // 0: unordered adds into a scratch the launch cleared, converted by dq_convert_kernel
+                                   // 1: ordered adds, key block 0 finishes   2: unordered adds, the last part's CTA finishes
 };
 
 // Bounded wait until *sem >= want (acquire).  Lane 0 of the calling warp polls; the warp then synchronises.
@@ -345,11 +346,14 @@ __device__ __forceinline__ bool sem_wait_warp(const int* sem, int want, volatile
 }
 
 // shared: K 16K | V 16K | Q[2] 32K | dO[2] 32K | P 32K | dS[2] 64K | dQ staging (fp32) 32K | barriers   (one CTA per SM)
-constexpr int BWD_SMEM = 14 * TILE_BYTES + 128;
+constexpr int BWD_SMEM = 14 * TILE_BYTES + 512;     // tiles | barriers, flags and the finishing warp's ring
 constexpr int BWD_MMA_WARP = 16;           // warps 0..15 compute, warp 16 issues TMA loads and MMA,
 constexpr int BWD_STORE_WARP = 17;         // warp 17 issues the dQ reduce-stores
-constexpr int BWD_THREADS = 18 * 32;
+constexpr int BWD_FINISH_WARP = 18;        // warp 18 (mode 2) converts the dQ tiles whose last part this CTA added
+constexpr int BWD_THREADS = 19 * 32;
+constexpr int FIN_RING = CME_ATTN_FINISH_MAX_QBLOCKS;   // a CTA hands over at most one tile per query block
 constexpr int BWD_TMEM_COLS = 512;     // S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ [384,448)
+static_assert(12 * 8 + 4 + 4 + 4 + FIN_RING * 4 <= 512, "barriers, flags and ring exceed their block");
 static_assert(BWD_SMEM <= 227 * 1024, "backward shared-memory carve-up exceeds what one CTA may have");
 static_assert(2 * 128 + 3 * HD <= BWD_TMEM_COLS, "backward TMEM budget: S, dP, dV, dK, dQ");
 
@@ -382,13 +386,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint64_t* s_free = bars + 11;              // S and dP of a query block are in registers (512 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* fin_count = abort_flag + 1;  // tiles handed to the finishing warp so far; -1 - n once the store warp
+                                               // has ended after n tiles
+    volatile int* fin_ring = abort_flag + 2;   // [FIN_RING] query-block indices
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Ordered form: higher key blocks are dispatched first, so a CTA only ever waits for the dQ parts of key blocks
     // above its own, which are then resident or finished.  Unordered form: the key blocks with the most query blocks
     // (the lowest) first.
     const int nkb = gridDim.x;
-    const bool ordered = p.dq_sem != nullptr;
+    const bool ordered = p.dq_mode == 1, finish_last = p.dq_mode == 2;
     const int kb = ordered ? nkb - 1 - (int)blockIdx.x : (int)blockIdx.x, k0 = kb * BKV;
     const int bh = blockIdx.y, b = bh / p.nh, h = bh % p.nh;
     const int nq = (p.T + BQ - 1) / BQ;
@@ -400,6 +407,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        *fin_count = 0;
         mbar_init(kv_full, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
         mbar_init(s_full, 1);
@@ -534,9 +542,78 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     asm volatile("fence.proxy.async.global;" ::: "memory");
                     __threadfence();
                     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(sem), "r"(turn + 1) : "memory");
+                } else if (finish_last) {
+                    // count this part in once the adds have been performed; whoever brings the count to the number of
+                    // key blocks that see the tile hands it to the finishing warp
+                    tma_store_wait<0>();
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    __threadfence();
+                    int before;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;"
+                                 : "=r"(before) : "l"(p.dq_sem + (long long)bh * nq + qi) : "memory");
+                    if (before + 1 == first_kb(qi) + 1) {
+                        const int n = *fin_count;
+                        fin_ring[n % FIN_RING] = qi;
+                        __threadfence_block();
+                        *fin_count = n + 1;
+                    }
                 }
             }
             tma_store_wait<0>();
+            if (finish_last) { __threadfence_block(); *fin_count = -1 - *fin_count; }
+        }
+    } else if (warp == BWD_FINISH_WARP) {
+        // ---------------- finishing warp (mode 2): every part of a handed-over tile is in the scratch; scale and cast the
+        // sums to dQ, and leave zeros behind for the next launch.  A tile is 128 x 64 fp32 = 32 KB of contiguous scratch.
+        if (finish_last && n_it > 0) {
+            int taken = 0;
+            bool ok = true;
+            for (uint32_t spin = 0; ok;) {
+                const int c = *fin_count;
+                const int avail = c >= 0 ? c : -1 - c;
+                if (taken == avail) {
+                    if (c < 0) break;                                   // the store warp has ended and nothing is left
+                    if ((++spin & 255u) == 0 && *abort_flag) break;
+                    if (spin >= (1u << 24)) { *abort_flag = 1; break; }
+                    __nanosleep(200);
+                    continue;
+                }
+                spin = 0;
+                __threadfence_block();
+                const int qi = fin_ring[taken % FIN_RING];
+                ++taken;
+                __threadfence();
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                const int q0 = qi * BQ;
+                const int rows_here = min(BQ, p.T - q0);
+                float4* tile = reinterpret_cast<float4*>(p.dq_accum + ((long long)bh * p.T + q0) * HD);
+                __nv_bfloat16* dst0 = p.dq + (long long)b * p.sb + (long long)h * p.sh + (long long)q0 * p.st;
+                const int n4 = rows_here * (HD / 4);                    // float4 elements of the tile
+#pragma unroll 1
+                for (int base = 0; base < n4; base += 32 * 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int i = base + j * 32 + lane;
+                        v[j] = i < n4 ? __ldcg(tile + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int i = base + j * 32 + lane;
+                        if (i < n4) {
+                            const int r = i / (HD / 4), c4 = i % (HD / 4);
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v[j].x * p.scale, v[j].y * p.scale);
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(v[j].z * p.scale, v[j].w * p.scale);
+                            uint2 out;
+                            out.x = *reinterpret_cast<uint32_t*>(&lo);
+                            out.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(dst0 + (long long)r * p.st + c4 * 4) = out;
+                            __stcg(tile + i, make_float4(0.f, 0.f, 0.f, 0.f));
+                        }
+                    }
+                }
+                if (lane == 0) p.dq_sem[(long long)bh * nq + qi] = 0;  // nobody else touches it before the next launch
+            }
         }
     } else {
         // ---------------- gradient warps: 16 warps; warp w owns TMEM lanes 32*(w&3).. (query rows) and the
@@ -822,8 +899,12 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
     if ((rc = make_map4(&mv, a->v, a->T, a->nh, a->nb, a->st, a->sh, a->sb, 128))) return rc;
     if ((rc = make_map4(&mdo, a->d_o, a->T, a->nh, a->nb, a->ost, a->osh, a->osb, 128))) return rc;
     if ((rc = make_map_dq(&mdq, a->dq_accum, a->T, a->nb * a->nh))) return rc;
-    const bool ordered = a->dq_sem != nullptr;
-    if (!ordered) CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
+    const int mode = a->dq_mode;
+    CME_REQUIRE(mode >= 0 && mode <= 2 && (mode == 0 || a->dq_sem != nullptr), CME_ERR_SHAPE,
+                "attention backward: dq_mode 1 and 2 need the counter array");
+    CME_REQUIRE(mode != 2 || cme_cdiv(a->T, BQ) <= CME_ATTN_FINISH_MAX_QBLOCKS, CME_ERR_LIMIT,
+                "attention backward: dq_mode 2 handles up to %d query blocks", CME_ATTN_FINISH_MAX_QBLOCKS);
+    if (mode == 0) CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
     static bool attr[CME_MAX_DEVICES] = {};               // function attributes are per device
     int dev = 0;
     CME_CUDA(cudaGetDevice(&dev));
@@ -833,11 +914,11 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
     }
     BwdParams p{a->T, a->nh, a->causal, a->scale, a->scale * LOG2E, a->lse, a->delta, a->dq_accum,
                 (__nv_bfloat16*)a->dk, (__nv_bfloat16*)a->dv, a->sb, a->sh, a->st, g_attn_status, a->dq_sem,
-                (__nv_bfloat16*)a->dq};
+                (__nv_bfloat16*)a->dq, mode};
     dim3 grid(cme_cdiv(a->T, BKV), a->nb * a->nh);
     attn_bwd_tc_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, mdo, mdq, p);
     CME_LAUNCH_CHECK();
-    if (ordered) return CME_OK;                    // dQ was completed inside the kernel
+    if (mode != 0) return CME_OK;                  // dQ was completed inside the kernel
     const long long nthreads = rows * (HD / 8);
     CME_CUDA(cme_launch_dependent(dq_convert_kernel, dim3(cme_cdiv(nthreads, 256)), dim3(256), 0, st,
                                   (const float*)a->dq_accum, (__nv_bfloat16*)a->dq, a->T, a->nh, a->sb, a->sh, a->st,

@@ -220,6 +220,12 @@ bool attn_ordered_dq() {
     return on;
 }
 
+// CME213_ATTN_DQ_MODE=0: dQ through a cleared scratch and a conversion kernel (for A/B measurements).
+bool attn_dq_finish() {
+    static const bool on = !(getenv("CME213_ATTN_DQ_MODE") && getenv("CME213_ATTN_DQ_MODE")[0] == '0');
+    return on;
+}
+
 void fill_attn(const Engine& e, int l, CmeAttn& a) {
     const CmeEngineDesc& d = e.d;
     const int HD = d.D / d.H;
@@ -240,7 +246,10 @@ void fill_attn(const Engine& e, int l, CmeAttn& a) {
     if (d.head_flat) { a.osb = (long long)d.T * HD; a.osh = 0; a.ost = HD; }
     else { a.osb = (long long)d.T * D; a.osh = HD; a.ost = D; }
     a.lse = e.la[l].lse; a.delta = e.delta; a.dq_accum = e.dq_accum;
-    a.dq_sem = attn_ordered_dq() ? e.dq_sem : nullptr;
+    // dQ: in arrival order and finished inside the kernel by the last part's CTA (mode 2, scratch stays clear); the
+    // deterministic form on request (mode 1); long sequences or CME213_ATTN_DQ_MODE=0 clear and convert per launch
+    a.dq_sem = e.dq_sem;
+    a.dq_mode = attn_ordered_dq() ? 1 : attn_dq_finish() && (d.T + 127) / 128 <= CME_ATTN_FINISH_MAX_QBLOCKS ? 2 : 0;
     a.ws = e.attn_ws; a.ws_bytes = e.attn_ws_bytes;
 }
 
@@ -283,8 +292,9 @@ CME_API int cme_engine_bind(void* h, void* params, void* grads, void* workspace,
     CME_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, CME_ERR_SHAPE, "engine: workspace must be 256-byte aligned");
     e->params = (char*)params; e->grads = (char*)grads; e->ws = (char*)workspace;
     carve(*e, e->ws);
-    // the attention backward's ordering counters start at zero; every launch leaves them at zero again
+    // the attention backward's counters and its dQ scratch start at zero; every launch leaves them at zero again
     CME_CUDA(cudaMemset(e->dq_sem, 0, (size_t)e->BH * ((e->d.T + 127) / 128) * 4));
+    CME_CUDA(cudaMemset(e->dq_accum, 0, (size_t)e->BT * e->d.D * 4));
     return CME_OK;
 }
 

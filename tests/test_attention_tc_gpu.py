@@ -124,3 +124,29 @@ def test_backward_dq_is_bit_reproducible_and_both_forms_agree(B, H, T, causal):
     old = ops.attention_bwd(q, k, v, out, lse, do, B, H, T, "split", causal, backend="tc", ordered_dq=False)
     for a, b in zip(old, runs[0]):
         assert (a.float() - b.float()).abs().max().item() < 2e-2 * max(1.0, b.float().abs().max().item())
+
+
+@pytest.mark.parametrize("B,H,T,layout,causal", [(2, 4, 1024, "split", True), (1, 2, 512, "split", False),
+                                                 (1, 3, 200, "split", True), (2, 4, 256, "flat", False)])
+def test_backward_dq_finished_by_the_last_part_and_scratch_left_clear(B, H, T, layout, causal):
+    """The default way of completing dQ: the CTA whose part of a query tile arrives last scales and casts the
+    tile's sums inside the kernel and writes zeros back.  Three launches share one scratch and one counter array:
+    each must match the fp32 reference and the two-kernel form (cleared scratch + conversion), and leave both
+    buffers zero."""
+    from cme213_final_project_b200 import ops
+    q, k, v, do = _inputs(B, H, T, seed=4)
+    _, dq_ref, dk_ref, dv_ref = _ref(q, k, v, do, B, H, T, layout, causal)
+    out, lse = ops.attention_fwd(q, k, v, B, H, T, layout, causal, backend="tc")
+    two_kernel = ops.attention_bwd(q, k, v, out, lse, do, B, H, T, layout, causal, backend="tc", dq_mode=0)
+    acc = torch.zeros(q.numel(), dtype=torch.float32, device="cuda")
+    sem = torch.zeros(B * H * ((T + 127) // 128), dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        got = ops.attention_bwd(q, k, v, out, lse, do, B, H, T, layout, causal, backend="tc", dq_mode=2,
+                                scratch=(acc, sem))
+        torch.cuda.synchronize()
+        assert ops.attention_check_status() == 0
+        assert acc.abs().max().item() == 0.0 and sem.abs().max().item() == 0
+        for name, a, want, other in zip(("dq", "dk", "dv"), got, (dq_ref, dk_ref, dv_ref), two_kernel):
+            scale = max(1.0, want.abs().max().item())
+            assert (a.float() - want).abs().max().item() < 3e-2 * scale, name
+            assert (a.float() - other.float()).abs().max().item() < 1e-2 * scale, name
