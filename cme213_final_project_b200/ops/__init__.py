@@ -410,9 +410,10 @@ def attention_bwd(q, k, v, out, lse, dout, B: int, H: int, T: int, layout: str =
                   backend: str = "auto", ordered_dq: bool = False, dq_mode: Optional[int] = None,
                   scratch=None):
     """Returns ``(dq, dk, dv)``.  How the tensor-core kernel completes dQ from the key blocks' parts (``dq_mode``):
-    2 (default up to 64 query blocks) adds them to an fp32 scratch in arrival order and lets the CTA whose part
-    comes last scale and cast the sums; 1 (``ordered_dq``) adds them in a fixed order (bit-reproducible, slower);
-    0 clears the scratch per launch and converts it with a second kernel.  ``scratch`` = (fp32 tensor of ``q.numel()``
+    0 (default) clears an fp32 scratch, adds the parts in arrival order and converts the sums with a second kernel;
+    1 (``ordered_dq``) adds them in a fixed order (bit-reproducible, slower); 2 (up to 64 query blocks) adds them in
+    arrival order and lets the CTA whose part comes last scale and cast the sums (two launches fewer, slower at
+    large shapes).  ``scratch`` = (fp32 tensor of ``q.numel()``
     zeros, int32 tensor of ``B * H * ceil(T / 128)`` zeros) lets calls share the buffers; modes 1 and 2 leave both
     zero again."""
     _cuda(q, k, v, out, lse, dout)
@@ -420,7 +421,7 @@ def attention_bwd(q, k, v, out, lse, dout, B: int, H: int, T: int, layout: str =
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty_like(lse)
     if dq_mode is None:
-        dq_mode = 1 if ordered_dq else 2 if (T + 127) // 128 <= 64 else 0
+        dq_mode = 1 if ordered_dq else 0
     if scratch is not None:
         acc, sem = scratch
     else:

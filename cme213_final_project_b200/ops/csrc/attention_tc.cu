@@ -17,10 +17,12 @@
 //     dV += P^T dO_i,  dK += dS^T Q_i (A operand read transposed; TMEM accumulators),  dQ_i = dS K (TMEM).
 //     dQ_i gets a part from every key block that sees query block i.  The parts are added to an fp32 scratch with
 //     bulk reduce-adds in whatever order the CTAs arrive (fast; the last bits of dQ depend on the order), and
-//     either (dq_mode 2, the engine's default) a counter per tile tells the CTA whose part arrived last to scale and
-//     cast the tile's sums itself -- a spare warp does it and writes zeros back, so the scratch is clear for the next
-//     launch and no clearing or conversion pass runs -- or (dq_mode 0) the launch clears the scratch first and a
-//     small kernel converts it afterwards.  Deterministic form (dq_mode 1): the
+//     either (dq_mode 0, the default) the launch clears the scratch first and a small kernel scales and casts the
+//     sums afterwards, or (dq_mode 2) a counter per tile tells the CTA whose part arrived last to do that itself --
+//     a spare warp converts the tile and writes zeros back, so no clearing or conversion pass runs; the query
+//     blocks are then walked downwards so that the finishing work spreads over the CTAs.  Still slower at large shapes
+//     (about 0.05 ms per call at 16 x 12 heads x 1024 tokens: every reduce-add has to complete before its part is
+//     counted in, and one warp converts a 32 KB tile).  Deterministic form (dq_mode 1): the
 //     highest key block stores its part, each lower one adds its own when the tile's counter says it is its turn,
 //     and key block 0, whose turn is last, adds the sum to its part in registers, scales, casts and writes dQ --
 //     bit-reproducible, no clearing or conversion pass, but the chain of turns makes CTAs wait for one another
@@ -404,6 +406,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     auto first_kb = [&](int qi) { return p.causal ? min(qi, nkb - 1) : nkb - 1; };
     const int i_begin = p.causal ? kb : 0;     // query blocks that see this key block
     const int n_it = nq - i_begin;
+    // Query block of iteration `it`.  Mode 2 walks them downwards: the key blocks of a head start together, so all of
+    // them then reach a query tile in the same iteration and whichever comes last finishes it -- the finishing work
+    // spreads over the CTAs instead of queueing up on key block 0, which is the last arrival of every tile when all
+    // walk upwards.
+    auto qblock = [&](int it) { return finish_last ? nq - 1 - it : i_begin + it; };
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -439,8 +446,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             auto load_q = [&](int it) {
                 const int st = it & 1;
                 mbar_arrive_expect_tx(&q_full[st], 2 * TILE_BYTES);
-                tma_load_4d(sQ + st * TILE_BYTES, &tmQ, &q_full[st], 0, (i_begin + it) * BQ, h, b);
-                tma_load_4d(sdO + st * TILE_BYTES, &tmdO, &q_full[st], 0, (i_begin + it) * BQ, h, b);
+                tma_load_4d(sQ + st * TILE_BYTES, &tmQ, &q_full[st], 0, qblock(it) * BQ, h, b);
+                tma_load_4d(sdO + st * TILE_BYTES, &tmdO, &q_full[st], 0, qblock(it) * BQ, h, b);
             };
             // descriptors are encoded once; per MMA only a byte offset is added
             const uint64_t kK = make_smem_desc(smem_u32(sK), 0, 1024), vK = make_smem_desc(smem_u32(sV), 0, 1024);
@@ -513,7 +520,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0 && !(ordered && kb == 0)) {
             for (int f = 0; f < n_it; ++f) {
                 if (!mbar_wait(dqs_full, f & 1, abort_flag)) break;
-                const int qi = i_begin + f, q0 = qi * BQ;
+                const int qi = qblock(f), q0 = qi * BQ;
                 int* sem = ordered ? p.dq_sem + (long long)bh * nq + qi : nullptr;
                 const int turn = ordered ? first_kb(qi) - kb : 1;
                 if (ordered) {
@@ -636,7 +643,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (finisher) {
                 // every other key block's part of this query block is in the scratch tile (their counters say so):
                 // add it to this thread's 16 columns, scale, cast, store dQ
-                const int qi = i_begin + f, need = first_kb(qi);
+                const int qi = qblock(f), need = first_kb(qi);
                 const int qrow = qi * BQ + row;
                 float v[16];
 #pragma unroll
@@ -677,14 +684,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // row statistics of a query block are fetched one block ahead: their global-memory latency must not sit
         // between the arrival of S and the first exponential
         auto row_stats = [&](int it2, float& l2, float& d2) {
-            const int qc2 = min((i_begin + it2) * BQ + row, p.T - 1);
+            const int qc2 = min(qblock(it2) * BQ + row, p.T - 1);
             l2 = p.lse[(long long)bh * p.T + qc2] * LOG2E;
             d2 = p.delta[(long long)bh * p.T + qc2];
         };
         float lse2_n = 0.f, dl_n = 0.f;
         if (n_it > 0) row_stats(0, lse2_n, dl_n);
         for (int it = 0; it < n_it && ok; ++it) {
-            const int qi0 = (i_begin + it) * BQ;
+            const int qi0 = qblock(it) * BQ;
             const int q = qi0 + row;
             const float lse2 = lse2_n, dl = dl_n;
             if (it + 1 < n_it) row_stats(it + 1, lse2_n, dl_n);

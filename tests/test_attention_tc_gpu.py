@@ -129,8 +129,8 @@ def test_backward_dq_is_bit_reproducible_and_both_forms_agree(B, H, T, causal):
 @pytest.mark.parametrize("B,H,T,layout,causal", [(2, 4, 1024, "split", True), (1, 2, 512, "split", False),
                                                  (1, 3, 200, "split", True), (2, 4, 256, "flat", False)])
 def test_backward_dq_finished_by_the_last_part_and_scratch_left_clear(B, H, T, layout, causal):
-    """The default way of completing dQ: the CTA whose part of a query tile arrives last scales and casts the
-    tile's sums inside the kernel and writes zeros back.  Three launches share one scratch and one counter array:
+    """dQ completed inside the kernel (``dq_mode=2``): the CTA whose part of a query tile arrives last scales and
+    casts the tile's sums and writes zeros back.  Three launches share one scratch and one counter array:
     each must match the fp32 reference and the two-kernel form (cleared scratch + conversion), and leave both
     buffers zero."""
     from cme213_final_project_b200 import ops
