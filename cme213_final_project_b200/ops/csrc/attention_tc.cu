@@ -257,20 +257,30 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 l *= alpha;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float sum8[8];                                 // one partial row sum per position in a group: independent chains
+            // scale-and-shift and the row sum on packed pairs (one instruction per two keys); four independent chains
+            const F32x2 sc2 = f2_splat(p.scale_log2), nm2 = f2_splat(-m_use);
+            F32x2 sum2[4];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) sum8[c] = 0.f;
+            for (int c = 0; c < 4; ++c) sum2[c] = f2_splat(0.f);
 #pragma unroll
             for (int g = 0; g < 16; ++g) {                 // 16 groups of 8 keys = 16-byte chunks of the P row
                 float pr[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    pr[i] = ex2_approx(fmaf(__uint_as_float(r[g * 8 + i]), p.scale_log2, -m_use));
-                    sum8[i] += pr[i];
+                for (int i = 0; i < 8; i += 2) {
+                    float a0, a1;
+                    f2_unpack(f2_fma(f2_pack(__uint_as_float(r[g * 8 + i]), __uint_as_float(r[g * 8 + i + 1])), sc2, nm2),
+                              a0, a1);
+                    pr[i] = ex2_approx(a0);
+                    pr[i + 1] = ex2_approx(a1);
+                    sum2[i >> 1] = f2_add(sum2[i >> 1], f2_pack(pr[i], pr[i + 1]));
                 }
                 *reinterpret_cast<uint4*>(sP + (g >> 3) * TILE_BYTES + swz(row, g & 7)) = pack8(pr);
             }
-            l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+            {
+                float s0, s1;
+                f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), s0, s1);
+                l += s0 + s1;
+            }
             tc_fence_before();
             fence_proxy_async();
             mbar_arrive(p_ready);
@@ -707,18 +717,27 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc_fence_before();
             mbar_arrive(s_free);                        // S and dP may be overwritten by the next block's products
             if (it > 0 && !mbar_wait(p_free, (it - 1) & 1, abort_flag)) { ok = false; break; }
+            // scale-and-shift, dP - delta and the product on packed pairs (one instruction per two keys)
+            const F32x2 sc2 = f2_splat(p.scale_log2), nl2 = f2_splat(-lse2), nd2 = f2_splat(-dl);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 float pr[8], ds[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float pv = ex2_approx(fmaf(__uint_as_float(rs[g * 8 + i]), p.scale_log2, -lse2));
+                for (int i = 0; i < 8; i += 2) {
+                    float a0, a1;
+                    f2_unpack(f2_fma(f2_pack(__uint_as_float(rs[g * 8 + i]), __uint_as_float(rs[g * 8 + i + 1])), sc2, nl2),
+                              a0, a1);
+                    float pv0 = ex2_approx(a0), pv1 = ex2_approx(a1);
                     if (need_mask) {
                         const int key = k0 + cg * 32 + g * 8 + i;
-                        if (q >= p.T || key >= p.T || (p.causal && key > q)) pv = 0.f;
+                        if (q >= p.T || key >= p.T || (p.causal && key > q)) pv0 = 0.f;
+                        if (q >= p.T || key + 1 >= p.T || (p.causal && key + 1 > q)) pv1 = 0.f;
                     }
-                    pr[i] = pv;
-                    ds[i] = pv * (__uint_as_float(rd[g * 8 + i]) - dl);
+                    pr[i] = pv0;
+                    pr[i + 1] = pv1;
+                    f2_unpack(f2_mul(f2_pack(pv0, pv1),
+                                     f2_add(f2_pack(__uint_as_float(rd[g * 8 + i]), __uint_as_float(rd[g * 8 + i + 1])), nd2)),
+                              ds[i], ds[i + 1]);
                 }
                 const uint32_t off = (cg >> 1) * TILE_BYTES + swz(row, (cg & 1) * 4 + g);
                 *reinterpret_cast<uint4*>(bufP + off) = pack8(pr);

@@ -175,6 +175,50 @@ __device__ __forceinline__ void gelu_and_grad_fast(float x, float& g, float& d) 
     d = fmaf(hx * fmaf(-t, t, 1.f), fmaf(0.1070322243f, x2, 0.7978845608f), fmaf(0.5f, t, 0.5f));
 }
 
+// Packed fp32 pairs (sm_100: add / sub / mul / fma on two fp32 values held in one 64-bit register issue as one
+// instruction).  The arithmetic-heavy epilogues are bound by issue slots, so pairs halve their cost.
+typedef unsigned long long F32x2;
+__device__ __forceinline__ F32x2 f2_pack(float lo, float hi) {
+    F32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(F32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ F32x2 f2_splat(float c) { return f2_pack(c, c); }
+__device__ __forceinline__ F32x2 f2_fma(F32x2 a, F32x2 b, F32x2 c) {
+    F32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ F32x2 f2_mul(F32x2 a, F32x2 b) {
+    F32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ F32x2 f2_add(F32x2 a, F32x2 b) {
+    F32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// GELU and its derivative for two values at once, from one hardware tanh each.  With a = (1 + t) / 2:
+//   gelu = x a,   gelu' = a (1 + 2 x u'(x) (1 - a))   since 1 - t^2 = 4 a (1 - a);   u' = 0.79788 + 0.10703 x^2.
+__device__ __forceinline__ void gelu_and_grad_fast2(float& x0, float& x1, float& d0, float& d1) {
+    const F32x2 x = f2_pack(x0, x1);
+    const F32x2 x2 = f2_mul(x, x);
+    const F32x2 u = f2_mul(x, f2_fma(f2_splat(0.0356774081f), x2, f2_splat(0.7978845608f)));
+    float u0, u1;
+    f2_unpack(u, u0, u1);
+    const F32x2 t = f2_pack(tanh_fast(u0), tanh_fast(u1));
+    const F32x2 a = f2_fma(f2_splat(0.5f), t, f2_splat(0.5f));
+    const F32x2 oma = f2_fma(f2_splat(-0.5f), t, f2_splat(0.5f));
+    const F32x2 r = f2_mul(x, f2_fma(f2_splat(0.2140644486f), x2, f2_splat(1.5957691216f)));
+    f2_unpack(f2_mul(x, a), x0, x1);
+    f2_unpack(f2_mul(a, f2_fma(r, oma, f2_splat(1.f))), d0, d1);
+}
+
 // 8 x bf16 <-> 8 x f32 through one 128-bit word (a uint4, so loads and stores stay single 128-bit accesses).
 typedef uint4 Bf16x8;
 __device__ __forceinline__ float2 bf2_to_f2(uint32_t w) {

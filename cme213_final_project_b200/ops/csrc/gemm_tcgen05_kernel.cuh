@@ -283,14 +283,16 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
             float b[8];
             unpack8(*reinterpret_cast<const uint4*>(bias8 + g * 8), b);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += b[q];
+            for (int q = 0; q < 8; q += 2)
+                f2_unpack(f2_add(f2_pack(acc[g * 8 + q], acc[g * 8 + q + 1]), f2_pack(b[q], b[q + 1])), acc[g * 8 + q],
+                          acc[g * 8 + q + 1]);
         }
     }
     const bool deriv = S::aux_deriv(p);
     if (S::aux_out(p) && deriv && act == CME_ACT_GELU) {
         // activation and its derivative from one tanh; the derivative is what backward multiplies by
 #pragma unroll
-        for (int j = 0; j < 32; ++j) gelu_and_grad_fast(acc[j], acc[j], pre[j]);
+        for (int j = 0; j < 32; j += 2) gelu_and_grad_fast2(acc[j], acc[j + 1], pre[j], pre[j + 1]);
     } else {
         if (S::aux_out(p)) {
 #pragma unroll
@@ -310,11 +312,17 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
         for (int g = 0; g < 4; ++g) {
             float x[8];
             if (in_kind == 1) unpack8(in_raw[g], x); else load8_guard(X, n + g * 8, p.N, row_ok, x);
+            if (dact != CME_ACT_RELU && deriv) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-                acc[g * 8 + q] = (dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
-                                 : deriv              ? acc[g * 8 + q] * x[q]
-                                                      : acc[g * 8 + q] * dgelu_fast(x[q]);
+                for (int q = 0; q < 8; q += 2)
+                    f2_unpack(f2_mul(f2_pack(acc[g * 8 + q], acc[g * 8 + q + 1]), f2_pack(x[q], x[q + 1])), acc[g * 8 + q],
+                              acc[g * 8 + q + 1]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    acc[g * 8 + q] = (dact == CME_ACT_RELU) ? (x[q] > 0.f ? acc[g * 8 + q] : 0.f)
+                                                            : acc[g * 8 + q] * dgelu_fast(x[q]);
+            }
         }
     }
     if (S::residual(p)) {
@@ -324,7 +332,9 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& p, float* acc, fl
             float x[8];
             if (in_kind == 2) unpack8(in_raw[g], x); else load8_guard(R, n + g * 8, p.N, row_ok, x);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) acc[g * 8 + q] += x[q];
+            for (int q = 0; q < 8; q += 2)
+                f2_unpack(f2_add(f2_pack(acc[g * 8 + q], acc[g * 8 + q + 1]), f2_pack(x[q], x[q + 1])), acc[g * 8 + q],
+                          acc[g * 8 + q + 1]);
         }
     }
     if (S::accumulate(p)) {
