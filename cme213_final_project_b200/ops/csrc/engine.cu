@@ -258,6 +258,13 @@ void fill_attn(const Engine& e, int l, CmeAttn& a) {
 
 #define TRY(expr) do { int rc__ = (expr); if (rc__) return rc__; } while (0)
 
+// CME213_FFN_COLSUM=0: the gradient of b1 as a column-sum kernel on the second stream instead of inside the epilogue
+// of the product that makes d ff_pre (for A/B measurements).
+bool ffn_colsum() {
+    static const bool on = !(getenv("CME213_FFN_COLSUM") && getenv("CME213_FFN_COLSUM")[0] == '0');
+    return on;
+}
+
 // CME213_FFN_DERIV=0 goes back to keeping the pre-activation and re-evaluating the derivative in backward, with the
 // bias gradient as a separate column-sum kernel (for A/B measurements of the fused form).
 bool ffn_deriv() {
@@ -541,7 +548,8 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         } else {
             if (fused) {
                 TRY(gemm(e, st, BT, FF, D, dx, D, 0, e.P(s.W2), D, 1, e.dff, FF, 0, nullptr, 0, nullptr, d.act, aux, FF, nullptr,
-                         0, 1, 0, 0, 0, /*aux_deriv=*/deriv ? 1 : 0, deriv ? e.slab_scratch : nullptr, &slabs));
+                         0, 1, 0, 0, 0, /*aux_deriv=*/deriv ? 1 : 0, deriv && ffn_colsum() ? e.slab_scratch : nullptr,
+                         &slabs));
             } else {
                 // plain product, then the derivative and the bias gradient in one element-wise pass (the reference's
                 // fused_relu_backward_bias_backward_kernel, FINAL_CLEAN_CODE_/src/kernels/activations.cu:247-283)

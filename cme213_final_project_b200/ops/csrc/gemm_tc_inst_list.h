@@ -65,6 +65,7 @@ CME_GEMM_TC_EXTERN(64, false, false, SPEC_BIAS_GELU_AUXD)
 CME_GEMM_TC_EXTERN(256, false, true, SPEC_DMUL_COLSUM)
 CME_GEMM_TC_EXTERN(128, false, false, SPEC_DMUL_COLSUM)
 CME_GEMM_TC_EXTERN(64, false, false, SPEC_DMUL_COLSUM)
+CME_GEMM_TC_EXTERN(256, false, true, SPEC_DMUL)            // same without the column sums (caller sums C itself)
 #endif
 #if CME_GEMM_TC_GROUP == -1 || CME_GEMM_TC_GROUP == 10     // ReLU derivative with column sums
 CME_GEMM_TC_EXTERN(256, false, true, SPEC_DRELU_COLSUM)

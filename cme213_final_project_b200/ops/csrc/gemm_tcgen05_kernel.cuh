@@ -895,6 +895,7 @@ constexpr int SPEC_TF32 = (1 << 11) | (1 << 14);      // fp32 operands multiplie
 // the pair the transformer's MLP uses: forward leaves GELU'(pre-activation), backward multiplies by it and sums columns
 constexpr int SPEC_BIAS_GELU_AUXD = spec_pack(true, CME_ACT_GELU, 0, false, false, true, 0, true, true);
 constexpr int SPEC_DMUL_COLSUM = spec_pack(false, 0, CME_ACT_GELU, false, false, false, 1, false, true, true);
+constexpr int SPEC_DMUL = spec_pack(false, 0, CME_ACT_GELU, false, false, false, 1, false, true, false);
 constexpr int SPEC_DRELU_COLSUM = spec_pack(false, 0, CME_ACT_RELU, false, false, false, 1, false, false, true);
 constexpr int SPEC_ACC = spec_pack(false, 0, 0, false, true, false, 3, false);
 
