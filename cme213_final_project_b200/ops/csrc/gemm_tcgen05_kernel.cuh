@@ -51,6 +51,15 @@ constexpr int NUM_THREADS_WIDE = 320;     // ... + 8 epilogue warps (two per sch
 // chunks ahead (across tile boundaries), and the bias of the next tile is read while the current one is processed.
 // The plain epilogue only stores (NB = 2).
 constexpr int SMEM_LIMIT = 232448;     // 227 KB per CTA
+// Ring buffers per epilogue warp of the compile-time variants with a TMA-fed input / a second output.  Deeper rings
+// (3 / 4) were measured slower at the GPT-2 small shapes: they cost the main loop one of its four stages
+// (bias + GELU + derivative 86 -> 98 us, bias + residual 68 -> 74 us).
+#ifndef CME_GEMM_NB_IN
+#define CME_GEMM_NB_IN 2
+#endif
+#ifndef CME_GEMM_NB_AUX
+#define CME_GEMM_NB_AUX 2
+#endif
 template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
     static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN;       // B columns staged by this CTA
     static constexpr bool TF32 = spec_tf32(SPEC);
@@ -67,7 +76,9 @@ template <int BN, bool PAIR, bool SIMPLE, int SPEC = -1> struct Cfg {
     static constexpr bool WIDE = !SIMPLE && SPEC >= 0 && (((SPEC >> 8) & 3) != 0 || ((SPEC >> 10) & 1) != 0);
     static constexpr int EPI_WARPS = WIDE ? 8 : 4;
     static constexpr int THREADS = WIDE ? NUM_THREADS_WIDE : NUM_THREADS;
-    static constexpr int NB = SIMPLE ? 2 : SPEC < 0 ? 3 : 2;
+    static constexpr bool IN_FED = !SIMPLE && SPEC >= 0 && ((SPEC >> 8) & 3) != 0;     // an operand arrives through the ring
+    static constexpr bool AUX_RING = !SIMPLE && SPEC >= 0 && ((SPEC >> 10) & 1) != 0;  // a second output leaves through it
+    static constexpr int NB = SIMPLE ? 2 : SPEC < 0 ? 3 : AUX_RING ? CME_GEMM_NB_AUX : IN_FED ? CME_GEMM_NB_IN : 2;
     static constexpr int AUX_ALLOW = (NB - 2) / 2;    // bulk groups that may still be reading when a chunk takes 2 buffers
     static constexpr int WARP_RING_BYTES = NB * 4096;
     static constexpr int STAGING_BYTES = EPI_WARPS * WARP_RING_BYTES;
