@@ -53,6 +53,8 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--single-bucketed", action="store_true",
                     help="one GPU: apply AdamW bucket by bucket on a second stream during backward")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-nccl-baseline", action="store_true",
+                    help="N > 1: skip the short second run of the same engine on the NCCL all-reduce path")
     ap.add_argument("--sync-mode", default="overlap", choices=["overlap", "blocking"])
     return ap.parse_args()
 
@@ -170,6 +172,36 @@ def main() -> int:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         exposed_ms = t.item()
 
+    # ---- the same engine with host-issued NCCL all-reduces and a separate AdamW pass, same ranks, same box: what the
+    # fused path is measured against (a second model instance; a failure here leaves the main numbers alone) -------
+    sync_label = (f"{ctx.backend}/{run.sync_mode}/bucket_mb={a.bucket_mb}" if world > 1 else
+                  "single rank: " + ("AdamW per bucket on a second stream under backward"
+                                     if fused is not None else "separate AdamW kernel"))
+    sync_detail = ctx.backend_note or None
+    nccl_ms, nccl_note = None, None
+    if world > 1 and a.comm == "fused" and not a.no_nccl_baseline:
+        try:
+            import dataclasses
+            run2 = dataclasses.replace(run, comm_backend="nccl")
+            model2 = build_model(cfg, optim, run2, ctx, seed=42)
+            trainer2 = Trainer(model2, ctx, run2, optim)
+            n2, w2 = min(a.steps, 10), 3
+            for s in range(w2):
+                trainer2.step([dx[s * accum + i] for i in range(accum)], [dy[s * accum + i] for i in range(accum)])
+            barrier()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record()
+            for s in range(w2, w2 + n2):
+                trainer2.step([dx[s * accum + i] for i in range(accum)], [dy[s * accum + i] for i in range(accum)])
+            f1.record()
+            barrier()
+            t = torch.tensor([f0.elapsed_time(f1) / n2], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            nccl_ms, nccl_note = t.item(), f"{n2} steps after {w2} warm-up, eager, overlapped bucketed all-reduce + AdamW kernel"
+            del trainer2, model2
+        except Exception as exc:                                  # noqa: BLE001
+            nccl_note = f"not measured: {type(exc).__name__}: {exc}"
+
     # ---- validity: status words (max over ranks) and the cross-rank parameter checksum span -------------------
     st = torch.tensor([ops.gemm_check_status(), ops.attention_check_status(),
                        fused.check_status() if fused is not None else 0], dtype=torch.int32, device=dev)
@@ -198,10 +230,7 @@ def main() -> int:
             "impl": "ours",
             "config": {"model": a.config, "global_batch": cfg.batch_size * accum * world, "seq_len": cfg.seq_len,
                        "micro_batch_per_gpu": cfg.batch_size, "grad_accum": accum,
-                       "parallelism": f"dp{world}", "sync": (f"{ctx.backend}/{run.sync_mode}/bucket_mb={a.bucket_mb}" if world > 1 else
-                                "single rank: " + ("AdamW per bucket on a second stream under backward"
-                                                   if fused is not None else "separate AdamW kernel")),
-                       "sync_detail": ctx.backend_note or None,
+                       "parallelism": f"dp{world}", "sync": sync_label, "sync_detail": sync_detail,
                        "cuda_graph": bool(graphed), "optimizer": "adamw" if optim.weight_decay > 0 else "adam+clip",
                        "l2": "per-step working set (activations + weights, several GB) is far larger than the 126 MB L2"},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
@@ -209,6 +238,7 @@ def main() -> int:
                     "h2d_bytes_per_step": 2 * accum * BT * 4, "d2h_bytes_per_step": 4,
                     "clocks": {"sm_mhz": clocks_e2e["sm_mhz"], "reasons": clocks_e2e["reasons"]}},
             "gpu_launches": int(launches),
+            "nccl_path": {"ms_per_step": nccl_ms, "note": nccl_note},
             "exposed_comm_ms_per_step": exposed_ms,
             "comm_timeline_ms": timeline,
             "loss": last_loss[0], "loss_resident": loss_resident,

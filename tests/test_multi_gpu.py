@@ -144,6 +144,7 @@ def test_peer_memory_collectives_and_fused_sync():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "MP_RESULT" in r.stdout
+    print("\n".join(l for l in r.stdout.splitlines() if l.startswith("MP_RESULT")))     # shown with pytest -s
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
