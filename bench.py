@@ -164,13 +164,18 @@ def main() -> int:
 
     # ---- exposed gradient-synchronisation time of the last timed step, from device timestamps written inside the
     # (replayed) step: end of the last synchronisation kernel minus end of backward, max over ranks ---------------
-    exposed_ms, timeline = None, None
+    exposed_ms, exposed_min_ms, timeline = None, None, None
     if fused is not None:
         timeline = fused.timeline()
         t = torch.tensor([timeline["exposed_ms"]], dtype=torch.float64, device=dev)
+        tmin = t.clone()
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        exposed_ms = t.item()
+            dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        # The maximum is the rank that reached the end of backward first: its last bucket kernel also waits for the
+        # slowest rank (the GPUs settle at different clocks under their power caps and the compute streams only meet
+        # at the end of the step).  The minimum is the rank everyone waits for: what the synchronisation itself costs.
+        exposed_ms, exposed_min_ms = t.item(), tmin.item()
 
     # ---- the same engine with host-issued NCCL all-reduces and a separate AdamW pass, same ranks, same box: what the
     # fused path is measured against (a second model instance; a failure here leaves the main numbers alone) -------
@@ -239,7 +244,7 @@ def main() -> int:
                     "clocks": {"sm_mhz": clocks_e2e["sm_mhz"], "reasons": clocks_e2e["reasons"]}},
             "gpu_launches": int(launches),
             "nccl_path": {"ms_per_step": nccl_ms, "note": nccl_note},
-            "exposed_comm_ms_per_step": exposed_ms,
+            "exposed_comm_ms_per_step": exposed_ms, "exposed_comm_ms_slowest_rank": exposed_min_ms,
             "comm_timeline_ms": timeline,
             "loss": last_loss[0], "loss_resident": loss_resident,
             "device_status": gemm_status, "attn_status": attn_status, "comm_status": comm_status,
