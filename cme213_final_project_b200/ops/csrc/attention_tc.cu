@@ -114,7 +114,7 @@ constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O accumulator: [128,19
 static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM's shared memory");
 static_assert(128 + HD <= FWD_TMEM_COLS && 2 * FWD_TMEM_COLS <= 512, "forward TMEM budget: S + O per CTA, two CTAs per SM");
 #ifndef CME_ATTN_FWD_POLY_PAIRS
-#define CME_ATTN_FWD_POLY_PAIRS 2
+#define CME_ATTN_FWD_POLY_PAIRS 1
 #endif
 constexpr int FWD_POLY_PAIRS = CME_ATTN_FWD_POLY_PAIRS;   // of every 4 score pairs, how many take 2^x on the FMA pipe
 constexpr float RESCALE_THRESHOLD = 8.f;   // log2 units: the running maximum is only raised when it grows by > 2^8
@@ -285,23 +285,29 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             F32x2 sum2[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) sum2[c] = f2_splat(0.f);
+            // In passes over 32 keys, so that the 16 scale-and-shifts, then the 32 exponentials, then the sums and
+            // stores are each a run of independent instructions (no exponential waits for its own operand or result)
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {                 // 16 groups of 8 keys = 16-byte chunks of the P row
-                float pr[8];
+            for (int c = 0; c < 4; ++c) {
+                float* x = reinterpret_cast<float*>(r + c * 32);
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    float a0, a1;
-                    f2_unpack(f2_fma(f2_pack(__uint_as_float(r[g * 8 + i]), __uint_as_float(r[g * 8 + i + 1])), sc2, nm2),
-                              a0, a1);
-                    if (i < 2 * FWD_POLY_PAIRS) {
-                        ex2_poly2(a0, a1, pr[i], pr[i + 1]);
+                for (int i = 0; i < 32; i += 2) f2_unpack(f2_fma(f2_pack(x[i], x[i + 1]), sc2, nm2), x[i], x[i + 1]);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    if ((i & 7) < 2 * FWD_POLY_PAIRS) {
+                        ex2_poly2(x[i], x[i + 1], x[i], x[i + 1]);
                     } else {
-                        pr[i] = ex2_approx(a0);
-                        pr[i + 1] = ex2_approx(a1);
+                        x[i] = ex2_approx(x[i]);
+                        x[i + 1] = ex2_approx(x[i + 1]);
                     }
-                    sum2[i >> 1] = f2_add(sum2[i >> 1], f2_pack(pr[i], pr[i + 1]));
                 }
-                *reinterpret_cast<uint4*>(sP + (g >> 3) * TILE_BYTES + swz(row, g & 7)) = pack8(pr);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) sum2[(i >> 1) & 3] = f2_add(sum2[(i >> 1) & 3], f2_pack(x[i], x[i + 1]));
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {              // 16-byte chunks of the P row
+                    const int gg = c * 4 + g;
+                    *reinterpret_cast<uint4*>(sP + (gg >> 3) * TILE_BYTES + swz(row, gg & 7)) = pack8(x + g * 8);
+                }
             }
             {
                 float s0, s1;
