@@ -1,6 +1,6 @@
 // Fused flash-style attention on the 5th-generation tensor cores (head size 64, bf16, causal or not, both
-// head layouts): scores and output partials live in TMEM, probabilities go to the second MMA through shared
-// memory, nothing of size T x T reaches global memory, only the per-row log-sum-exp is saved for backward.
+// head layouts): scores, probabilities (forward) and output partials live in TMEM, nothing of size T x T reaches
+// global memory, only the per-row log-sum-exp is saved for backward.
 //
 // Replaces the reference's production attention -- two strided-batched GEMMs around an in-place softmax
 // with P, dP and dS materialised as [B*H, T, T] buffers, and four more batched GEMMs plus a dS kernel in
@@ -9,8 +9,10 @@
 // Forward, per CTA = one (batch, head) and 128 queries; 4 softmax warps (thread = query row) + 1 warp whose
 // lane 0 issues TMA loads and tcgen05.mma:
 //     S_j = Q K_j^T (TMEM) -> copied to registers (the tensor core starts S_{j+1} at once) -> online softmax with a
-//     lazily raised reference maximum -> P_j (bf16, shared, swizzled K-major) -> O += P_j V_j (TMEM accumulator,
-//     rescaled in place only when the reference maximum is raised)
+//     lazily raised reference maximum; a quarter of the exponentials are a packed cubic on the FMA pipe, the rest go
+//     to the special-function unit -> P_j (bf16 pairs) written back to tensor memory with tcgen05.st
+//     -> O += P_j V_j with the A operand read from tensor memory (P never passes through shared memory; TMEM
+//     accumulator, rescaled in place only when the reference maximum is raised)
 // Backward, per CTA = one (batch, head) and 128 keys, looping over query blocks (thread = query row, so the
 // row's log-sum-exp and delta are two registers):
 //     S = Q_i K^T,  dP = dO_i V^T (TMEM)  ->  P, dS (bf16, shared, double buffered)
@@ -107,12 +109,13 @@ struct FwdParams {
 // ------------------------------------------------------------------------------------------------------
 // Forward
 // ------------------------------------------------------------------------------------------------------
-// shared: Q 16K | K[2] 32K | V[2] 32K | P 32K | barriers
-constexpr int FWD_SMEM = 7 * TILE_BYTES + 128;      // two CTAs per SM must fit: 2 x (this + 1 KB reserved) <= 228 KB
+// shared: Q 16K | K[2] 32K | V[2] 32K | barriers      (P never passes through shared memory)
+constexpr int FWD_SMEM = 5 * TILE_BYTES + 128;      // two CTAs per SM must fit: 2 x (this + 1 KB reserved) <= 228 KB
 constexpr int FWD_THREADS = 160;
-constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O accumulator: [128,192)
+constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O accumulator: [128,192)  P (bf16 pairs): [192,256)
 static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM's shared memory");
-static_assert(128 + HD <= FWD_TMEM_COLS && 2 * FWD_TMEM_COLS <= 512, "forward TMEM budget: S + O per CTA, two CTAs per SM");
+static_assert(128 + HD + BKV / 2 <= FWD_TMEM_COLS && 2 * FWD_TMEM_COLS <= 512,
+              "forward TMEM budget: S + O + P per CTA, two CTAs per SM");
 #ifndef CME_ATTN_FWD_POLY_PAIRS
 #define CME_ATTN_FWD_POLY_PAIRS 1
 #endif
@@ -131,14 +134,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + TILE_BYTES;            // 2 stages
     uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
-    uint8_t* sP = sV + 2 * TILE_BYTES;        // 2 atoms of 64 keys (also the output staging area)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TILE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * TILE_BYTES);
     uint64_t* q_full = bars;                  // 1
     uint64_t* kv_full = bars + 1;             // [2]
     uint64_t* kv_empty = bars + 3;            // [2]
     uint64_t* s_full = bars + 5;              // S ready for softmax
     uint64_t* s_free = bars + 6;              // S copied to registers (128 arrivals): the next S may be issued
-    uint64_t* p_ready = bars + 7;             // P written, O rescaled (128 arrivals)
+    uint64_t* p_ready = bars + 7;             // P written to tensor memory, O rescaled (128 arrivals)
     uint64_t* o_full = bars + 8;              // P V accumulated, P consumed
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -164,7 +166,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128, tmem_P = tmem_base + 128 + HD;
     pdl_wait();        // barrier set-up and TMEM allocation above may overlap the tail of the previous kernel
 
     if (warp == 4) {
@@ -184,7 +186,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const uint64_t dQ_ = make_smem_desc(smem_u32(sQ), 0, 1024);
             const uint64_t dK0 = make_smem_desc(smem_u32(sK), 0, 1024);
             const uint64_t dV0 = make_smem_desc(smem_u32(sV), TILE_BYTES, 1024);
-            const uint64_t dP_ = make_smem_desc(smem_u32(sP), 0, 1024);
             auto issue_s = [&](int j) {
                 const uint64_t kd = desc_add(dK0, (j & 1) * TILE_BYTES);
 #pragma unroll
@@ -209,9 +210,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tc_fence_after();
                 const uint64_t vd = desc_add(dV0, st * TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < BKV / 16; ++k)
-                    mma_f16_ss(tmem_O, desc_add(dP_, (k >> 2) * TILE_BYTES + (k & 3) * 32), desc_add(vd, k * 2048),
-                               idesc_o, (j > 0 || k > 0));
+                for (int k = 0; k < BKV / 16; ++k)       // A = P from tensor memory: 16 keys = 8 columns per step
+                    mma_f16_ts(tmem_O, tmem_P + k * 8, desc_add(vd, k * 2048), idesc_o, (j > 0 || k > 0));
                 mma_commit(o_full);
                 mma_commit(&kv_empty[st]);
                 if (j + 2 < nkv) {
@@ -303,19 +303,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) sum2[(i >> 1) & 3] = f2_add(sum2[(i >> 1) & 3], f2_pack(x[i], x[i + 1]));
+                // 32 probabilities = 16 columns of bf16 pairs, straight into the A operand of the P V product
+                uint32_t pw[16];
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {              // 16-byte chunks of the P row
-                    const int gg = c * 4 + g;
-                    *reinterpret_cast<uint4*>(sP + (gg >> 3) * TILE_BYTES + swz(row, gg & 7)) = pack8(x + g * 8);
-                }
+                for (int i = 0; i < 16; ++i) pw[i] = f2_to_bf2(x[2 * i], x[2 * i + 1]);
+                tmem_st16(tmem_P + lane_addr + c * 16, pw);
             }
+            tmem_wait_st();
             {
                 float s0, s1;
                 f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), s0, s1);
                 l += s0 + s1;
             }
             tc_fence_before();
-            fence_proxy_async();
             mbar_arrive(p_ready);
         }
         if (ok && nkv > 0) {
@@ -333,8 +333,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
                 for (int i = 0; i < HD; ++i) o[i] *= inv;
-                // stage this warp's 32 rows (P is free now) and store them with one TMA tile store
-                uint8_t* stage = sP + warp * 4096;
+                // stage this warp's 32 rows (every product is complete and no load is in flight: the first K stage is
+                // free) and store them with one TMA tile store
+                uint8_t* stage = sK + warp * 4096;
 #pragma unroll
                 for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(stage + swz(lane, g)) = pack8(o + g * 8);
                 fence_proxy_async();
