@@ -35,3 +35,19 @@ def test_trajectory_parse_and_compare():
     c = compare_trajectories(ta, tb)
     assert c["ok"] and c["max_sum_span"] == 1e-6
     assert not compare_trajectories(ta, tb[:2])["ok"]
+
+
+def test_trajectory_comparison_has_two_levels():
+    """Same arithmetic in another schedule must reproduce the sums; different arithmetic (bf16 gradient sums taken in
+    another order, amplified by Adam on near-zero gradients) may move the plain sum -- a residual of cancelling
+    values -- while loss, sum of squares and largest magnitude agree."""
+    mk = lambda s, sq, mx, loss: "\n".join(
+        ckpt.trajectory_line(1, i + 1, loss, ckpt.ParamStats(s, sq, mx, 0x1), (0.0, 0.0, 0.0)) for i in range(2))
+    base = parse_trajectory(mk(-0.14, 812.0, 0.25, 3.9))
+    same = compare_trajectories(base, parse_trajectory(mk(-0.14, 812.0, 0.25, 3.9)), n_params=222592)
+    assert same["identical_path"] and same["ok"] and same["max_sum_diff_per_param"] == 0.0
+    moved = compare_trajectories(base, parse_trajectory(mk(-0.17, 812.9, 0.2501, 3.9004)), n_params=222592)
+    assert moved["ok"] and not moved["identical_path"]
+    assert abs(moved["max_sum_diff_per_param"] - 0.03 / 222592) < 1e-12
+    off = compare_trajectories(base, parse_trajectory(mk(-0.14, 840.0, 0.25, 3.9)))
+    assert not off["ok"] and "max_sum_diff_per_param" not in off
