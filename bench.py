@@ -53,8 +53,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--single-bucketed", action="store_true",
                     help="one GPU: apply AdamW bucket by bucket on a second stream during backward")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--no-nccl-baseline", action="store_true",
-                    help="N > 1: skip the short second run of the same engine on the NCCL all-reduce path")
+    ap.add_argument("--nccl-baseline", action="store_true",
+                    help="N > 1: after the timed regions, also time a short run of the same engine on the NCCL "
+                         "all-reduce path (a second model instance) and report it as nccl_path")
     ap.add_argument("--sync-mode", default="overlap", choices=["overlap", "blocking"])
     return ap.parse_args()
 
@@ -184,7 +185,7 @@ def main() -> int:
                                      if fused is not None else "separate AdamW kernel"))
     sync_detail = ctx.backend_note or None
     nccl_ms, nccl_note = None, None
-    if world > 1 and a.comm == "fused" and not a.no_nccl_baseline:
+    if world > 1 and a.comm == "fused" and a.nccl_baseline:
         try:
             import dataclasses
             run2 = dataclasses.replace(run, comm_backend="nccl")
