@@ -109,8 +109,10 @@ struct FwdParams {
 // ------------------------------------------------------------------------------------------------------
 // Forward
 // ------------------------------------------------------------------------------------------------------
-// shared: Q 16K | K[2] 32K | V[2] 32K | barriers      (P never passes through shared memory)
-constexpr int FWD_SMEM = 5 * TILE_BYTES + 128;      // two CTAs per SM must fit: 2 x (this + 1 KB reserved) <= 228 KB
+// shared: Q 16K | K[3] 48K | V[3] 48K | barriers      (P never passes through shared memory)
+constexpr int FWD_KV_STAGES = 3;           // a K / V tile is requested two blocks ahead of its use: its ~1200-clock
+                                           // latency no longer delays the next S product
+constexpr int FWD_SMEM = (1 + 2 * FWD_KV_STAGES) * TILE_BYTES + 128;   // two CTAs per SM: 2 x (this + 1 KB) <= 228 KB
 constexpr int FWD_THREADS = 160;
 constexpr int FWD_TMEM_COLS = 256;         // S: [0,128)  O accumulator: [128,192)  P (bf16 pairs): [192,256)
 static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM's shared memory");
@@ -132,17 +134,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         return;
     }
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + TILE_BYTES;            // 2 stages
-    uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * TILE_BYTES);
+    uint8_t* sK = sQ + TILE_BYTES;                            // FWD_KV_STAGES stages
+    uint8_t* sV = sK + FWD_KV_STAGES * TILE_BYTES;            // FWD_KV_STAGES stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + FWD_KV_STAGES * TILE_BYTES);
     uint64_t* q_full = bars;                  // 1
-    uint64_t* kv_full = bars + 1;             // [2]
-    uint64_t* kv_empty = bars + 3;            // [2]
-    uint64_t* s_full = bars + 5;              // S ready for softmax
-    uint64_t* s_free = bars + 6;              // S copied to registers (128 arrivals): the next S may be issued
-    uint64_t* p_ready = bars + 7;             // P written to tensor memory, O rescaled (128 arrivals)
-    uint64_t* o_full = bars + 8;              // P V accumulated, P consumed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t* kv_full = bars + 1;             // [3]
+    uint64_t* kv_empty = bars + 4;            // [3]
+    uint64_t* s_full = bars + 7;              // S ready for softmax
+    uint64_t* s_free = bars + 8;              // S copied to registers (128 arrivals): the next S may be issued
+    uint64_t* p_ready = bars + 9;             // P written to tensor memory, O rescaled (128 arrivals)
+    uint64_t* o_full = bars + 10;             // P V accumulated, P consumed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,7 +156,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < FWD_KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
         mbar_init(s_full, 1);
         mbar_init(s_free, 128);
         mbar_init(p_ready, 128);
@@ -178,7 +180,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_arrive_expect_tx(q_full, TILE_BYTES);
             tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
             auto load_kv = [&](int j) {
-                const int st = j & 1;
+                const int st = j % FWD_KV_STAGES;
                 mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
                 tma_load_4d(sK + st * TILE_BYTES, &tmK, &kv_full[st], 0, j * BKV, h, b);
                 tma_load_4d(sV + st * TILE_BYTES, &tmV, &kv_full[st], 0, j * BKV, h, b);
@@ -187,22 +189,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const uint64_t dK0 = make_smem_desc(smem_u32(sK), 0, 1024);
             const uint64_t dV0 = make_smem_desc(smem_u32(sV), TILE_BYTES, 1024);
             auto issue_s = [&](int j) {
-                const uint64_t kd = desc_add(dK0, (j & 1) * TILE_BYTES);
+                const uint64_t kd = desc_add(dK0, (j % FWD_KV_STAGES) * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
                     mma_f16_ss(tmem_S, desc_add(dQ_, k * 32), desc_add(kd, k * 32), idesc_s, k > 0);
                 mma_commit(s_full);
             };
-            load_kv(0);
-            if (nkv > 1) load_kv(1);
+            for (int j = 0; j < FWD_KV_STAGES && j < nkv; ++j) load_kv(j);
             ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
             if (ok) { tc_fence_after(); issue_s(0); }
             for (int j = 0; j < nkv && ok; ++j) {
-                const int st = j & 1;
+                const int st = j % FWD_KV_STAGES;
+                if (j >= 1 && j + 2 < nkv) {
+                    // the stage that block j - 1 used is refilled with block j + 2: its P V product was issued one
+                    // block ago, so this wait does not hold anything up
+                    if (!mbar_wait(&kv_empty[(j - 1) % FWD_KV_STAGES], ((j - 1) / FWD_KV_STAGES) & 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    load_kv(j + 2);
+                }
                 if (j + 1 < nkv) {
                     // S_j sits in registers now: the tensor core computes S_{j+1} while softmax_j runs
                     if (!mbar_wait(s_free, j & 1, abort_flag) ||
-                        !mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                        !mbar_wait(&kv_full[(j + 1) % FWD_KV_STAGES], ((j + 1) / FWD_KV_STAGES) & 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
@@ -214,10 +227,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     mma_f16_ts(tmem_O, tmem_P + k * 8, desc_add(vd, k * 2048), idesc_o, (j > 0 || k > 0));
                 mma_commit(o_full);
                 mma_commit(&kv_empty[st]);
-                if (j + 2 < nkv) {
-                    if (!mbar_wait(&kv_empty[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
-                    load_kv(j + 2);
-                }
             }
             if (!ok) for (int i = 0; i < 2000; ++i) __nanosleep(500);
         }
