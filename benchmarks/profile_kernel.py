@@ -5,7 +5,7 @@ Role of the reference's profiler drivers (FINAL_CLEAN_CODE_/scripts/profile_fusi
 CUDA-event timing when ncu is refused; profile_training_hotspots.sh:50-58 wraps ncu around a dedicated driver;
 summarize_fusion_profiles.py / roofline_fusion_analysis.py turn the raw CSV into roofline rows).
 
-    python benchmarks/profile_kernel.py --kernel attn_fwd_tc --skip 2 --count 1 --out gpurun_out/prof_attn_fwd \
+    python benchmarks/profile_kernel.py --kernel attn_fwd_tc --skip 2 --count 1 --out prof_attn_fwd \
         -- python benchmarks/bench_attention.py --iters 2
 
 Rules this wrapper enforces, because a profiler run that goes wrong can take a shared GPU down with it:
