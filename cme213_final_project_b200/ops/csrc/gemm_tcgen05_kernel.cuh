@@ -596,6 +596,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ++f_cnt;
             f_c += ESETS;
         };
+        constexpr bool FETCH_AT_TOP = C::NB == 2;
         if (in_kind) {
             for (int i = 0; i < C::NB - 1; ++i) fetch_next();
         }
@@ -735,6 +736,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (n >= p.N) break;
                     uint8_t* sbC = ring + (slot % C::NB) * 4096;
                     uint8_t* sbX = ring + ((slot + 1) % C::NB) * 4096;
+                    if (in_kind && FETCH_AT_TOP) {
+                        // Two buffers: the other one holds the previous chunk, whose copy-out was issued a moment ago.  As
+                        // soon as the copy engine has read it (a short wait) the next chunk's input is requested into it,
+                        // and arrives while this chunk is processed -- instead of being requested after this chunk and
+                        // awaited at once with its full latency.
+                        if (lane == 0) tma_store_wait_read<0>();
+                        __syncwarp();
+                        fetch_next();
+                    }
                     if (in_kind) {
                         if (!mbar_wait(&my_in_bar[slot % C::NB], (slot / C::NB) & 1, abort_flag)) { ok = false; break; }
                     }
@@ -818,8 +828,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                     }
                     slot += aux_ring ? 2 : 1;
-                    if (in_kind) {
-                        // refill the buffer stored one chunk ago with the chunk NB - 1 ahead
+                    if (in_kind && !FETCH_AT_TOP) {
+                        // three buffers: refill the one stored one chunk ago with the chunk two ahead
                         if (lane == 0) tma_store_wait_read<1>();
                         __syncwarp();
                         fetch_next();
