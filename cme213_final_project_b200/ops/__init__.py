@@ -365,7 +365,7 @@ class CmeAttn(ctypes.Structure):
         ("d_o", ctypes.c_void_p), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
         ("delta", ctypes.c_void_p), ("dq_accum", ctypes.c_void_p),
         ("ws", ctypes.c_void_p), ("ws_bytes", ctypes.c_longlong),
-        ("dq_sem", ctypes.c_void_p), ("dq_mode", ctypes.c_int),
+        ("dq_sem", ctypes.c_void_p), ("dq_mode", ctypes.c_int), ("dq_accum_clean", ctypes.c_int),
     ]
 
 

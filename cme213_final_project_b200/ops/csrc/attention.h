@@ -34,6 +34,8 @@ struct CmeAttn {
                                  //   1  the parts are added in a fixed order (bit-reproducible); key block 0 finishes
                                  //   2  arrival order; the CTA whose part comes last scales, casts and writes zeros back:
                                  //      dq_accum must be zero before the first launch and is zero after every launch
+    int dq_accum_clean;          // dq_mode 0: non-zero = the caller has cleared dq_accum itself (e.g. on another stream,
+                                 // ahead of time); the launch then skips its own clear
 };
 
 constexpr int CME_ATTN_FINISH_MAX_QBLOCKS = 64;      // dq_mode 2: query blocks (of 128 rows) per sequence

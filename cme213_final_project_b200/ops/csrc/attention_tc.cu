@@ -973,7 +973,7 @@ int attention_tc_bwd(const CmeAttn* a, cudaStream_t st) {
                 "attention backward: dq_mode 1 and 2 need the counter array");
     CME_REQUIRE(mode != 2 || cme_cdiv(a->T, BQ) <= CME_ATTN_FINISH_MAX_QBLOCKS, CME_ERR_LIMIT,
                 "attention backward: dq_mode 2 handles up to %d query blocks", CME_ATTN_FINISH_MAX_QBLOCKS);
-    if (mode == 0) CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
+    if (mode == 0 && !a->dq_accum_clean) CME_CUDA(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * HD * sizeof(float), st));
     static bool attr[CME_MAX_DEVICES] = {};               // function attributes are per device
     int dev = 0;
     CME_CUDA(cudaGetDevice(&dev));

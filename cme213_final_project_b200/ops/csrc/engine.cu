@@ -94,6 +94,9 @@ struct Engine {
     // backward temporaries
     char *dxa, *dxb, *dff, *dln, *dqkv, *dattn;
     float *delta, *dq_accum, *ln_scratch, *col_scratch;
+    float* dq_accum2 = nullptr;     // second dQ scratch: the layers alternate, so that a layer's scratch can be cleared on the
+                                    // second stream while the layer above still uses the other one
+    cudaEvent_t ev_dq[4] = {};      // [0..1] scratch b was converted (main stream)   [2..3] scratch b is clear (second stream)
     int* dq_sem = nullptr;          // per (batch, head, query block) counters ordering the dQ parts; zero between launches
     void* attn_ws; long long attn_ws_bytes;
     void* gemm_ws; long long gemm_ws_bytes;
@@ -150,6 +153,7 @@ size_t carve(Engine& e, char* base) {
     e.dattn = take(BT * D * es);
     e.delta = (float*)take((size_t)e.BH * d.T * 4);
     e.dq_accum = (float*)take(BT * D * 4);
+    e.dq_accum2 = (float*)take(BT * D * 4);
     e.dq_sem = (int*)take((size_t)e.BH * ((d.T + 127) / 128) * 4);
     e.attn_ws_bytes = (d.head_flat && d.T <= 512) ? attention_gemm_ws_bytes(e.BH, d.T) : 0;
     e.attn_ws = e.attn_ws_bytes ? take((size_t)e.attn_ws_bytes) : nullptr;
@@ -305,12 +309,14 @@ CME_API int cme_engine_bind(void* h, void* params, void* grads, void* workspace,
     // the attention backward's counters and its dQ scratch start at zero; every launch leaves them at zero again
     CME_CUDA(cudaMemset(e->dq_sem, 0, (size_t)e->BH * ((e->d.T + 127) / 128) * 4));
     CME_CUDA(cudaMemset(e->dq_accum, 0, (size_t)e->BT * e->d.D * 4));
+    CME_CUDA(cudaMemset(e->dq_accum2, 0, (size_t)e->BT * e->d.D * 4));
     return CME_OK;
 }
 
 CME_API void cme_engine_destroy(void* h) {
     Engine* e = static_cast<Engine*>(h);
     for (cudaEvent_t v : e->ev) cudaEventDestroy(v);
+    for (cudaEvent_t v : e->ev_dq) if (v) cudaEventDestroy(v);
     if (e->side) cudaStreamDestroy(e->side);
     delete e;
 }
@@ -323,9 +329,11 @@ CME_API int cme_engine_set_overlap(void* h, int on) {
         CME_CUDA(cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking));
         e->ev.resize((size_t)(e->d.L + 1) * 8);
         for (cudaEvent_t& v : e->ev) CME_CUDA(cudaEventCreateWithFlags(&v, cudaEventDisableTiming));
+        for (cudaEvent_t& v : e->ev_dq) CME_CUDA(cudaEventCreateWithFlags(&v, cudaEventDisableTiming));
     } else if (!on && e->side) {
         CME_CUDA(cudaStreamSynchronize(e->side));
         for (cudaEvent_t v : e->ev) cudaEventDestroy(v);
+        for (cudaEvent_t& v : e->ev_dq) { cudaEventDestroy(v); v = nullptr; }
         e->ev.clear();
         CME_CUDA(cudaStreamDestroy(e->side));
         e->side = nullptr;
@@ -587,7 +595,25 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         fill_attn(e, l, at);
         at.o = a.attn; at.d_o = e.dattn;
         if (below_top) TRY(need(l + 1, 3));                                 // dqkv is read by the layer above's dWqkv
+        // dQ scratch of the tensor-core kernel (arrival-order form): the layers alternate between two buffers, and a
+        // buffer is cleared on the second stream as soon as its sums have been converted -- two layers before it is
+        // needed again -- instead of by a clear in front of every launch on this stream.  Both start clear (bind), and
+        // a step ends with both cleared again, since the caller joins the second stream before the next step.
+        const bool side_clear = ov && at.dq_mode == 0 && (d.attn_backend == 0 || d.attn_backend == 1) &&
+                                attention_tc_supported(&at);
+        const int b01 = l & 1;
+        if (side_clear) {
+            at.dq_accum = b01 ? e.dq_accum2 : e.dq_accum;
+            at.dq_accum_clean = 1;
+            if (l + 2 <= d.L - 1) CME_CUDA(cudaStreamWaitEvent(st, e.ev_dq[2 + b01], 0));   // cleared after layer l + 2
+        }
         TRY(cme_attention_bwd(&at, d.attn_backend, st));
+        if (side_clear) {
+            CME_CUDA(cudaEventRecord(e.ev_dq[b01], st));
+            CME_CUDA(cudaStreamWaitEvent(ws, e.ev_dq[b01], 0));
+            CME_CUDA(cudaMemsetAsync(at.dq_accum, 0, (size_t)BT * D * 4, ws));
+            CME_CUDA(cudaEventRecord(e.ev_dq[2 + b01], ws));
+        }
         // ---- QKV projection
         TRY(ready(l, 3));                                                   // dqkv exists
         if (d.fused_qkv) {
