@@ -29,6 +29,8 @@ int cme_layernorm_fwd(int, const void*, const void*, void*, const void*, const v
 int cme_layernorm_bwd_blocks(int);
 int cme_layernorm_bwd(int, const void*, const void*, const void*, const float*, const float*, const void*, void*, void*,
                       void*, float*, int, int, int, void*);
+int cme_layernorm_bwd_split(int, const void*, const void*, const void*, const float*, const float*, const void*, void*,
+                            void*, void*, float*, int, int, int, void*, void*, void*);
 int cme_colsum_splits(int, int);
 int cme_dact_colsum(int, const void*, const void*, void*, void*, float*, int, int, int, int, void*);
 int cme_colsum_slabs_finalize(int, const float*, int, int, void*, int, void*);
@@ -96,6 +98,8 @@ struct Engine {
     float *delta, *dq_accum, *ln_scratch, *col_scratch;
     float* dq_accum2 = nullptr;     // second dQ scratch: the layers alternate, so that a layer's scratch can be cleared on the
                                     // second stream while the layer above still uses the other one
+    std::vector<cudaEvent_t> ev_ln;  // one per LayerNorm site: its main kernel has run (the sums follow on the second stream)
+    size_t ln_scratch_stride = 0;    // floats per LayerNorm site in ln_scratch (2 L + 1 sites)
     cudaEvent_t ev_dq[4] = {};      // [0..1] scratch b was converted (main stream)   [2..3] scratch b is clear (second stream)
     int* dq_sem = nullptr;          // per (batch, head, query block) counters ordering the dQ parts; zero between launches
     void* attn_ws; long long attn_ws_bytes;
@@ -158,7 +162,10 @@ size_t carve(Engine& e, char* base) {
     e.attn_ws_bytes = (d.head_flat && d.T <= 512) ? attention_gemm_ws_bytes(e.BH, d.T) : 0;
     e.attn_ws = e.attn_ws_bytes ? take((size_t)e.attn_ws_bytes) : nullptr;
     const size_t widest = FF > D ? FF : D;
-    e.ln_scratch = (float*)take((size_t)cme_layernorm_bwd_blocks((int)BT) * 2 * D * 4);
+    // one region per LayerNorm site: the sums of a site's partials run on the second stream, after the next site's
+    // main kernel may already have started
+    e.ln_scratch_stride = (size_t)cme_layernorm_bwd_blocks((int)BT) * 2 * D;
+    e.ln_scratch = (float*)take(e.ln_scratch_stride * 4 * (2 * (size_t)d.L + 1));
     e.col_scratch = (float*)take((size_t)(cme_colsum_splits((int)BT, (int)D) + cme_colsum_splits((int)BT, (int)FF)) *
                                  widest * 4);
     // split-K partials (fp32): room for four splits of the widest activation-gradient product, e.g. the LM-head
@@ -317,6 +324,7 @@ CME_API void cme_engine_destroy(void* h) {
     Engine* e = static_cast<Engine*>(h);
     for (cudaEvent_t v : e->ev) cudaEventDestroy(v);
     for (cudaEvent_t v : e->ev_dq) if (v) cudaEventDestroy(v);
+    for (cudaEvent_t v : e->ev_ln) cudaEventDestroy(v);
     if (e->side) cudaStreamDestroy(e->side);
     delete e;
 }
@@ -330,10 +338,14 @@ CME_API int cme_engine_set_overlap(void* h, int on) {
         e->ev.resize((size_t)(e->d.L + 1) * 8);
         for (cudaEvent_t& v : e->ev) CME_CUDA(cudaEventCreateWithFlags(&v, cudaEventDisableTiming));
         for (cudaEvent_t& v : e->ev_dq) CME_CUDA(cudaEventCreateWithFlags(&v, cudaEventDisableTiming));
+        e->ev_ln.resize(2 * (size_t)e->d.L + 1);
+        for (cudaEvent_t& v : e->ev_ln) CME_CUDA(cudaEventCreateWithFlags(&v, cudaEventDisableTiming));
     } else if (!on && e->side) {
         CME_CUDA(cudaStreamSynchronize(e->side));
         for (cudaEvent_t v : e->ev) cudaEventDestroy(v);
         for (cudaEvent_t& v : e->ev_dq) { cudaEventDestroy(v); v = nullptr; }
+        for (cudaEvent_t v : e->ev_ln) cudaEventDestroy(v);
+        e->ev_ln.clear();
         e->ev.clear();
         CME_CUDA(cudaStreamDestroy(e->side));
         e->side = nullptr;
@@ -496,6 +508,15 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         return CME_OK;
     };
     float* col_s = ov ? e.col_scratch_side : e.col_scratch;
+    // LayerNorm backward at `site` (2 l + 1: LN2 of block l, 2 l: LN1, 2 L: final): dx on `st`; the sums of the
+    // per-block partial d(gamma) / d(beta) follow on the second stream when there is one
+    auto ln_bwd = [&](int site, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                      const void* dres, void* dxo, void* dgamma, void* dbeta) -> int {
+        float* scr = e.ln_scratch + (size_t)site * e.ln_scratch_stride;
+        if (!ov) return cme_layernorm_bwd(dt, dy, x, gamma, mean, rstd, dres, dxo, dgamma, dbeta, scr, BT, D, accumulate, st);
+        return cme_layernorm_bwd_split(dt, dy, x, gamma, mean, rstd, dres, dxo, dgamma, dbeta, scr, BT, D, accumulate, st, ws,
+                                       e.ev_ln[(size_t)site]);
+    };
     const void* xlast = d.final_ln ? e.xf : e.x[d.L];
     char* dx = e.dxa;       // gradient w.r.t. the residual stream entering the part being processed
     char* dx_other = e.dxb;
@@ -513,8 +534,8 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         emit();
     }
     if (d.final_ln) {
-        TRY(cme_layernorm_bwd(dt, dx, e.x[d.L], e.P(e.gs.lnfg), e.meanf, e.rstdf, nullptr, dx_other, e.G(e.gs.lnfg),
-                              e.G(e.gs.lnfb), e.ln_scratch, BT, D, accumulate, st));
+        TRY(ln_bwd(2 * d.L, dx, e.x[d.L], e.P(e.gs.lnfg), e.meanf, e.rstdf, nullptr, dx_other, e.G(e.gs.lnfg),
+                   e.G(e.gs.lnfb)));
         std::swap(dx, dx_other);
         emit();
     }
@@ -580,8 +601,7 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         }
         // ---- LN2 (+ residual gradient): d x_mid = LN'(d ln2) + dx
         if (below_top) TRY(need(l + 1, 2));                                 // dx_other is read by the layer above's dWo
-        TRY(cme_layernorm_bwd(dt, e.dln, a.xmid, e.P(s.ln2g), a.mean2, a.rstd2, dx, dx_other, e.G(s.ln2g), e.G(s.ln2b),
-                              e.ln_scratch, BT, D, accumulate, st));
+        TRY(ln_bwd(2 * l + 1, e.dln, a.xmid, e.P(s.ln2g), a.mean2, a.rstd2, dx, dx_other, e.G(s.ln2g), e.G(s.ln2b)));
         std::swap(dx, dx_other);                                            // dx = d x_mid
         emit();
         // ---- attention output projection:  x_mid = x + attn @ Wo
@@ -630,8 +650,7 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         emit();
         // ---- LN1 (+ residual gradient): d x = LN'(d ln1) + d x_mid
         TRY(need(l, 0));                                                    // dx_other is still read by this layer's dW2
-        TRY(cme_layernorm_bwd(dt, e.dln, e.x[l], e.P(s.ln1g), a.mean1, a.rstd1, dx, dx_other, e.G(s.ln1g), e.G(s.ln1b),
-                              e.ln_scratch, BT, D, accumulate, st));
+        TRY(ln_bwd(2 * l, e.dln, e.x[l], e.P(s.ln1g), a.mean1, a.rstd1, dx, dx_other, e.G(s.ln1g), e.G(s.ln1b)));
         std::swap(dx, dx_other);
         emit();
     }

@@ -356,7 +356,7 @@ int ln_bwd_vec_launch(const T* dy, const T* x, const T* g, const float* mean, co
 template <typename T>
 int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, const float* rstd, const void* dres,
              void* dx, void* dgamma, void* dbeta, float* scratch, int nblocks, int rows, int D, int accumulate,
-             cudaStream_t st) {
+             cudaStream_t st, cudaStream_t fin_st = nullptr, cudaEvent_t fin_ev = nullptr) {
     constexpr int W = VecOf<T>::N;
     const bool vec = (D % W == 0) && (D / W <= 32 * LN_MAX_VEC);
     if (vec) {
@@ -375,6 +375,11 @@ int ln_bwd_t(const void* dy, const void* x, const void* g, const float* mean, co
                                       (const T*)g, mean, rstd, (const T*)dres, (T*)dx, scratch, rows, D));
     }
     CME_LAUNCH_CHECK();
+    if (fin_st != nullptr && fin_st != st) {       // the weight gradients are finished on another stream
+        CME_CUDA(cudaEventRecord(fin_ev, st));
+        CME_CUDA(cudaStreamWaitEvent(fin_st, fin_ev, 0));
+        st = fin_st;
+    }
     CME_CUDA(cme_launch_dependent(ln_bwd_finalize_kernel<T>, dim3(cme_cdiv(2 * D, 16)), dim3(256), 0, st,
                                   (const float*)scratch, nblocks, D, (T*)dgamma, (T*)dbeta, accumulate));
     CME_LAUNCH_CHECK();
@@ -412,4 +417,24 @@ CME_API int cme_layernorm_bwd(int dtype, const void* dy, const void* x, const vo
                                          accumulate, st)
                : ln_bwd_t<float>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, nb, rows, D, accumulate,
                                  st);
+}
+
+// Same, with the small kernel that sums the per-block partial d(gamma) / d(beta) on `fin_stream` (ordered after the main
+// kernel through `fin_event`, a cudaEvent_t of the caller): nothing on `stream` needs those sums, so the chain of
+// activation-gradient work on `stream` does not wait for them.  `scratch` must stay untouched until that kernel has run.
+CME_API int cme_layernorm_bwd_split(int dtype, const void* dy, const void* x, const void* gamma, const float* mean,
+                                    const float* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
+                                    float* scratch, int rows, int D, int accumulate, void* stream, void* fin_stream,
+                                    void* fin_event) {
+    cudaStream_t st = (cudaStream_t)stream;
+    CME_REQUIRE(rows > 0 && D > 0, CME_ERR_SHAPE, "layernorm: empty input");
+    CME_REQUIRE((size_t)LN_WARPS * 2 * D * 4 <= 200 * 1024, CME_ERR_LIMIT, "layernorm backward: D too large (%d)", D);
+    CME_REQUIRE(fin_stream == nullptr || fin_stream == stream || fin_event != nullptr, CME_ERR_SHAPE,
+                "layernorm backward: a second stream needs an event");
+    const int nb = cme_layernorm_bwd_blocks(rows);
+    return dtype == CME_BF16
+               ? ln_bwd_t<__nv_bfloat16>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, nb, rows, D,
+                                         accumulate, st, (cudaStream_t)fin_stream, (cudaEvent_t)fin_event)
+               : ln_bwd_t<float>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, nb, rows, D, accumulate,
+                                 st, (cudaStream_t)fin_stream, (cudaEvent_t)fin_event);
 }
