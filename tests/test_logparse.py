@@ -51,3 +51,34 @@ def test_trajectory_comparison_has_two_levels():
     assert abs(moved["max_sum_diff_per_param"] - 0.03 / 222592) < 1e-12
     off = compare_trajectories(base, parse_trajectory(mk(-0.14, 840.0, 0.25, 3.9)))
     assert not off["ok"] and "max_sum_diff_per_param" not in off
+
+
+def test_launch_list_summary(tmp_path):
+    """Profiler launch list -> per-kernel table of the last complete step (banner lines skipped, units converted,
+    template arguments kept, parameter lists dropped)."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "summarize_launches", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks",
+                                           "summarize_launches.py"))
+    sl = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sl)
+    hdr = '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"'
+    row = lambda i, k, v, unit="ns": f'"{i}","1","python","h","{k}","1","7","(128, 1, 1)","(1, 1, 1)","0","10.0","s","gpu__time_duration.sum","{unit}","{v}"'
+    names = ["void <unnamed>::embed_fwd_kernel<__nv_bfloat16>(int const*, T1*)",
+             "void gemm_tc::gemm_tc_kernel<256, 0, 1, 0, 1, 545>(CUtensorMap_st, gemm_tc::EpiParams)",
+             "<unnamed>::attn_fwd_tc_kernel(CUtensorMap_st, <unnamed>::FwdParams)",
+             "void gemm_tc::gemm_tc_kernel<256, 0, 1, 0, 1, 545>(CUtensorMap_st, gemm_tc::EpiParams)"]
+    lines = ["==PROF== Connected to process 1", hdr]
+    i = 0
+    for step in range(3):
+        for k, v in zip(names, ("12,000", "60000", "80", "40000")):
+            lines.append(row(i, k, v, "us" if v == "80" else "ns"))
+            i += 1
+    p = tmp_path / "launches.csv"
+    p.write_text("\n".join(lines) + "\n")
+    s = sl.summarize(sl.last_step(sl.read_launches(str(p)), "embed_fwd"))
+    assert s["launches"] == 4 and abs(s["total_us"] - (12 + 60 + 80 + 40)) < 1e-9
+    top = s["kernels"][0]
+    assert top["kernel"] == "gemm_tc_kernel<256,0,1,0,1,545>" and top["launches"] == 2 and abs(top["total_us"] - 100) < 1e-9
+    assert s["kernels"][1]["kernel"] == "attn_fwd_tc_kernel" and "| `attn_fwd_tc_kernel` | 1 | 80 |" in sl.to_markdown(s)
