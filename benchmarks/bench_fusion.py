@@ -120,6 +120,27 @@ def main():
         opt.step()
         comp.copy_(pt.detach())            # and the bf16 copy of the parameters is one more pass
     rec("adamw step (vs torch fused AdamW + casts)", fused, time_kernel(unf7, 3, a.iters, fl), n * 30)
+
+    # token + position embedding, forward and backward (tied-table scatter with atomics), GPT-2 small sizes, against
+    # torch.nn.functional.embedding and its index_add backward
+    V, T, D, B = 50304, 1024, 768, 16
+    tok_w, pos_w = torch.randn(V, D, device="cuda").to(bf), torch.randn(T, D, device="cuda").to(bf)
+    ids = torch.randint(0, V, (B * T,), device="cuda", dtype=torch.int32)
+    ids64 = ids.long()
+    pos_ids = torch.arange(T, device="cuda").repeat(B)
+    dout = torch.randn(B * T, D, device="cuda").to(bf)
+    fused = time_kernel(lambda: ops.embedding_fwd(ids, tok_w, pos_w), 3, a.iters, fl)
+    unf8 = lambda: torch.nn.functional.embedding(ids64, tok_w) + torch.nn.functional.embedding(pos_ids, pos_w)
+    rec("embedding fwd, token + position (vs torch)", fused, time_kernel(unf8, 3, a.iters, fl), B * T * D * 2 * 2)
+    dtok, dpos = torch.zeros(V, D, device="cuda", dtype=bf), torch.zeros(T, D, device="cuda", dtype=bf)
+    fused = time_kernel(lambda: ops.embedding_bwd(ids, dout, V, T, dtok=dtok, dpos=dpos, accumulate=True), 3, a.iters, fl)
+    gt, gp = torch.zeros(V, D, device="cuda", dtype=bf), torch.zeros(T, D, device="cuda", dtype=bf)
+
+    def unf9():
+        gt.index_add_(0, ids64, dout)
+        gp.index_add_(0, pos_ids, dout)
+    rec("embedding bwd, scatter-add into both tables (vs torch index_add)", fused, time_kernel(unf9, 3, a.iters, fl),
+        B * T * D * 2 * 3)
     if a.json:
         json.dump(out, open(a.json, "w"), indent=1)
 
