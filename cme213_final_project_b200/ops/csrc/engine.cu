@@ -662,8 +662,20 @@ CME_API int cme_engine_backward(void* h, const int* tokens, int accumulate, CmeB
         CME_CUDA(cudaEventRecord(fin, ws));
         CME_CUDA(cudaStreamWaitEvent(st, fin, 0));
     }
-    TRY(cme_embedding_bwd(dt, tokens, dx, e.G(e.gs.tok), nullptr, BT, d.T, D, V, (d.tied || accumulate) ? 1 : 0, st));
-    TRY(cme_embedding_bwd(dt, tokens, dx, nullptr, e.G(e.gs.pos), BT, d.T, D, V, accumulate, st));
+    // the two tables are independent: the position table's sums run on the second stream beside the token scatter,
+    // and join before the last bucket is handed over
+    if (ov) {
+        cudaEvent_t dx0 = evt(d.L, 6), posd = evt(d.L, 7);
+        CME_CUDA(cudaEventRecord(dx0, st));
+        CME_CUDA(cudaStreamWaitEvent(ws, dx0, 0));
+        TRY(cme_embedding_bwd(dt, tokens, dx, nullptr, e.G(e.gs.pos), BT, d.T, D, V, accumulate, ws));
+        CME_CUDA(cudaEventRecord(posd, ws));
+        TRY(cme_embedding_bwd(dt, tokens, dx, e.G(e.gs.tok), nullptr, BT, d.T, D, V, (d.tied || accumulate) ? 1 : 0, st));
+        CME_CUDA(cudaStreamWaitEvent(st, posd, 0));
+    } else {
+        TRY(cme_embedding_bwd(dt, tokens, dx, e.G(e.gs.tok), nullptr, BT, d.T, D, V, (d.tied || accumulate) ? 1 : 0, st));
+        TRY(cme_embedding_bwd(dt, tokens, dx, nullptr, e.G(e.gs.pos), BT, d.T, D, V, accumulate, st));
+    }
     emit();
     return CME_OK;
 }
